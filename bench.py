@@ -1,0 +1,589 @@
+"""Benchmark of the B200 execution path for cantors-gift Executables.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload gemm|eltwise|rowreduce|matmul_f32]
+                    [--impl ours|reference] [--no-also]
+
+One JSON line on stdout (rank 0). The headline workload is the bf16 4096^3 GEMM with fused
+bias + GELU(tanh) (TFLOP/s); the memory-bound kernels of the path (fused elementwise chain,
+softmax -> layernorm; GB/s) and the fp32 1024^3 matmul are reported in the same line under
+"also". All inputs are seeded synthetic data of the configured shapes.
+
+Timing: W >= 3 warm-up steps, then K steps between two CUDA events on the launching stream,
+bracketed by barrier + synchronize, max over ranks. Memory-bound workloads stream inputs larger
+than L2 every step; the GEMM rotates over buffer sets larger than L2.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+METRIC = "fused bf16 GEMM TFLOP/s & elementwise/softmax GB/s vs roofline"
+PROG_CHAIN = [("input", 0), ("input", 1), "mul", ("input", 2), "add", "relu", ("imm", 0.5), "mul"]
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
+# profiles/ (None until a capture exists for that kernel).
+NCU_TRAFFIC_BYTES = {"gemm": None, "eltwise": None, "rowreduce": None, "matmul_f32": None}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---- workloads -----------------------------------------------------------------------------------
+class Workload:
+    """A step = one pass of the hot path over one batch of synthetic input."""
+    name = ""
+    unit = ""
+    bound = ""
+    dtype = ""
+    launches_per_step = 1
+
+    def setup(self, rank, world):
+        raise NotImplementedError
+
+    def step(self, i):
+        raise NotImplementedError
+
+    def work_per_step(self):            # in the metric's numerator unit (GB or TFLOP), whole job
+        raise NotImplementedError
+
+    def algorithmic_per_launch(self):   # bytes or flop of the dominant kernel, per launch, this rank
+        raise NotImplementedError
+
+
+class EltwiseWorkload(Workload):
+    name, unit, bound, dtype = "eltwise", "GB/s", "hbm", "f32"
+    n = 1 << 26
+
+    def config(self, world):
+        return {"workload": "cfg2: y=relu(a*b+c)*0.5 over 2^26 fp32 per GPU, one fused kernel",
+                "elements_per_gpu": self.n, "l2": "inputs (768 MiB) larger than L2 every step",
+                "parallelism": f"replicas x{world}"}
+
+    def setup(self, rank, world):
+        import torch
+        from cantors_gift_b200 import capi
+        self.world = world
+        g = torch.Generator(device="cuda").manual_seed(1 + rank)
+        self.ins = [torch.randn(self.n, device="cuda", generator=g) for _ in range(3)]
+        self.out = torch.empty(self.n, device="cuda")
+        self.desc = capi.make_eltwise_desc(capi.F32, PROG_CHAIN, ["full"] * 3)
+
+    def step(self, i):
+        from cantors_gift_b200 import ops
+        ops.eltwise(self.desc, self.ins, self.out)
+
+    def work_per_step(self):
+        return 4 * 4 * self.n * self.world / 1e9
+
+    def algorithmic_per_launch(self):
+        return 4 * 4 * self.n
+
+    # end to end: host buffers in, host buffer out
+    def e2e_setup(self):
+        import torch
+        from cantors_gift_b200 import ops
+        self.runner = ops.HostRunner()
+        self.h_in = [t.cpu().pin_memory() for t in self.ins]
+        self.h_out = torch.empty(self.n, dtype=torch.float32).pin_memory()
+        return 3 * 4 * self.n, 4 * self.n
+
+    def e2e_step(self):
+        import ctypes as C
+        from cantors_gift_b200 import capi
+        r = self.runner
+        d = [r.h2d(f"in{k}", h) for k, h in enumerate(self.h_in)]
+        o = r.dev("out", 4 * self.n)
+        arr = (C.c_void_p * 3)(*[p.value for p in d])
+        capi.check(capi.lib().cg_b200_eltwise(C.byref(self.desc), arr, 3, o, self.n, r.stream), "eltwise")
+        r.d2h(self.h_out, o)
+        r.sync()
+
+    def cpu_baseline(self, budget_s, prefer_ref=True):
+        from oracle import oracle as O
+        n = self.n
+        rng = np.random.default_rng(1)
+        a, b, c = (rng.standard_normal(n, dtype=np.float32) for _ in range(3))
+        out = np.empty_like(a)
+        threads = os.cpu_count() or 1
+        if prefer_ref and O.have_ref():
+            kind = "reference"
+            run = lambda: O.ref_fma_relu_scale(a, b, c, 0.5, threads=threads, out=out)  # noqa: E731
+        else:
+            kind = "port"
+            O.set_num_threads(threads)
+            d = O.make_eltwise_desc(O.F32, PROG_CHAIN, ["full"] * 3)
+            run = lambda: O.eltwise(d, [a, b, c], n)  # noqa: E731
+        run()
+        t0 = time.perf_counter()
+        reps = 0
+        while reps < 3 or (time.perf_counter() - t0 < min(budget_s, 10.0) and reps < 200):
+            run()
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps
+        return {"value": 16 * n / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
+                "sample": f"the full 2^26-element chain, {reps} repetitions"}, dt
+
+
+class RowReduceWorkload(Workload):
+    name, unit, bound, dtype = "rowreduce", "GB/s", "hbm", "bf16"
+    rows, cols = 32768, 4096
+
+    def config(self, world):
+        return {"workload": "cfg4: layernorm(softmax(x)), bf16 [32768, 4096] per GPU, eps 1e-5, one fused kernel",
+                "l2": "input + output (512 MiB) larger than L2 every step", "parallelism": f"replicas x{world}"}
+
+    def setup(self, rank, world):
+        import torch
+        self.world = world
+        g = torch.Generator(device="cuda").manual_seed(3 + rank)
+        self.x = torch.randn(self.rows, self.cols, device="cuda", generator=g).to(torch.bfloat16)
+        self.y = torch.empty_like(self.x)
+
+    def step(self, i):
+        from cantors_gift_b200 import ops
+        ops.softmax_layernorm(self.x, eps=1e-5, out=self.y)
+
+    def work_per_step(self):
+        return 2 * 2 * self.rows * self.cols * self.world / 1e9
+
+    def algorithmic_per_launch(self):
+        return 2 * 2 * self.rows * self.cols
+
+    def e2e_setup(self):
+        import torch
+        from cantors_gift_b200 import ops
+        self.runner = ops.HostRunner()
+        self.h_x = self.x.cpu().pin_memory()
+        self.h_y = torch.empty_like(self.h_x).pin_memory()
+        nb = 2 * self.rows * self.cols
+        return nb, nb
+
+    def e2e_step(self):
+        from cantors_gift_b200 import capi
+        r = self.runner
+        nb = 2 * self.rows * self.cols
+        d = r.h2d("x", self.h_x)
+        o = r.dev("y", nb)
+        capi.check(capi.lib().cg_b200_softmax_layernorm(capi.BF16, d, None, None, 1e-5, o, self.rows, self.cols,
+                                                        r.stream), "softmax_layernorm")
+        r.d2h(self.h_y, o)
+        r.sync()
+
+    def cpu_baseline(self, budget_s, prefer_ref=True):
+        from oracle import oracle as O
+        threads = os.cpu_count() or 1
+        O.set_num_threads(threads)
+        rows = 4096
+        rng = np.random.default_rng(3)
+        x = O.to_bf16(rng.standard_normal((rows, self.cols), dtype=np.float32))
+        O.softmax_layernorm(x, O.BF16)
+        t0 = time.perf_counter()
+        reps = 0
+        while reps < 2 or (time.perf_counter() - t0 < min(budget_s, 10.0) and reps < 100):
+            O.softmax_layernorm(x, O.BF16)
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps
+        return {"value": 4 * rows * self.cols / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+                "sample": f"{rows} of {self.rows} rows, {reps} repetitions (the reference has no executable "
+                          "softmax/layernorm)"}, dt * self.rows / rows
+
+
+class GemmWorkload(Workload):
+    """bf16 M=N=K=4096, C = gelu_tanh(A B + bias); M-sharded over the ranks, in-place all-gather."""
+    name, unit, bound, dtype = "gemm", "TFLOP/s", "tensor", "bf16"
+    M = N = K = 4096
+    in_dtype_name, epilogue = "BF16", "bias_gelu_tanh"
+    sets = 4
+
+    def config(self, world):
+        return {"workload": "cfg3: bf16 GEMM M=N=K=4096 + bias + GELU(tanh), fp32 accumulate",
+                "M": self.M, "N": self.N, "K": self.K,
+                "l2": f"rotating over {self.sets} (A, B, C) buffer sets, 384 MiB > L2",
+                "parallelism": "1 GPU" if world == 1 else f"M-sharded x{world}, in-place NCCL all-gather of C"}
+
+    def setup(self, rank, world):
+        import torch
+        from cantors_gift_b200 import capi
+        self.rank, self.world = rank, world
+        assert self.M % world == 0
+        self.Ms = self.M // world
+        in_dt = getattr(capi, self.in_dtype_name)
+        tdt = {"BF16": torch.bfloat16, "F32": torch.float32}[self.in_dtype_name]
+        g = torch.Generator(device="cuda").manual_seed(2)          # same data on every rank
+        scale = 0.02 if self.in_dtype_name == "BF16" else 1.0
+        self.A, self.B, self.C = [], [], []
+        for _ in range(self.sets):
+            if self.in_dtype_name == "BF16":
+                A = (torch.randn(self.M, self.K, device="cuda", generator=g) * scale).to(tdt)
+                B = (torch.randn(self.K, self.N, device="cuda", generator=g) * scale).to(tdt)
+            else:
+                A = torch.rand(self.M, self.K, device="cuda", generator=g) * 2 - 1
+                B = torch.rand(self.K, self.N, device="cuda", generator=g) * 2 - 1
+            self.A.append(A[rank * self.Ms:(rank + 1) * self.Ms].contiguous())
+            self.B.append(B)
+            self.C.append(torch.empty(self.M, self.N, device="cuda", dtype=tdt))
+        self.bias = torch.randn(self.N, device="cuda", generator=g).to(tdt)
+        self.desc = capi.make_gemm_desc(self.Ms, self.N, self.K, in_dt, in_dt, epilogue=self.epilogue)
+        self.ws, self.ws_bytes = None, 0
+        from cantors_gift_b200 import ops
+        self.ws, self.ws_bytes = ops.gemm_workspace(self.desc, self.A[0].device)
+        self.comm = None
+        if world > 1:
+            self.comm = make_comm(rank, world)
+        self.launches_per_step = 1 if self.in_dtype_name == "BF16" else 3
+
+    def step(self, i):
+        import ctypes as C
+        from cantors_gift_b200 import capi, ops
+        s = i % self.sets
+        c_shard = self.C[s][self.rank * self.Ms:(self.rank + 1) * self.Ms]
+        ops.gemm(self.desc, self.A[s], self.B[s], c_shard, bias=self.bias if self.epilogue != "none" else None,
+                 workspace=self.ws)
+        if self.comm is not None:
+            import torch
+            shard_bytes = self.Ms * self.N * self.C[s].element_size()
+            capi.check(capi.lib().cg_b200_allgather_inplace(self.comm, C.c_void_p(self.C[s].data_ptr()), shard_bytes,
+                                                            C.c_void_p(torch.cuda.current_stream().cuda_stream)),
+                       "allgather_inplace")
+
+    def flops(self):
+        return 2.0 * self.M * self.N * self.K
+
+    def work_per_step(self):
+        return self.flops() / 1e12
+
+    def algorithmic_per_launch(self):
+        return self.flops() / self.world
+
+    def e2e_setup(self):
+        import torch
+        from cantors_gift_b200 import ops
+        self.runner = ops.HostRunner()
+        self.h_A = self.A[0].cpu().pin_memory()
+        self.h_B = self.B[0].cpu().pin_memory()
+        self.h_bias = self.bias.cpu().pin_memory()
+        self.h_C = torch.empty(self.Ms, self.N, dtype=self.A[0].dtype).pin_memory()
+        es = self.h_A.element_size()
+        if self.ws_bytes:
+            self.runner.dev("ws", self.ws_bytes)
+        return (self.h_A.numel() + self.h_B.numel() + self.h_bias.numel()) * es, self.h_C.numel() * es
+
+    def e2e_step(self):
+        import ctypes as C
+        from cantors_gift_b200 import capi
+        r = self.runner
+        a, b, bias = r.h2d("A", self.h_A), r.h2d("B", self.h_B), r.h2d("bias", self.h_bias)
+        c = r.dev("C", self.h_C.numel() * self.h_C.element_size())
+        ws = r.dev("ws", self.ws_bytes) if self.ws_bytes else None
+        capi.check(capi.lib().cg_b200_gemm(C.byref(self.desc), a, b, bias if self.epilogue != "none" else None, None,
+                                           c, ws, self.ws_bytes, r.stream), "gemm")
+        r.d2h(self.h_C, c)
+        r.sync()
+
+    def cpu_baseline(self, budget_s, prefer_ref=True):
+        from oracle import oracle as O
+        threads = os.cpu_count() or 1
+        O.set_num_threads(threads)
+        M, N, K = self.M, self.N, self.K
+        rng = np.random.default_rng(2)
+        if self.in_dtype_name == "BF16":
+            dt = O.BF16
+            A = O.to_bf16(rng.standard_normal((M, K), dtype=np.float32) * 0.02)
+            B = O.to_bf16(rng.standard_normal((K, N), dtype=np.float32) * 0.02)
+            bias = O.to_bf16(rng.standard_normal(N, dtype=np.float32))
+        else:
+            dt = O.F32
+            A = (rng.random((M, K), dtype=np.float32) * 2 - 1).astype(np.float32)
+            B = (rng.random((K, N), dtype=np.float32) * 2 - 1).astype(np.float32)
+            bias = None
+        d = O.make_gemm_desc(M, N, K, dt, dt, epilogue=self.epilogue)
+        probe = np.arange(0, min(M, 4 * threads), dtype=np.int64)
+        out = np.zeros(M * N, dtype=O.NP_OF[dt])
+        t0 = time.perf_counter()
+        O.gemm(d, A, B, bias=bias, rows=probe, out=out)
+        per_row = (time.perf_counter() - t0) / probe.size
+        n_rows = int(max(threads, min(M, budget_s / max(per_row, 1e-9))))
+        rows = np.arange(0, n_rows, dtype=np.int64)
+        t0 = time.perf_counter()
+        O.gemm(d, A, B, bias=bias, rows=rows, out=out)
+        dt_s = time.perf_counter() - t0
+        return {"value": 2.0 * n_rows * N * K / dt_s / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                "sample": f"rows 0..{n_rows} of {M} (all N and K), sequential-k fp32 FMA chain as the reference's "
+                          "scalar JIT matmul, vectorised over n; the reference has no bf16/epilogue code"}, dt_s * M / n_rows
+
+
+class MatmulF32Workload(GemmWorkload):
+    """fp32 M=N=K=1024 through the 3xTF32 split (latency-bound: about 2 GFLOP per launch)."""
+    name, dtype = "matmul_f32", "f32 (3xTF32)"
+    M = N = K = 1024
+    in_dtype_name, epilogue = "F32", "none"
+    sets = 16
+
+    def config(self, world):
+        return {"workload": "cfg1: fp32 matmul M=N=K=1024 (3xTF32 split + tcgen05 kind::tf32)",
+                "l2": f"rotating over {self.sets} buffer sets, 192 MiB > L2", "parallelism": f"x{world}"}
+
+
+WORKLOADS = {"gemm": GemmWorkload, "eltwise": EltwiseWorkload, "rowreduce": RowReduceWorkload,
+             "matmul_f32": MatmulF32Workload}
+
+
+def make_comm(rank, world):
+    """One NCCL communicator through the C ABI; the id travels over torch.distributed."""
+    import ctypes as C
+    import torch
+    import torch.distributed as dist
+    from cantors_gift_b200 import capi
+    idbuf = (C.c_char * capi.COMM_ID_BYTES)()
+    if rank == 0:
+        capi.check(capi.lib().cg_b200_comm_unique_id(idbuf), "comm_unique_id")
+    t = torch.frombuffer(bytearray(bytes(idbuf)), dtype=torch.uint8).cuda()
+    dist.broadcast(t, src=0)
+    raw = bytes(t.cpu().numpy().tobytes())
+    comm = C.c_void_p()
+    capi.check(capi.lib().cg_b200_comm_init_rank(C.byref(comm), world, rank, raw), "comm_init_rank")
+    return comm
+
+
+def time_workload(w, steps, warmup, rank, world, sample_clocks):
+    """Returns (seconds for `steps` steps, max over ranks; clocks dict)."""
+    import torch
+    import torch.distributed as dist
+    for i in range(warmup):
+        w.step(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(torch.cuda.current_device()) if sample_clocks else None
+    if sampler:
+        sampler.start()
+        time.sleep(0.25)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        w.step(warmup + i)
+    e1.record()
+    torch.cuda.synchronize()
+    secs = e0.elapsed_time(e1) * 1e-3
+    if world > 1:
+        dist.barrier()
+        t = torch.tensor([secs], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        secs = float(t.item())
+    clocks = sampler.stop() if sampler else None
+    return secs, clocks
+
+
+def time_e2e(w, steps, warmup, world):
+    import torch
+    import torch.distributed as dist
+    h2d, d2h = w.e2e_setup()
+    for _ in range(max(1, min(warmup, 3))):
+        w.e2e_step()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        w.e2e_step()
+    secs = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([secs], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        secs = float(t.item())
+    w.runner.close()
+    return secs, h2d, d2h
+
+
+def run_workload(name, steps, warmup, rank, world, peaks, sample_clocks, with_cpu, cpu_budget):
+    w = WORKLOADS[name]()
+    w.setup(rank, world)
+    secs, clocks = time_workload(w, steps, warmup, rank, world, sample_clocks)
+    ms_per_step = secs / steps * 1e3
+    value = w.work_per_step() * steps / secs
+    e2e_steps = max(3, min(steps, 10))
+    e_secs, h2d, d2h = time_e2e(w, e2e_steps, warmup, world)
+    e2e_work = w.work_per_step() if name not in ("gemm", "matmul_f32") else w.work_per_step()
+    if w.bound == "hbm":
+        achieved = w.algorithmic_per_launch() / (secs / steps) / 1e9
+        peak, unit = peaks["hbm_gbs"], "GB/s"
+    else:
+        achieved = w.algorithmic_per_launch() / (secs / steps) / 1e12
+        peak, unit = peaks["bf16_tflops_sustained"], "TFLOP/s"
+    res = {
+        "metric": METRIC, "value": value, "unit": w.unit, "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong" if name in ("gemm", "matmul_f32") else "weak", "vs_baseline": None,
+        "dtype": w.dtype, "data": "synthetic", "config": w.config(world),
+        "e2e": {"value": e2e_work * e2e_steps / e_secs, "unit": w.unit, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                "note": "host buffers through the C ABI: H2D copies, kernel, D2H copy, stream sync per step"},
+        "gpu_launches": steps * w.launches_per_step,
+        "roofline": {"bound": w.bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+                     "traffic": NCU_TRAFFIC_BYTES.get(name), "peak_source": peaks["source"] +
+                     (" (sustained cuBLAS bf16)" if w.bound == "tensor" else " (copy bandwidth)"),
+                     "note": "per rank; achieved = algorithmic work per launch / mean step time on the device"
+                             + (" (includes the all-gather)" if world > 1 and name in ("gemm", "matmul_f32") else "")},
+    }
+    if clocks is not None:
+        res["clocks"] = clocks
+    if with_cpu and rank == 0:
+        cpu, _ = w.cpu_baseline(cpu_budget)
+        res["cpu_baseline"] = cpu
+    del w
+    import torch
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_reference_arm(args, rank, world):
+    """The reference's CPU implementation of the path on the host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    w = WORKLOADS[args.workload]()
+    w.world = 1
+    budget = 4.0
+    for _ in range(args.warmup):
+        w.cpu_baseline(budget if args.workload != "gemm" else 1.0)
+    vals, secs = [], []
+    t_all = time.perf_counter()
+    for _ in range(args.steps):
+        cpu, full_secs = w.cpu_baseline(budget)
+        vals.append(cpu["value"])
+        secs.append(full_secs)
+        if time.perf_counter() - t_all > 150:
+            break
+    v = float(np.median(vals))
+    cpu["value"] = v
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": w.unit, "n_gpus": args.gpus,
+            "steps": len(vals), "warmup": args.warmup, "ms_per_step": float(np.median(secs)) * 1e3,
+            "higher_is_better": True, "scaling": "strong" if args.workload in ("gemm", "matmul_f32") else "weak",
+            "vs_baseline": None, "dtype": w.dtype, "data": "synthetic", "config": w.config(1),
+            "cpu_baseline": cpu,
+            "e2e": {"value": v, "unit": w.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+            "note": "CPU arm: ms_per_step is the sample's time scaled to the full workload"}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="gemm", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-also", action="store_true", help="skip the secondary workloads")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return 0
+
+    import torch
+    import torch.distributed as dist
+    import cantors_gift_b200  # noqa: F401  (fails loudly if the CUDA library is missing)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if world != args.gpus and rank == 0:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
+    peaks = measured_peaks()
+
+    line = run_workload(args.workload, args.steps, args.warmup, rank, world, peaks, sample_clocks=(rank == 0),
+                        with_cpu=(world == 1 and not args.no_cpu), cpu_budget=12.0)
+    if not args.no_also and world == 1:
+        also = []
+        for other in ("eltwise", "rowreduce", "matmul_f32"):
+            if other == args.workload:
+                continue
+            r = run_workload(other, args.steps, args.warmup, rank, world, peaks, sample_clocks=True,
+                             with_cpu=not args.no_cpu, cpu_budget=5.0)
+            also.append({k: r[k] for k in ("value", "unit", "ms_per_step", "dtype", "config", "e2e", "roofline",
+                                           "gpu_launches", "clocks", "cpu_baseline") if k in r})
+        line["also"] = also
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,108 @@
+// comm.cu - the one collective of the path: an in-place all-gather of M- or batch-sharded
+// outputs over NCCL (NVLink 5 / NVSwitch inside one box).
+//
+// The reference has no collective and no multi-device runtime; its only parallel execution
+// is the std::thread fan-out of include/cg/backend/parallel_executor.hpp:49-92. One process
+// drives one GPU; rank 0 makes the id, the caller ships it to the other ranks.
+//
+// NCCL is bound at run time with dlopen so that a process which already holds an NCCL (for
+// instance through torch.distributed) shares that copy instead of loading a second one.
+#include <dlfcn.h>
+#include <string.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace cgb {
+
+struct NcclId {
+    char internal[CG_B200_COMM_ID_BYTES];
+};
+typedef int (*GetUniqueIdFn)(NcclId*);
+typedef int (*CommInitRankFn)(void**, int, NcclId, int);
+typedef int (*AllGatherFn)(const void*, void*, size_t, int, void*, cudaStream_t);
+typedef int (*CommDestroyFn)(void*);
+
+struct NcclApi {
+    void* handle = nullptr;
+    GetUniqueIdFn get_unique_id = nullptr;
+    CommInitRankFn comm_init_rank = nullptr;
+    AllGatherFn all_gather = nullptr;
+    CommDestroyFn comm_destroy = nullptr;
+    bool ok = false;
+};
+
+static NcclApi& nccl() {
+    static NcclApi api;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        const char* names[] = {"libnccl.so.2", "libnccl.so"};
+        for (const char* n : names) {
+            api.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+            if (api.handle) break;
+        }
+        if (!api.handle) return;
+        api.get_unique_id = (GetUniqueIdFn)dlsym(api.handle, "ncclGetUniqueId");
+        api.comm_init_rank = (CommInitRankFn)dlsym(api.handle, "ncclCommInitRank");
+        api.all_gather = (AllGatherFn)dlsym(api.handle, "ncclAllGather");
+        api.comm_destroy = (CommDestroyFn)dlsym(api.handle, "ncclCommDestroy");
+        api.ok = api.get_unique_id && api.comm_init_rank && api.all_gather && api.comm_destroy;
+    });
+    return api;
+}
+
+struct Comm {
+    void* nccl_comm;
+    int world;
+    int rank;
+};
+
+}  // namespace cgb
+
+using namespace cgb;
+
+extern "C" int cg_b200_comm_unique_id(void* host_unique_id) {
+    if (!host_unique_id) return CG_B200_ERR_NULL_POINTER;
+    NcclApi& api = nccl();
+    if (!api.ok) return CG_B200_ERR_COMM;
+    NcclId id;
+    if (api.get_unique_id(&id) != 0) return CG_B200_ERR_COMM;
+    memcpy(host_unique_id, &id, sizeof(id));
+    return CG_B200_OK;
+}
+
+extern "C" int cg_b200_comm_init_rank(void** comm, int world, int rank, const void* host_unique_id) {
+    if (!comm || !host_unique_id) return CG_B200_ERR_NULL_POINTER;
+    *comm = nullptr;
+    if (world < 1 || rank < 0 || rank >= world) return CG_B200_ERR_INVALID_ARG;
+    int st = require_sm100();
+    if (st) return st;
+    NcclApi& api = nccl();
+    if (!api.ok) return CG_B200_ERR_COMM;
+    NcclId id;
+    memcpy(&id, host_unique_id, sizeof(id));
+    void* c = nullptr;
+    if (api.comm_init_rank(&c, world, id, rank) != 0) return CG_B200_ERR_COMM;
+    *comm = new Comm{c, world, rank};
+    return CG_B200_OK;
+}
+
+extern "C" int cg_b200_allgather_inplace(void* comm, void* buf, size_t shard_bytes, void* stream) {
+    if (!comm) return CG_B200_ERR_NULL_POINTER;
+    if (shard_bytes == 0) return CG_B200_OK;
+    if (!buf) return CG_B200_ERR_NULL_POINTER;
+    Comm* c = static_cast<Comm*>(comm);
+    const char* send = static_cast<const char*>(buf) + (size_t)c->rank * shard_bytes;
+    // datatype 0 = ncclInt8: the shards are opaque bytes
+    if (nccl().all_gather(send, buf, shard_bytes, 0, c->nccl_comm, (cudaStream_t)stream) != 0) return CG_B200_ERR_COMM;
+    return CG_B200_OK;
+}
+
+extern "C" int cg_b200_comm_destroy(void* comm) {
+    if (!comm) return CG_B200_OK;
+    Comm* c = static_cast<Comm*>(comm);
+    int r = nccl().comm_destroy(c->nccl_comm);
+    delete c;
+    return r == 0 ? CG_B200_OK : CG_B200_ERR_COMM;
+}

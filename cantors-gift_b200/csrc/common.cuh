@@ -1,0 +1,94 @@
+// common.cuh - shared host/device helpers of the cg_b200 library (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "cg_b200.h"
+
+namespace cgb {
+
+// ---- host-side status plumbing -------------------------------------------------------------
+// Last CUDA error text seen by this thread, appended to cg_b200_status_string(ERR_CUDA)
+// callers that want detail can read it through cg_b200_last_cuda_error().
+void note_cuda_error(cudaError_t e, const char* where);
+
+#define CGB_CUDA(call)                                        \
+    do {                                                      \
+        cudaError_t e__ = (call);                             \
+        if (e__ != cudaSuccess) {                             \
+            ::cgb::note_cuda_error(e__, #call);               \
+            return e__ == cudaErrorNoDevice || e__ == cudaErrorInsufficientDriver \
+                       ? CG_B200_ERR_NO_DEVICE                \
+                       : CG_B200_ERR_CUDA;                    \
+        }                                                     \
+    } while (0)
+
+// CG_B200_OK when a device of compute capability 10.x is current; cached per device.
+int require_sm100();
+int sm_count();
+
+inline bool dtype_ok(int dt) { return dt == CG_B200_F16 || dt == CG_B200_BF16 || dt == CG_B200_F32; }
+inline size_t dtype_bytes(int dt) { return dt == CG_B200_F32 ? 4 : 2; }
+inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// Device error word shared by kernels with bounded waits (0 = no error).
+uint32_t* device_error_word();   // device pointer, lazily allocated per device; nullptr on failure
+
+// ---- device-side element conversion -----------------------------------------------------------
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+    static constexpr int dtype = CG_B200_F32;
+    __device__ static float to_f32(float v) { return v; }
+    __device__ static float from_f32(float v) { return v; }
+};
+template <> struct Elem<__nv_bfloat16> {
+    static constexpr int dtype = CG_B200_BF16;
+    __device__ static float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+    __device__ static __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
+};
+template <> struct Elem<__half> {
+    static constexpr int dtype = CG_B200_F16;
+    __device__ static float to_f32(__half v) { return __half2float(v); }
+    __device__ static __half from_f32(float v) { return __float2half_rn(v); }
+};
+
+// A 16-byte packet of T.
+template <typename T> struct alignas(16) Vec16 {
+    static constexpr int N = 16 / sizeof(T);
+    T v[N];
+};
+
+template <typename T>
+__device__ __forceinline__ Vec16<T> ld_stream(const T* p) {
+    // read-once data: bypass L1 allocation
+    const int4 r = __ldcs(reinterpret_cast<const int4*>(p));
+    Vec16<T> o;
+    *reinterpret_cast<int4*>(&o) = r;
+    return o;
+}
+template <typename T>
+__device__ __forceinline__ Vec16<T> ld_keep(const T* p) {
+    const int4 r = __ldg(reinterpret_cast<const int4*>(p));
+    Vec16<T> o;
+    *reinterpret_cast<int4*>(&o) = r;
+    return o;
+}
+template <typename T>
+__device__ __forceinline__ void st_stream(T* p, const Vec16<T>& v) {
+    __stcs(reinterpret_cast<int4*>(p), *reinterpret_cast<const int4*>(&v));
+}
+
+// gelu, tanh form: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), every product rounded
+// separately so the value does not depend on contraction choices.
+__device__ __forceinline__ float gelu_tanh_f32(float x) {
+    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+    float x3 = __fmul_rn(__fmul_rn(x, x), x);
+    float t = __fadd_rn(x, __fmul_rn(k1, x3));
+    float u = __fmul_rn(k0, t);
+    return __fmul_rn(__fmul_rn(0.5f, x), __fadd_rn(1.0f, tanhf(u)));
+}
+
+}  // namespace cgb

@@ -1,0 +1,748 @@
+// gemm_sm100.cu - C = epilogue(A x B) on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+// Stands where the reference lowers OP_MATMUL to 3 Const, 2 shared VectorLoad and K/k_tile
+// FMA instructions on one thread's registers (src/lowering/tensor_to_codegen.cpp:137-210)
+// and where its tensor-core text generator prints an mma.sync m16n8k16 skeleton with the
+// global->shared copies elided (src/backend/tensor_core/ptx_mma.cpp:115-258). Neither is
+// executable. The only matmul the reference runs is the scalar x86 FMA loop of
+// benchmarks/benchmark.py:326-438; parity is defined against that accumulation.
+//
+// Structure (one CTA per SM, persistent over output tiles, 192 threads):
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of A and B k-blocks (128 bytes of K
+//               per row, 128-byte swizzle) into a ring of shared-memory stages
+//   warp 1      TMEM allocator + single-thread tcgen05.mma issuer; tcgen05.commit releases
+//               a stage / publishes an accumulator through mbarriers
+//   warps 2-5   epilogue: tcgen05.ld of the fp32 accumulator (one TMEM lane = one row),
+//               bias / activation / residual in registers, packed stores to C
+// Two accumulators of BN columns live in TMEM so the epilogue of tile i overlaps the
+// main loop of tile i+1. fp32 inputs use kind::tf32 on a hi/lo split prepared by a
+// pre-pass (3 MMAs per k-step: lo*hi, hi*lo, hi*hi).
+//
+// Tensor-core bound: 2*M*N*K flop per problem. Every device-side wait is bounded; when a
+// wait runs out the kernel records an error word, stops waiting everywhere, drains its
+// copies, frees TMEM and returns.
+#include <cuda.h>
+#include <string.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace cgb {
+
+constexpr int kBM = 128;            // rows per tile = TMEM lanes
+constexpr int kRowBytes = 128;      // bytes of K per row per stage (one swizzle span)
+constexpr int kUmmaKBytes = 32;     // bytes of K one tcgen05.mma consumes per row
+constexpr int kThreads = 192;
+constexpr int kMaxStages = 6;
+constexpr int kSmemBudget = 200 * 1024;
+constexpr uint32_t kTmemCols = 512;
+
+struct GemmParams {
+    long long M, N, K, batch;
+    long long ldc, batch_stride_c;
+    const void* bias;
+    const void* residual;
+    void* C;
+    int epilogue;
+    float alpha;
+    int b_mn_major;       // 1: B is [K, N] row-major (N contiguous); 0: B is [N, K]
+    int a_batched, b_batched;
+    int tiles_m, tiles_n;
+    long long num_tiles;
+    int num_kb;
+    uint32_t idesc;
+    uint32_t* err_word;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait. Returns false when the wait was abandoned: either this wait ran longer than
+// `limit_ns`, or another thread of the CTA already raised `*abort_flag`.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          uint32_t* err_word, uint32_t code,
+                                          unsigned long long limit_ns = 2000000000ull) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 0xff) == 0) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > limit_ns) {
+                *abort_flag = 1;
+                if (err_word) atomicCAS(err_word, 0u, code);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+template <bool kTF32>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    if constexpr (kTF32) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+            : "memory");
+    }
+}
+
+// 32 lanes x 32 consecutive fp32 columns: thread l of the warp receives lane (base + l).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
+// lbo / sbo in bytes.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3fffu);
+    d |= (uint64_t)((lbo >> 4) & 0x3fffu) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3fffu) << 32;
+    d |= 1ull << 46;   // version
+    d |= 2ull << 61;   // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ float tanh_fast(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <typename OutT>
+__device__ __forceinline__ float gelu_epilogue(float x) {
+    if constexpr (sizeof(OutT) == 4) {
+        return gelu_tanh_f32(x);  // fp32 results keep the accurate tanh
+    } else {
+        const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+        const float u = k0 * (x + k1 * x * x * x);
+        return 0.5f * x * (1.0f + tanh_fast(u));
+    }
+}
+
+struct TileCoord {
+    int b, m0, n0;
+};
+__device__ __forceinline__ TileCoord decode_tile(long long tile, const GemmParams& p, int bn) {
+    const long long per_batch = (long long)p.tiles_m * p.tiles_n;
+    TileCoord t;
+    t.b = (int)(tile / per_batch);
+    const int r = (int)(tile - (long long)t.b * per_batch);
+    t.m0 = (r / p.tiles_n) * kBM;
+    t.n0 = (r % p.tiles_n) * bn;
+    return t;
+}
+
+// kCopies: operand copies per stage (1, or 2 = hi and lo halves of the fp32 split)
+template <int kCopies, int BN>
+struct StageLayout {
+    static constexpr int kABytes = kBM * kRowBytes;      // 16 KiB
+    static constexpr int kBBytes = BN * kRowBytes;
+    static constexpr int kStageBytes = kCopies * (kABytes + kBBytes);
+    static constexpr int kStagesFit = kSmemBudget / kStageBytes;
+    static constexpr int kStages = kStagesFit > kMaxStages ? kMaxStages : kStagesFit;
+    static constexpr int kDynSmem = kStages * kStageBytes + 1024;   // + alignment slack
+    static_assert(kStages >= 2, "at least a double buffer");
+};
+
+template <bool kTF32, bool kSplit, int BN, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_lo,
+                  const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b_lo,
+                  const __grid_constant__ GemmParams p) {
+    constexpr int kCopies = kSplit ? 2 : 1;
+    constexpr int kPasses = kSplit ? 3 : 1;   // tcgen05.mma passes per k-step
+    using L = StageLayout<kCopies, BN>;
+    constexpr int kStages = L::kStages;
+    constexpr int kElem = kTF32 ? 4 : 2;
+    constexpr int kBKElems = kRowBytes / kElem;         // K elements per stage
+    constexpr int kKSteps = kRowBytes / kUmmaKBytes;     // tcgen05.mma per stage per pass
+    constexpr int kBBoxCols = kRowBytes / kElem;         // N elements per B box when B is N-contiguous
+    constexpr int kBBoxBytes = kBKElems * kRowBytes;     // bytes of one such box
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_full[kMaxStages];
+    __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
+    __shared__ __align__(8) uint64_t bar_acc_full[2];
+    __shared__ __align__(8) uint64_t bar_acc_empty[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile uint32_t abort_flag;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&bar_acc_full[a]), 1);
+            mbar_init(smem_u32(&bar_acc_empty[a]), 4);
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            long long issued = 0;
+            bool ok = true;
+            for (long long tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+                const TileCoord t = decode_tile(tile, p, BN);
+                const int za = p.a_batched ? t.b : 0, zb = p.b_batched ? t.b : 0;
+                for (int kb = 0; kb < p.num_kb; ++kb) {
+                    if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag, p.err_word, 0x100u + stage)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t full = smem_u32(&bar_full[stage]);
+                    mbar_expect_tx(full, (uint32_t)L::kStageBytes);
+                    const uint32_t sa = smem_base + stage * L::kStageBytes;
+                    const uint32_t sb = sa + kCopies * L::kABytes;
+                    const int k0 = kb * kBKElems;
+#pragma unroll
+                    for (int ps = 0; ps < kCopies; ++ps) {
+                        const CUtensorMap* ma = ps == 0 ? &tm_a : &tm_a_lo;
+                        const CUtensorMap* mb = ps == 0 ? &tm_b : &tm_b_lo;
+                        tma_load_3d(sa + ps * L::kABytes, ma, full, k0, t.m0, za);
+                        if (p.b_mn_major) {
+#pragma unroll
+                            for (int j = 0; j < BN / kBBoxCols; ++j)
+                                tma_load_3d(sb + ps * L::kBBytes + j * kBBoxBytes, mb, full, t.n0 + j * kBBoxCols, k0, zb);
+                        } else {
+                            tma_load_3d(sb + ps * L::kBBytes, mb, full, k0, t.n0, zb);
+                        }
+                    }
+                    ++issued;
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok) {
+                // Let copies already in flight land before the CTA can exit: wait (bounded, ignoring the
+                // abort flag) on the full barrier of every stage that may still have one outstanding.
+                volatile uint32_t never = 0;
+                const long long back = issued < kStages ? issued : kStages;
+                int s = stage;
+                uint32_t ph = phase;
+                for (long long i = 0; i < back; ++i) {
+                    if (--s < 0) {
+                        s = kStages - 1;
+                        ph ^= 1u;
+                    }
+                    mbar_wait(smem_u32(&bar_full[s]), ph, &never, nullptr, 0, 50000000ull);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            const uint32_t a_lbo = 16, a_sbo = 1024;
+            const uint32_t b_lbo = p.b_mn_major ? (uint32_t)kBBoxBytes : 16u, b_sbo = 1024;
+            // bytes to advance the B descriptor per tcgen05.mma: one 32-byte K slice inside the swizzle
+            // span when K is contiguous, kUmmaK rows of 128 bytes when N is contiguous
+            const uint32_t b_kstep = p.b_mn_major ? (uint32_t)(kUmmaKBytes / kElem) * kRowBytes : (uint32_t)kUmmaKBytes;
+            for (long long tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+                if (!mbar_wait(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, &abort_flag, p.err_word, 0x200u + acc)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+                uint32_t first = 0;
+                for (int kb = 0; kb < p.num_kb; ++kb) {
+                    if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag, p.err_word, 0x300u + stage)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + stage * L::kStageBytes;
+                    const uint32_t sb = sa + kCopies * L::kABytes;
+                    // passes: (lo, hi), (hi, lo), (hi, hi) for the split; (hi, hi) alone otherwise
+#pragma unroll
+                    for (int ps = 0; ps < kPasses; ++ps) {
+                        const int ia = (kPasses == 3 && ps == 0) ? 1 : 0;
+                        const int ib = (kPasses == 3 && ps == 1) ? 1 : 0;
+                        const uint64_t da = make_smem_desc(sa + ia * L::kABytes, a_lbo, a_sbo);
+                        const uint64_t db = make_smem_desc(sb + ib * L::kBBytes, b_lbo, b_sbo);
+#pragma unroll
+                        for (int k = 0; k < kKSteps; ++k) {
+                            umma<kTF32>(tmem_d, da + (uint64_t)((k * kUmmaKBytes) >> 4), db + (uint64_t)((k * b_kstep) >> 4),
+                                        p.idesc, first);
+                            first = 1;
+                        }
+                    }
+                    tc_commit(smem_u32(&bar_empty[stage]));
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                tc_commit(smem_u32(&bar_acc_full[acc]));
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5; TMEM lane quarter = warp id mod 4) ----------------
+        const int q = warp & 3;
+        const int row_in_tile = q * 32 + lane;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        OutT* Cbase = static_cast<OutT*>(p.C);
+        const OutT* Rbase = static_cast<const OutT*>(p.residual);
+        const OutT* bias = static_cast<const OutT*>(p.bias);
+        const int epi = p.epilogue;
+        const bool has_bias = epi == CG_B200_EPI_BIAS || epi == CG_B200_EPI_BIAS_RELU ||
+                              epi == CG_B200_EPI_BIAS_GELU_TANH || epi == CG_B200_EPI_BIAS_RESIDUAL;
+        const bool has_res = epi == CG_B200_EPI_BIAS_RESIDUAL || epi == CG_B200_EPI_RESIDUAL;
+        const bool bias_vec = has_bias && ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
+        constexpr int kPack = 16 / sizeof(OutT);  // elements per 16-byte store
+        for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+            bool ok = mbar_wait(smem_u32(&bar_acc_full[acc]), acc_phase, &abort_flag, p.err_word, 0x400u + acc);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const TileCoord t = decode_tile(tile, p, BN);
+            const long long m = (long long)t.m0 + row_in_tile;
+            const bool row_ok = m < p.M;
+            const long long row_off = (long long)t.b * p.batch_stride_c + m * p.ldc;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                float v[32];
+                __syncwarp();  // lanes that skipped stores rejoin before the warp-wide TMEM load
+                if (p.num_kb > 0) {
+                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = 0.0f;
+                }
+                const long long n0 = (long long)t.n0 + c0;
+                if (n0 >= p.N) continue;
+                const bool full = n0 + 32 <= p.N;
+                if (epi == CG_B200_EPI_SCALE) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+                }
+                if (has_bias) {
+                    if (full && bias_vec) {
+#pragma unroll
+                        for (int g = 0; g < 32 / kPack; ++g) {
+                            Vec16<OutT> bv = ld_keep(bias + n0 + g * kPack);
+#pragma unroll
+                            for (int j = 0; j < kPack; ++j) v[g * kPack + j] += Elem<OutT>::to_f32(bv.v[j]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (n0 + j < p.N) v[j] += Elem<OutT>::to_f32(bias[n0 + j]);
+                    }
+                }
+                if (epi == CG_B200_EPI_BIAS_RELU) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
+                } else if (epi == CG_B200_EPI_BIAS_GELU_TANH) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = gelu_epilogue<OutT>(v[j]);
+                }
+                if (!row_ok) continue;
+                OutT* crow = Cbase + row_off + n0;
+                if (full) {
+                    if (has_res) {
+                        const OutT* rrow = Rbase + row_off + n0;
+#pragma unroll
+                        for (int g = 0; g < 32 / kPack; ++g) {
+                            Vec16<OutT> rv = ld_stream(rrow + g * kPack);
+#pragma unroll
+                            for (int j = 0; j < kPack; ++j) v[g * kPack + j] += Elem<OutT>::to_f32(rv.v[j]);
+                        }
+                    }
+#pragma unroll
+                    for (int g = 0; g < 32 / kPack; ++g) {
+                        Vec16<OutT> o;
+#pragma unroll
+                        for (int j = 0; j < kPack; ++j) o.v[j] = Elem<OutT>::from_f32(v[g * kPack + j]);
+                        *reinterpret_cast<int4*>(crow + g * kPack) = *reinterpret_cast<const int4*>(&o);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (n0 + j < p.N) {
+                            float r = v[j];
+                            if (has_res) r += Elem<OutT>::to_f32(Rbase[row_off + n0 + j]);
+                            crow[j] = Elem<OutT>::from_f32(r);
+                        }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// Splits fp32 x into hi = x with the low 13 mantissa bits cleared (exactly a tf32 value) and
+// lo = (x - hi) cleared the same way. rows x cols with source row stride ld_src, destination ld_dst.
+__global__ void __launch_bounds__(256)
+tf32_split_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo, long long rows,
+                  long long cols, long long ld_src, long long ld_dst, long long batch, long long bs_src,
+                  long long bs_dst) {
+    const long long per = rows * ld_dst;
+    const long long total = per * batch;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const long long b = i / per;
+        const long long r = (i - b * per) / ld_dst;
+        const long long c = i - b * per - r * ld_dst;
+        float x = 0.0f;
+        if (c < cols) x = src[b * bs_src + r * ld_src + c];
+        const float h = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
+        const float l = __uint_as_float(__float_as_uint(x - h) & 0xffffe000u);
+        hi[b * bs_dst + r * ld_dst + c] = h;
+        lo[b * bs_dst + r * ld_dst + c] = l;
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)f;
+    });
+    return fn;
+}
+
+// 3-D map {inner, rows, batch}; box {box_inner, box_rows, 1}; 128-byte swizzle; OOB reads give zero.
+static int make_map(CUtensorMap* map, const void* base, int dtype, uint64_t inner, uint64_t rows, uint64_t batch,
+                    uint64_t ld_elems, uint64_t batch_stride_elems, uint32_t box_inner, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return CG_B200_ERR_CUDA;
+    const uint64_t esz = dtype_bytes(dtype);
+    CUtensorMapDataType dt = dtype == CG_B200_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                  : (dtype == CG_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                           : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+    cuuint64_t dims[3] = {inner, rows, batch};
+    cuuint64_t strides[2] = {ld_elems * esz, batch_stride_elems * esz};
+    cuuint32_t box[3] = {box_inner, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        note_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+        return CG_B200_ERR_CUDA;
+    }
+    return CG_B200_OK;
+}
+
+static uint32_t make_idesc(int in_dtype, bool tf32, bool b_mn_major, int bn) {
+    uint32_t d = 0;
+    d |= 1u << 4;                                                   // accumulator format: F32
+    const uint32_t fmt = tf32 ? 2u : (in_dtype == CG_B200_BF16 ? 1u : 0u);
+    d |= fmt << 7;                                                  // A format
+    d |= fmt << 10;                                                 // B format
+    d |= 0u << 15;                                                  // A: K-major
+    d |= (b_mn_major ? 1u : 0u) << 16;                              // B: MN-major when N is contiguous
+    d |= (uint32_t)(bn >> 3) << 17;                                 // N / 8
+    d |= (uint32_t)(kBM >> 4) << 24;                                // M / 16
+    return d;
+}
+
+struct SplitPlan {
+    bool split;            // 3xTF32 with workspace
+    long long lda_w, ldb_w;   // workspace row strides (elements)
+    long long a_elems, b_elems;  // per hi (or lo) array
+    size_t bytes;
+};
+
+static inline long long round_up(long long x, long long a) { return (x + a - 1) / a * a; }
+
+static SplitPlan plan_split(const cg_b200_gemm_desc* d) {
+    SplitPlan s{};
+    s.split = d->in_dtype == CG_B200_F32 && d->compute != CG_B200_COMPUTE_TF32;
+    if (!s.split) return s;
+    s.lda_w = round_up(d->K, 4);
+    s.ldb_w = round_up(d->b_transposed ? d->K : d->N, 4);
+    const long long a_batches = d->batch_stride_a == 0 ? 1 : d->batch;
+    const long long b_batches = d->batch_stride_b == 0 ? 1 : d->batch;
+    s.a_elems = round_up(a_batches * d->M * s.lda_w, 64);
+    s.b_elems = round_up(b_batches * (d->b_transposed ? d->N : d->K) * s.ldb_w, 64);
+    s.bytes = (size_t)(2 * (s.a_elems + s.b_elems)) * sizeof(float);
+    return s;
+}
+
+static int validate_desc(const cg_b200_gemm_desc* d) {
+    if (!d) return CG_B200_ERR_NULL_POINTER;
+    if (!dtype_ok(d->in_dtype) || !dtype_ok(d->out_dtype)) return CG_B200_ERR_INVALID_ARG;
+    if (d->M < 0 || d->N < 0 || d->K < 0 || d->batch < 1) return CG_B200_ERR_INVALID_ARG;
+    if (d->epilogue < CG_B200_EPI_NONE || d->epilogue > CG_B200_EPI_SCALE) return CG_B200_ERR_INVALID_ARG;
+    if (d->compute < CG_B200_COMPUTE_DEFAULT || d->compute > CG_B200_COMPUTE_TF32) return CG_B200_ERR_INVALID_ARG;
+    if (d->in_dtype != CG_B200_F32 && d->compute != CG_B200_COMPUTE_DEFAULT) return CG_B200_ERR_INVALID_ARG;
+    if (d->in_dtype == CG_B200_F32 && d->out_dtype != CG_B200_F32) return CG_B200_ERR_UNSUPPORTED;
+    if (d->lda < d->K || d->ldc < d->N) return CG_B200_ERR_INVALID_ARG;
+    if (d->ldb < (d->b_transposed ? d->K : d->N)) return CG_B200_ERR_INVALID_ARG;
+    if (d->batch_stride_a < 0 || d->batch_stride_b < 0 || d->batch_stride_c < 0) return CG_B200_ERR_INVALID_ARG;
+    if (d->batch > 1 && d->batch_stride_c < d->M * d->ldc) return CG_B200_ERR_INVALID_ARG;
+    if (d->M > 0x7fffffffLL || d->N > 0x7fffffffLL || d->K > 0x7fffffffLL || d->batch > 0x7fffffffLL)
+        return CG_B200_ERR_UNSUPPORTED;
+    return CG_B200_OK;
+}
+
+template <bool kTF32, bool kSplit, int BN, typename OutT>
+static int launch_variant(const CUtensorMap& ta, const CUtensorMap& ta_lo, const CUtensorMap& tb,
+                          const CUtensorMap& tb_lo, GemmParams& p, cudaStream_t s) {
+    using L = StageLayout<kSplit ? 2 : 1, BN>;
+    auto kern = gemm_sm100_kernel<kTF32, kSplit, BN, OutT>;
+    // the attribute is per device; setting it again is cheap
+    CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynSmem));
+    const int elem = kTF32 ? 4 : 2;
+    p.tiles_m = (int)((p.M + kBM - 1) / kBM);
+    p.tiles_n = (int)((p.N + BN - 1) / BN);
+    p.num_tiles = (long long)p.tiles_m * p.tiles_n * p.batch;
+    p.num_kb = (int)((p.K + (kRowBytes / elem) - 1) / (kRowBytes / elem));
+    const long long sms = sm_count();
+    const int grid = (int)(p.num_tiles < sms ? p.num_tiles : sms);
+    kern<<<grid, kThreads, L::kDynSmem, s>>>(ta, ta_lo, tb, tb_lo, p);
+    CGB_CUDA(cudaGetLastError());
+    return CG_B200_OK;
+}
+
+template <bool kTF32, bool kSplit, typename OutT>
+static int launch_bn(int bn, const CUtensorMap& ta, const CUtensorMap& ta_lo, const CUtensorMap& tb,
+                     const CUtensorMap& tb_lo, GemmParams& p, cudaStream_t s) {
+    if constexpr (kSplit) {
+        (void)bn;
+        return launch_variant<kTF32, true, 128, OutT>(ta, ta_lo, tb, tb_lo, p, s);
+    } else {
+        if (bn == 64) return launch_variant<kTF32, false, 64, OutT>(ta, ta_lo, tb, tb_lo, p, s);
+        if (bn == 128) return launch_variant<kTF32, false, 128, OutT>(ta, ta_lo, tb, tb_lo, p, s);
+        return launch_variant<kTF32, false, 256, OutT>(ta, ta_lo, tb, tb_lo, p, s);
+    }
+}
+
+static int choose_bn(const cg_b200_gemm_desc* d, bool split) {
+    if (split) return 128;
+    if (d->N <= 64) return 64;
+    if (d->N <= 128) return 128;
+    return 256;
+}
+
+}  // namespace cgb
+
+using namespace cgb;
+
+extern "C" int cg_b200_gemm_workspace_bytes(const cg_b200_gemm_desc* desc, size_t* bytes) {
+    if (!bytes) return CG_B200_ERR_NULL_POINTER;
+    *bytes = 0;
+    int st = validate_desc(desc);
+    if (st) return st;
+    *bytes = plan_split(desc).bytes;
+    return CG_B200_OK;
+}
+
+extern "C" int cg_b200_gemm(const cg_b200_gemm_desc* desc, const void* A, const void* B, const void* bias,
+                            const void* residual, void* C, void* workspace, size_t workspace_bytes, void* stream) {
+    int st = validate_desc(desc);
+    if (st) return st;
+    const cg_b200_gemm_desc& d = *desc;
+    if (d.M == 0 || d.N == 0) return CG_B200_OK;
+    if (!A || !B || !C) return CG_B200_ERR_NULL_POINTER;
+    const int epi = d.epilogue;
+    const bool need_bias = epi == CG_B200_EPI_BIAS || epi == CG_B200_EPI_BIAS_RELU ||
+                           epi == CG_B200_EPI_BIAS_GELU_TANH || epi == CG_B200_EPI_BIAS_RESIDUAL;
+    const bool need_res = epi == CG_B200_EPI_BIAS_RESIDUAL || epi == CG_B200_EPI_RESIDUAL;
+    if (need_bias && !bias) return CG_B200_ERR_NULL_POINTER;
+    if (need_res && !residual) return CG_B200_ERR_NULL_POINTER;
+    const size_t in_sz = dtype_bytes(d.in_dtype), out_sz = dtype_bytes(d.out_dtype);
+    const SplitPlan sp = plan_split(desc);
+    // C rows are written with 16-byte stores
+    if (!aligned_to(C, 16) || (d.ldc * out_sz) % 16 || (d.batch_stride_c * out_sz) % 16) return CG_B200_ERR_MISALIGNED;
+    if (need_res && !aligned_to(residual, 16)) return CG_B200_ERR_MISALIGNED;
+    if (need_bias && !aligned_to(bias, out_sz)) return CG_B200_ERR_MISALIGNED;
+    if (!sp.split) {
+        // TMA reads A and B in place: 16-byte aligned bases and strides
+        if (!aligned_to(A, 16) || !aligned_to(B, 16)) return CG_B200_ERR_MISALIGNED;
+        if ((d.lda * in_sz) % 16 || (d.ldb * in_sz) % 16) return CG_B200_ERR_MISALIGNED;
+        if ((d.batch_stride_a * in_sz) % 16 || (d.batch_stride_b * in_sz) % 16) return CG_B200_ERR_MISALIGNED;
+    } else {
+        if (!aligned_to(A, 4) || !aligned_to(B, 4)) return CG_B200_ERR_MISALIGNED;
+        if (!workspace || workspace_bytes < sp.bytes) return CG_B200_ERR_WORKSPACE;
+        if (!aligned_to(workspace, 256)) return CG_B200_ERR_MISALIGNED;
+    }
+    st = require_sm100();
+    if (st) return st;
+    cudaStream_t s = (cudaStream_t)stream;
+
+    GemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.M = d.M; p.N = d.N; p.K = d.K; p.batch = d.batch;
+    p.ldc = d.ldc; p.batch_stride_c = d.batch_stride_c;
+    p.bias = bias; p.residual = residual; p.C = C;
+    p.epilogue = epi; p.alpha = d.alpha;
+    p.b_mn_major = d.b_transposed ? 0 : 1;
+    p.a_batched = d.batch_stride_a != 0 && d.batch > 1;
+    p.b_batched = d.batch_stride_b != 0 && d.batch > 1;
+    p.err_word = device_error_word();
+
+    const bool tf32 = d.in_dtype == CG_B200_F32;
+    const int bn = choose_bn(desc, sp.split);
+    p.idesc = make_idesc(d.in_dtype, tf32, p.b_mn_major != 0, bn);
+    const uint32_t box_k = (uint32_t)(kRowBytes / in_sz);
+
+    const void* a_hi = A;
+    const void* a_lo = A;
+    const void* b_hi = B;
+    const void* b_lo = B;
+    long long lda = d.lda, ldb = d.ldb, bsa = d.batch_stride_a, bsb = d.batch_stride_b;
+    const long long b_rows = d.b_transposed ? d.N : d.K, b_cols = d.b_transposed ? d.K : d.N;
+    if (sp.split) {
+        float* w = static_cast<float*>(workspace);
+        float* wa_hi = w;
+        float* wa_lo = w + sp.a_elems;
+        float* wb_hi = w + 2 * sp.a_elems;
+        float* wb_lo = wb_hi + sp.b_elems;
+        const long long a_batches = p.a_batched ? d.batch : 1, b_batches = p.b_batched ? d.batch : 1;
+        const int blocks = sm_count() * 8;
+        tf32_split_kernel<<<blocks, 256, 0, s>>>(static_cast<const float*>(A), wa_hi, wa_lo, d.M, d.K, d.lda, sp.lda_w,
+                                                 a_batches, d.batch_stride_a, d.M * sp.lda_w);
+        tf32_split_kernel<<<blocks, 256, 0, s>>>(static_cast<const float*>(B), wb_hi, wb_lo, b_rows, b_cols, d.ldb,
+                                                 sp.ldb_w, b_batches, d.batch_stride_b, b_rows * sp.ldb_w);
+        CGB_CUDA(cudaGetLastError());
+        a_hi = wa_hi; a_lo = wa_lo; b_hi = wb_hi; b_lo = wb_lo;
+        lda = sp.lda_w; ldb = sp.ldb_w;
+        bsa = d.M * sp.lda_w; bsb = b_rows * sp.ldb_w;
+    }
+    const uint64_t a_nb = p.a_batched ? (uint64_t)d.batch : 1, b_nb = p.b_batched ? (uint64_t)d.batch : 1;
+    // a batch stride of 0 cannot be encoded; with one batch slice the value is never used
+    const uint64_t bsa_enc = bsa > 0 ? (uint64_t)bsa : (uint64_t)d.M * lda;
+    const uint64_t bsb_enc = bsb > 0 ? (uint64_t)bsb : (uint64_t)b_rows * ldb;
+    // K == 0: no k-blocks, the maps are never dereferenced but must still encode
+    const uint64_t k_dim = d.K > 0 ? (uint64_t)d.K : 1;
+
+    alignas(64) CUtensorMap ta, ta_lo, tb, tb_lo;
+    st = make_map(&ta, a_hi, d.in_dtype, k_dim, d.M, a_nb, lda, bsa_enc, box_k, kBM);
+    if (st) return st;
+    st = make_map(&ta_lo, a_lo, d.in_dtype, k_dim, d.M, a_nb, lda, bsa_enc, box_k, kBM);
+    if (st) return st;
+    if (p.b_mn_major) {
+        st = make_map(&tb, b_hi, d.in_dtype, d.N, k_dim, b_nb, ldb, bsb_enc, box_k, box_k);
+        if (st) return st;
+        st = make_map(&tb_lo, b_lo, d.in_dtype, d.N, k_dim, b_nb, ldb, bsb_enc, box_k, box_k);
+    } else {
+        st = make_map(&tb, b_hi, d.in_dtype, k_dim, d.N, b_nb, ldb, bsb_enc, box_k, (uint32_t)bn);
+        if (st) return st;
+        st = make_map(&tb_lo, b_lo, d.in_dtype, k_dim, d.N, b_nb, ldb, bsb_enc, box_k, (uint32_t)bn);
+    }
+    if (st) return st;
+
+    if (tf32) {
+        if (sp.split) return launch_bn<true, true, float>(bn, ta, ta_lo, tb, tb_lo, p, s);
+        return launch_bn<true, false, float>(bn, ta, ta_lo, tb, tb_lo, p, s);
+    }
+    switch (d.out_dtype) {
+        case CG_B200_BF16: return launch_bn<false, false, __nv_bfloat16>(bn, ta, ta_lo, tb, tb_lo, p, s);
+        case CG_B200_F16: return launch_bn<false, false, __half>(bn, ta, ta_lo, tb, tb_lo, p, s);
+        default: return launch_bn<false, false, float>(bn, ta, ta_lo, tb, tb_lo, p, s);
+    }
+}

@@ -1,0 +1,295 @@
+// rowreduce.cu - last-axis softmax, layernorm and layernorm(softmax) in one HBM pass.
+//
+// The reference defines softmax and layernorm as attribute-less Tensor-IR ops over the last
+// axis (src/ir/ops.cpp:536-556) but never executes them: lowering falls through to an
+// "unknown opcode" Const (src/lowering/tensor_to_codegen.cpp:350-356) and the PTX emitter
+// prints a comment for CGOpcode::Reduce (src/backend/ptx/ptx_emitter.cpp:136-142); its
+// shuffle emission (ptx_emitter.cpp:165-189) is the only hint at a warp reduction.
+// Definitions used: max-subtracted softmax (include/cg/egraph/rewrite_rules.hpp:96-101);
+// layernorm = mean, biased variance, normalise, scale + shift
+// (src/analysis/arithmetic_intensity.cpp:138-146).
+//
+// HBM-bound: algorithmic bytes per row = 2 * cols * sizeof(T) (read once, write once).
+// Layout: [rows, cols] row-major. Register path: one CTA per row, the row lives in
+// registers as fp32 (CHUNKS 16-byte packets per thread, packet j of thread t is packet
+// j*THREADS + t of the row, so a warp reads 512 contiguous bytes); reductions are
+// shfl.bfly inside a warp plus one shared-memory hop across warps. Rows that are too long
+// or not 16-byte tiled take the streaming path, which re-reads the row (from L2) per pass.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace cgb {
+
+enum RowMode { kSoftmax = 0, kLayerNorm = 1, kSoftmaxLayerNorm = 2 };
+
+struct RowParams {
+    const void* in;
+    void* out;
+    const void* gamma;
+    const void* beta;
+    long long rows;
+    long long cols;
+    float eps;
+};
+
+struct MaxOp {
+    __device__ static float identity() { return -INFINITY; }
+    __device__ static float apply(float a, float b) { return fmaxf(a, b); }
+};
+struct SumOp {
+    __device__ static float identity() { return 0.0f; }
+    __device__ static float apply(float a, float b) { return a + b; }
+};
+
+// All threads of the CTA get the reduction of v. `scratch` holds one float per warp; `phase`
+// alternates between two scratch halves so back-to-back reductions need one barrier each.
+template <typename Op, int THREADS>
+__device__ __forceinline__ float block_reduce(float v, float* scratch, int& phase) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = Op::apply(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if constexpr (THREADS == 32) {
+        return v;
+    } else {
+        constexpr int W = THREADS / 32;
+        float* s = scratch + (phase & 1) * 32;
+        phase ^= 1;
+        if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = v;
+        __syncthreads();
+        float r = (threadIdx.x & 31) < W ? s[threadIdx.x & 31] : Op::identity();
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) r = Op::apply(r, __shfl_xor_sync(0xffffffffu, r, o));
+        return r;
+    }
+}
+
+template <typename T, int THREADS, int CHUNKS, int MODE>
+__global__ void __launch_bounds__(THREADS) row_reg_kernel(const __grid_constant__ RowParams p) {
+    constexpr int L = 16 / sizeof(T);
+    __shared__ float scratch[64];
+    int phase = 0;
+    const long long n_pkt = p.cols / L;  // cols % L == 0 on this path
+    const float inv_cols = 1.0f / (float)p.cols;
+
+    for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
+        const T* in = static_cast<const T*>(p.in) + row * p.cols;
+        T* out = static_cast<T*>(p.out) + row * p.cols;
+        float x[CHUNKS][L];
+        bool live[CHUNKS];
+#pragma unroll
+        for (int j = 0; j < CHUNKS; ++j) {
+            const long long pk = (long long)j * THREADS + threadIdx.x;
+            live[j] = pk < n_pkt;
+            if (live[j]) {
+                Vec16<T> v = ld_stream(in + pk * L);
+#pragma unroll
+                for (int l = 0; l < L; ++l) x[j][l] = Elem<T>::to_f32(v.v[l]);
+            }
+        }
+
+        if constexpr (MODE == kSoftmax || MODE == kSoftmaxLayerNorm) {
+            float m = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < CHUNKS; ++j)
+                if (live[j]) {
+#pragma unroll
+                    for (int l = 0; l < L; ++l) m = fmaxf(m, x[j][l]);
+                }
+            m = block_reduce<MaxOp, THREADS>(m, scratch, phase);
+            float s = 0.0f;
+#pragma unroll
+            for (int j = 0; j < CHUNKS; ++j)
+                if (live[j]) {
+#pragma unroll
+                    for (int l = 0; l < L; ++l) {
+                        x[j][l] = expf(x[j][l] - m);
+                        s += x[j][l];
+                    }
+                }
+            s = block_reduce<SumOp, THREADS>(s, scratch, phase);
+            const float inv = 1.0f / s;
+#pragma unroll
+            for (int j = 0; j < CHUNKS; ++j)
+                if (live[j]) {
+#pragma unroll
+                    for (int l = 0; l < L; ++l) {
+                        x[j][l] = x[j][l] * inv;
+                        // the tensor between the two ops has storage type T
+                        if constexpr (MODE == kSoftmaxLayerNorm) x[j][l] = Elem<T>::to_f32(Elem<T>::from_f32(x[j][l]));
+                    }
+                }
+        }
+
+        if constexpr (MODE == kLayerNorm || MODE == kSoftmaxLayerNorm) {
+            float s = 0.0f;
+#pragma unroll
+            for (int j = 0; j < CHUNKS; ++j)
+                if (live[j]) {
+#pragma unroll
+                    for (int l = 0; l < L; ++l) s += x[j][l];
+                }
+            const float mean = block_reduce<SumOp, THREADS>(s, scratch, phase) * inv_cols;
+            float q = 0.0f;
+#pragma unroll
+            for (int j = 0; j < CHUNKS; ++j)
+                if (live[j]) {
+#pragma unroll
+                    for (int l = 0; l < L; ++l) {
+                        const float d = x[j][l] - mean;
+                        q += d * d;
+                    }
+                }
+            const float var = block_reduce<SumOp, THREADS>(q, scratch, phase) * inv_cols;
+            const float rstd = rsqrtf(var + p.eps);
+            const T* gamma = static_cast<const T*>(p.gamma);
+            const T* beta = static_cast<const T*>(p.beta);
+#pragma unroll
+            for (int j = 0; j < CHUNKS; ++j)
+                if (live[j]) {
+                    const long long pk = (long long)j * THREADS + threadIdx.x;
+                    Vec16<T> g, b;
+                    if (gamma) g = ld_keep(gamma + pk * L);
+                    if (beta) b = ld_keep(beta + pk * L);
+#pragma unroll
+                    for (int l = 0; l < L; ++l) {
+                        float t = (x[j][l] - mean) * rstd;
+                        if (gamma) t = t * Elem<T>::to_f32(g.v[l]);
+                        if (beta) t = t + Elem<T>::to_f32(b.v[l]);
+                        x[j][l] = t;
+                    }
+                }
+        }
+
+#pragma unroll
+        for (int j = 0; j < CHUNKS; ++j)
+            if (live[j]) {
+                const long long pk = (long long)j * THREADS + threadIdx.x;
+                Vec16<T> o;
+#pragma unroll
+                for (int l = 0; l < L; ++l) o.v[l] = Elem<T>::from_f32(x[j][l]);
+                st_stream(out + pk * L, o);
+            }
+    }
+}
+
+// Streaming path: any cols, element-aligned. One CTA per row, several passes over the row.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256) row_stream_kernel(const __grid_constant__ RowParams p) {
+    constexpr int THREADS = 256;
+    __shared__ float scratch[64];
+    int phase = 0;
+    const float inv_cols = 1.0f / (float)p.cols;
+    const T* gamma = static_cast<const T*>(p.gamma);
+    const T* beta = static_cast<const T*>(p.beta);
+    for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
+        const T* in = static_cast<const T*>(p.in) + row * p.cols;
+        T* out = static_cast<T*>(p.out) + row * p.cols;
+        float m = 0.0f, inv = 1.0f;
+        if constexpr (MODE != kLayerNorm) {
+            m = -INFINITY;
+            for (long long c = threadIdx.x; c < p.cols; c += THREADS) m = fmaxf(m, Elem<T>::to_f32(in[c]));
+            m = block_reduce<MaxOp, THREADS>(m, scratch, phase);
+            float s = 0.0f;
+            for (long long c = threadIdx.x; c < p.cols; c += THREADS) s += expf(Elem<T>::to_f32(in[c]) - m);
+            s = block_reduce<SumOp, THREADS>(s, scratch, phase);
+            inv = 1.0f / s;
+        }
+        // value of the tensor that enters the layernorm stage (or the softmax result)
+        auto staged = [&](long long c) -> float {
+            float v = Elem<T>::to_f32(in[c]);
+            if constexpr (MODE != kLayerNorm) v = expf(v - m) * inv;
+            if constexpr (MODE == kSoftmaxLayerNorm) v = Elem<T>::to_f32(Elem<T>::from_f32(v));
+            return v;
+        };
+        if constexpr (MODE == kSoftmax) {
+            // `in == out` is allowed: every element is read and written by the same thread
+            for (long long c = threadIdx.x; c < p.cols; c += THREADS) out[c] = Elem<T>::from_f32(staged(c));
+        } else {
+            float s = 0.0f;
+            for (long long c = threadIdx.x; c < p.cols; c += THREADS) s += staged(c);
+            const float mean = block_reduce<SumOp, THREADS>(s, scratch, phase) * inv_cols;
+            float q = 0.0f;
+            for (long long c = threadIdx.x; c < p.cols; c += THREADS) {
+                const float d = staged(c) - mean;
+                q += d * d;
+            }
+            const float var = block_reduce<SumOp, THREADS>(q, scratch, phase) * inv_cols;
+            const float rstd = rsqrtf(var + p.eps);
+            __syncthreads();  // all reads of `in` for the statistics are done before any in-place write
+            for (long long c = threadIdx.x; c < p.cols; c += THREADS) {
+                float t = (staged(c) - mean) * rstd;
+                if (gamma) t = t * Elem<T>::to_f32(gamma[c]);
+                if (beta) t = t + Elem<T>::to_f32(beta[c]);
+                out[c] = Elem<T>::from_f32(t);
+            }
+        }
+    }
+}
+
+template <typename T, int THREADS, int CHUNKS, int MODE>
+static void launch_reg(const RowParams& p, int blocks, cudaStream_t s) {
+    row_reg_kernel<T, THREADS, CHUNKS, MODE><<<blocks, THREADS, 0, s>>>(p);
+}
+
+template <typename T, int MODE>
+static int launch_mode(const RowParams& p, cudaStream_t s) {
+    constexpr int L = 16 / sizeof(T);
+    const long long n_pkt = p.cols / L;
+    bool vec = (p.cols % L) == 0 && aligned_to(p.in, 16) && aligned_to(p.out, 16) &&
+               (!p.gamma || aligned_to(p.gamma, 16)) && (!p.beta || aligned_to(p.beta, 16));
+    const long long max_blocks = (long long)sm_count() * 32;
+    const int blocks = (int)(p.rows < max_blocks ? p.rows : max_blocks);
+    if (vec && n_pkt <= 32) launch_reg<T, 32, 1, MODE>(p, blocks, s);
+    else if (vec && n_pkt <= 64) launch_reg<T, 64, 1, MODE>(p, blocks, s);
+    else if (vec && n_pkt <= 128) launch_reg<T, 128, 1, MODE>(p, blocks, s);
+    else if (vec && n_pkt <= 256) launch_reg<T, 128, 2, MODE>(p, blocks, s);
+    else if (vec && n_pkt <= 512) launch_reg<T, 128, 4, MODE>(p, blocks, s);
+    else if (vec && n_pkt <= 1024) launch_reg<T, 256, 4, MODE>(p, blocks, s);
+    else if (vec && n_pkt <= 2048) launch_reg<T, 512, 4, MODE>(p, blocks, s);
+    else row_stream_kernel<T, MODE><<<blocks, 256, 0, s>>>(p);
+    CGB_CUDA(cudaGetLastError());
+    return CG_B200_OK;
+}
+
+static int row_entry(int mode, int dtype, const void* in, const void* gamma, const void* beta, float eps, void* out,
+                     int64_t rows, int64_t cols, void* stream) {
+    if (!dtype_ok(dtype) || rows < 0 || cols < 0) return CG_B200_ERR_INVALID_ARG;
+    if (mode != kSoftmax && !(eps >= 0.0f)) return CG_B200_ERR_INVALID_ARG;
+    if (rows == 0 || cols == 0) return CG_B200_OK;
+    if (!in || !out) return CG_B200_ERR_NULL_POINTER;
+    const size_t esz = dtype_bytes(dtype);
+    if (!aligned_to(in, esz) || !aligned_to(out, esz) || !aligned_to(gamma, esz) || !aligned_to(beta, esz))
+        return CG_B200_ERR_MISALIGNED;
+    int st = require_sm100();
+    if (st) return st;
+    RowParams p{in, out, gamma, beta, rows, cols, eps};
+    cudaStream_t s = (cudaStream_t)stream;
+#define CGB_ROW_DISPATCH(T)                                                     \
+    switch (mode) {                                                             \
+        case kSoftmax: return launch_mode<T, kSoftmax>(p, s);                   \
+        case kLayerNorm: return launch_mode<T, kLayerNorm>(p, s);               \
+        default: return launch_mode<T, kSoftmaxLayerNorm>(p, s);                \
+    }
+    switch (dtype) {
+        case CG_B200_F32: CGB_ROW_DISPATCH(float)
+        case CG_B200_BF16: CGB_ROW_DISPATCH(__nv_bfloat16)
+        default: CGB_ROW_DISPATCH(__half)
+    }
+#undef CGB_ROW_DISPATCH
+}
+
+}  // namespace cgb
+
+extern "C" int cg_b200_softmax(int dtype, const void* in, void* out, int64_t rows, int64_t cols, void* stream) {
+    return cgb::row_entry(cgb::kSoftmax, dtype, in, nullptr, nullptr, 0.0f, out, rows, cols, stream);
+}
+
+extern "C" int cg_b200_layernorm(int dtype, const void* in, const void* gamma, const void* beta, float eps, void* out,
+                                 int64_t rows, int64_t cols, void* stream) {
+    return cgb::row_entry(cgb::kLayerNorm, dtype, in, gamma, beta, eps, out, rows, cols, stream);
+}
+
+extern "C" int cg_b200_softmax_layernorm(int dtype, const void* in, const void* gamma, const void* beta, float eps,
+                                         void* out, int64_t rows, int64_t cols, void* stream) {
+    return cgb::row_entry(cgb::kSoftmaxLayerNorm, dtype, in, gamma, beta, eps, out, rows, cols, stream);
+}

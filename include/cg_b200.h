@@ -1,0 +1,262 @@
+/*
+ * cg_b200.h - C ABI of the B200 (sm_100a) execution path for cantors-gift Executables.
+ *
+ * Every entry point returns an int status (0 = CG_B200_OK); no exception crosses this
+ * boundary. Unless a parameter is named host_*, every data pointer is a device pointer
+ * on the CUDA device that is current on the calling thread. `stream` is a cudaStream_t
+ * passed as void* (NULL = the default stream). Launches are asynchronous on `stream`;
+ * cg_b200_stream_sync is the only blocking call besides the host copies.
+ *
+ * There is no CPU fallback: without a usable CUDA device the compute entry points
+ * return CG_B200_ERR_NO_DEVICE.
+ *
+ * Each declaration cites the interface of the reference project (cantors-gift, paths
+ * relative to its root) that it stands behind.
+ */
+#ifndef CG_B200_H
+#define CG_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+#define CG_B200_VERSION_MAJOR 0
+#define CG_B200_VERSION_MINOR 1
+
+/* ---- status codes --------------------------------------------------------------- */
+enum cg_b200_status {
+    CG_B200_OK = 0,
+    CG_B200_ERR_INVALID_ARG = 1,    /* bad size, count, enum value or program            */
+    CG_B200_ERR_NULL_POINTER = 2,   /* a required pointer is NULL                        */
+    CG_B200_ERR_MISALIGNED = 3,     /* a pointer or stride breaks the stated alignment   */
+    CG_B200_ERR_UNSUPPORTED = 4,    /* valid request that no kernel here implements      */
+    CG_B200_ERR_CUDA = 5,           /* a CUDA runtime/driver call failed                 */
+    CG_B200_ERR_NO_DEVICE = 6,      /* no CUDA device (there is no CPU fallback)         */
+    CG_B200_ERR_WORKSPACE = 7,      /* workspace missing or too small                    */
+    CG_B200_ERR_DEVICE_TIMEOUT = 8, /* a bounded device-side wait ran out                */
+    CG_B200_ERR_COMM = 9,           /* NCCL failure                                      */
+    CG_B200_ERR_FUSED_IR = 10,      /* IR carries the reference's lossy fusion markers   */
+    CG_B200_ERR_NOT_SM100 = 11      /* device is not compute capability 10.x             */
+};
+
+/* Element types. Numbering equals the reference's cg::DType (include/cg/core/dtype.hpp:14-40). */
+enum cg_b200_dtype {
+    CG_B200_F16 = 0,
+    CG_B200_BF16 = 1,
+    CG_B200_F32 = 2
+};
+
+/* ---- library / device ----------------------------------------------------------- */
+
+/* Packed version: (major << 16) | minor. */
+int cg_b200_version(void);
+/* Static, never-NULL description of a status code. */
+const char* cg_b200_status_string(int status);
+/* Text of the last CUDA error this thread saw inside the library ("" if none). */
+const char* cg_b200_last_cuda_error(void);
+/* Number of CUDA devices; *count = 0 and CG_B200_ERR_NO_DEVICE when there is none. */
+int cg_b200_device_count(int* count);
+
+/* Static capabilities of one device. Stands behind TargetInfo / HardwareModel
+ * (include/cg/backend/backend.hpp:48-65, src/cost/hardware_model.cpp:71-106), whose
+ * generic NVIDIA model holds A100-class constants. */
+typedef struct cg_b200_props {
+    char     name[64];
+    int32_t  cc_major, cc_minor;
+    int32_t  sm_count;
+    int32_t  max_smem_per_block;   /* opt-in bytes */
+    int32_t  l2_bytes;
+    int32_t  sm_clock_khz;
+    int32_t  mem_clock_khz;
+    int32_t  mem_bus_bits;
+    uint64_t hbm_bytes;
+    uint64_t tmem_bytes_per_sm;    /* 256 KiB on sm_100 */
+} cg_b200_props;
+int cg_b200_device_props(int device, cg_b200_props* out);
+int cg_b200_set_device(int device);
+
+/* ---- memory: stands behind cg::Allocator (include/cg/runtime/runtime.hpp:44-49) --- */
+/* Returned pointers are 256-byte aligned, as Allocator::allocate's default alignment. */
+int cg_b200_malloc(void** dev_ptr, size_t bytes);
+int cg_b200_free(void* dev_ptr);
+int cg_b200_malloc_host(void** host_ptr, size_t bytes);   /* pinned */
+int cg_b200_free_host(void* host_ptr);
+int cg_b200_memcpy_h2d(void* dev_dst, const void* host_src, size_t bytes, void* stream);
+int cg_b200_memcpy_d2h(void* host_dst, const void* dev_src, size_t bytes, void* stream);
+int cg_b200_memset(void* dev_dst, int byte, size_t bytes, void* stream);
+
+/* ---- streams / events: cg::Stream, cg::Event (include/cg/runtime/runtime.hpp:51-63) */
+int cg_b200_stream_create(void** stream);
+int cg_b200_stream_destroy(void* stream);
+int cg_b200_stream_sync(void* stream);
+int cg_b200_event_create(void** event);
+int cg_b200_event_destroy(void* event);
+int cg_b200_event_record(void* event, void* stream);
+int cg_b200_event_sync(void* event);
+/* Seconds between two recorded events (Event::elapsed_sec_since, runtime.hpp:62). */
+int cg_b200_event_elapsed_sec(void* earlier, void* later, double* seconds);
+
+/* ---- fused elementwise chain ------------------------------------------------------
+ * Replaces what TensorToCodegenLowering emits for elementwise ops (one un-looped
+ * VectorLoad/Add|Mul/VectorStore per op, src/lowering/tensor_to_codegen.cpp:60-135)
+ * and the straight-line ld/st PTX made from it (src/backend/ptx/ptx_emitter.cpp:60-232).
+ * One launch evaluates a whole chain of Tensor-IR elementwise ops
+ * (src/ir/ops.cpp:277-420) per output element.
+ *
+ * The chain is a postfix program over a value stack of depth <= 4. Arithmetic is fp32;
+ * ADD/SUB/MUL are separately rounded (never contracted into FMA), so chains of
+ * add/mul/max are bit-exact with the reference's x86 vaddps/vmulps/vmaxps kernels
+ * (benchmarks/benchmark_multithread.py:54-124). With 16-bit storage types and
+ * round_each_op != 0 every op result is rounded to the storage type, as if each op had
+ * produced a tensor of that type. */
+enum cg_b200_eltwise_op {
+    CG_B200_EW_INPUT = 0,   /* push inputs[arg][index]                          */
+    CG_B200_EW_IMM = 1,     /* push imm                                         */
+    CG_B200_EW_ADD = 2,     /* pop b, pop a, push a+b                           */
+    CG_B200_EW_SUB = 3,
+    CG_B200_EW_MUL = 4,
+    CG_B200_EW_DIV = 5,
+    CG_B200_EW_MAX = 6,     /* x86 maxps order: a > b ? a : b                   */
+    CG_B200_EW_MIN = 7,     /* x86 minps order: a < b ? a : b                   */
+    CG_B200_EW_NEG = 8,
+    CG_B200_EW_ABS = 9,
+    CG_B200_EW_RELU = 10,   /* x > 0 ? x : +0                                   */
+    CG_B200_EW_GELU_TANH = 11, /* 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))) */
+    CG_B200_EW_TANH = 12,
+    CG_B200_EW_SIGMOID = 13,
+    CG_B200_EW_EXP = 14,
+    CG_B200_EW_LOG = 15,
+    CG_B200_EW_SQRT = 16,
+    CG_B200_EW_RSQRT = 17,
+    CG_B200_EW_OP_COUNT = 18
+};
+
+/* How input i is indexed for flat output index e (row-major, NumPy right-aligned
+ * broadcast, src/shape/inference.cpp:11-31). */
+enum cg_b200_bcast {
+    CG_B200_BC_FULL = 0,    /* [n]            -> in[e]                    */
+    CG_B200_BC_SCALAR = 1,  /* [1]            -> in[0]                    */
+    CG_B200_BC_ROW = 2,     /* [inner]        -> in[e % inner]            */
+    CG_B200_BC_COL = 3      /* [n/inner, 1]   -> in[e / inner]            */
+};
+
+#define CG_B200_EW_MAX_INSTR 16
+#define CG_B200_EW_MAX_INPUTS 8
+#define CG_B200_EW_MAX_STACK 4
+
+typedef struct cg_b200_eltwise_instr {
+    int32_t op;    /* cg_b200_eltwise_op */
+    int32_t arg;   /* input index for EW_INPUT, else 0 */
+    float   imm;   /* value for EW_IMM, else 0 */
+} cg_b200_eltwise_instr;
+
+typedef struct cg_b200_eltwise_desc {
+    int32_t dtype;                               /* storage type of all inputs and the output */
+    int32_t n_instr;
+    cg_b200_eltwise_instr prog[CG_B200_EW_MAX_INSTR];
+    int32_t bcast[CG_B200_EW_MAX_INPUTS];        /* cg_b200_bcast per input */
+    int64_t inner;                               /* period for BC_ROW / BC_COL (>=1) */
+    int32_t round_each_op;                       /* 16-bit storage only */
+    int32_t reserved;
+} cg_b200_eltwise_desc;
+
+/* Checks a program without touching a device: stack discipline, op codes, input
+ * indices. Returns CG_B200_OK or CG_B200_ERR_INVALID_ARG. */
+int cg_b200_eltwise_validate(const cg_b200_eltwise_desc* desc, int n_inputs);
+/* out[e] = program(inputs..., e) for e in [0, n). BC_FULL inputs and `out` must be
+ * aligned to the element size; 16-byte alignment selects the 128-bit path. n == 0 is a
+ * no-op. */
+int cg_b200_eltwise(const cg_b200_eltwise_desc* desc, const void* const* inputs,
+                    int n_inputs, void* out, size_t n, void* stream);
+
+/* ---- row reductions ---------------------------------------------------------------
+ * The reference defines softmax/layernorm as attribute-less ops over the last axis
+ * (src/ir/ops.cpp:536-556), lowers them to an "unknown opcode" Const
+ * (src/lowering/tensor_to_codegen.cpp:350-356) and emits a comment for Reduce
+ * (src/backend/ptx/ptx_emitter.cpp:136-142). Definitions: max-subtracted softmax
+ * (include/cg/egraph/rewrite_rules.hpp:96-101); layernorm = mean, variance, normalise,
+ * scale + shift (src/analysis/arithmetic_intensity.cpp:138-146).
+ * in/out are [rows, cols] row-major contiguous; math is fp32; `in == out` is allowed. */
+int cg_b200_softmax(int dtype, const void* in, void* out, int64_t rows, int64_t cols,
+                    void* stream);
+/* gamma/beta: [cols] of `dtype`, or NULL for 1 / 0. Variance is the biased (1/cols)
+ * centred variance. */
+int cg_b200_layernorm(int dtype, const void* in, const void* gamma, const void* beta,
+                      float eps, void* out, int64_t rows, int64_t cols, void* stream);
+/* layernorm(softmax(in)) in one pass over HBM; the softmax result is rounded to `dtype`
+ * before the layernorm, exactly as the two-kernel sequence would produce it. */
+int cg_b200_softmax_layernorm(int dtype, const void* in, const void* gamma,
+                              const void* beta, float eps, void* out, int64_t rows,
+                              int64_t cols, void* stream);
+
+/* ---- GEMM with fused epilogue -----------------------------------------------------
+ * Replaces the matmul lowering (3 Const, 2 shared VectorLoad, K/k_tile FMA,
+ * src/lowering/tensor_to_codegen.cpp:137-210) and the mma.sync skeleton
+ * (src/backend/tensor_core/ptx_mma.cpp:115-258). Semantics follow OP_MATMUL
+ * (src/ir/ops.cpp, [.., M, K] x [.., K, N], batch dims broadcast; here batch strides
+ * in elements, 0 = broadcast). C = epilogue(A x B). */
+enum cg_b200_epilogue {
+    CG_B200_EPI_NONE = 0,
+    CG_B200_EPI_BIAS = 1,            /* + bias[n]                        */
+    CG_B200_EPI_BIAS_RELU = 2,
+    CG_B200_EPI_BIAS_GELU_TANH = 3,
+    CG_B200_EPI_BIAS_RESIDUAL = 4,   /* + bias[n] + residual[m, n]       */
+    CG_B200_EPI_RESIDUAL = 5,        /* + residual[m, n]                 */
+    CG_B200_EPI_SCALE = 6            /* * alpha                          */
+};
+
+enum cg_b200_compute {
+    CG_B200_COMPUTE_DEFAULT = 0,     /* bf16/f16: native kind::f16; f32: 3xTF32 split */
+    CG_B200_COMPUTE_TF32X3 = 1,      /* f32 inputs: hi*hi + hi*lo + lo*hi              */
+    CG_B200_COMPUTE_TF32 = 2         /* f32 inputs: single TF32 pass (relaxed numerics) */
+};
+
+typedef struct cg_b200_gemm_desc {
+    int64_t M, N, K;
+    int64_t batch;                   /* >= 1 */
+    int64_t lda, ldb, ldc;           /* row strides in elements (A [M,K], B [K,N] or [N,K] if b_transposed, C [M,N]) */
+    int64_t batch_stride_a, batch_stride_b, batch_stride_c; /* elements; 0 = broadcast (A, B only) */
+    int32_t in_dtype;                /* A and B */
+    int32_t out_dtype;               /* C, bias, residual */
+    int32_t compute;                 /* cg_b200_compute */
+    int32_t epilogue;                /* cg_b200_epilogue */
+    int32_t b_transposed;            /* 0: B is [K, N] row-major; 1: B is stored [N, K] row-major */
+    float   alpha;                   /* EPI_SCALE factor */
+} cg_b200_gemm_desc;
+
+/* Bytes of device scratch cg_b200_gemm needs for this problem (0 if none). */
+int cg_b200_gemm_workspace_bytes(const cg_b200_gemm_desc* desc, size_t* bytes);
+/* A, B, C: 16-byte aligned base pointers; strides multiples of 16 bytes. `bias` is [N],
+ * `residual` is [M, N] with row stride ldc (and batch_stride_c), both of out_dtype. */
+int cg_b200_gemm(const cg_b200_gemm_desc* desc, const void* A, const void* B,
+                 const void* bias, const void* residual, void* C, void* workspace,
+                 size_t workspace_bytes, void* stream);
+/* Reads and clears the error word written by a bounded device-side wait that ran out
+ * (0 = none). Synchronises `stream`. */
+int cg_b200_last_device_error(void* stream, uint32_t* word);
+
+/* ---- final all-gather for M- / batch-sharded outputs ------------------------------
+ * The reference has no collective (its only parallel runtime is the std::thread fan-out
+ * in include/cg/backend/parallel_executor.hpp:49-92). One communicator per process,
+ * one process per GPU. host_unique_id is CG_B200_COMM_ID_BYTES made by rank 0 and
+ * shipped to the other ranks by the caller. */
+#define CG_B200_COMM_ID_BYTES 128
+int cg_b200_comm_unique_id(void* host_unique_id);
+int cg_b200_comm_init_rank(void** comm, int world, int rank, const void* host_unique_id);
+/* buf holds world * shard_bytes; rank r's shard already sits at buf + r * shard_bytes. */
+int cg_b200_allgather_inplace(void* comm, void* buf, size_t shard_bytes, void* stream);
+int cg_b200_comm_destroy(void* comm);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* CG_B200_H */

@@ -1,0 +1,54 @@
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+@pytest.fixture(scope="session")
+def oracle():
+    """The CPU oracle (test infrastructure). Built by `make -C oracle`."""
+    from oracle import oracle as O
+    O.lib()
+    return O
+
+
+@pytest.fixture(scope="session")
+def cgb():
+    import cantors_gift_b200 as pkg
+    pkg.lib()
+    return pkg
+
+
+@pytest.fixture(scope="session")
+def ops(cgb):
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from cantors_gift_b200 import ops as _ops
+    return _ops
+
+
+def error_metrics(y, ref):
+    """(max|y-ref| / max|ref|, 99.9th percentile of |y-ref| / max(|ref|, 1e-3 max|ref|))."""
+    y = np.asarray(y, dtype=np.float64).ravel()
+    ref = np.asarray(ref, dtype=np.float64).ravel()
+    scale = max(np.abs(ref).max(), 1e-30)
+    diff = np.abs(y - ref)
+    norm = diff.max() / scale
+    rel = diff / np.maximum(np.abs(ref), 1e-3 * scale)
+    return norm, float(np.percentile(rel, 99.9))
+
+
+def assert_close(y, ref, tol, what=""):
+    """Both metrics must be within `tol` (1e-4 for fp32 paths, 1e-2 for bf16/f16 paths)."""
+    norm, p999 = error_metrics(y, ref)
+    assert norm <= tol and p999 <= tol, f"{what}: max-normalised {norm:.3e}, p99.9 relative {p999:.3e}, tol {tol}"

@@ -1,0 +1,161 @@
+"""Parity of the tcgen05 GEMM (+ fused epilogue) against the CPU oracle, through the C ABI.
+
+Tolerances are the path's stated bounds: rel-err <= 1e-4 for fp32 (3xTF32 split), <= 1e-2 for
+bf16/f16, on both metrics of conftest.assert_close."""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(ops, store, dtype):
+    import torch
+    if store is None:
+        return None
+    raw = torch.from_numpy(store.view(np.int16) if store.dtype != np.float32 else store).cuda()
+    return raw.view(ops.TORCH_DTYPE[dtype]) if store.dtype != np.float32 else raw
+
+
+def _host_f32(O, t, dtype):
+    import torch
+    c = t.cpu()
+    if dtype == O.F32:
+        return c.numpy()
+    return O.to_f32(c.view(torch.int16).numpy().view(np.uint16 if dtype == O.BF16 else np.float16), dtype)
+
+
+def run_case(ops, cgb, O, M, N, K, in_dt, out_dt, epilogue="none", batch=1, b_transposed=0, bsb=None,
+             compute="default", scale=0.05, seed=0, alpha=1.0, rows=None, pad=0):
+    """Returns (gpu fp32 [batch*M, N], oracle fp32 [batch*M, N] (only `rows` valid when given))."""
+    import torch
+    capi = cgb.capi
+    rng = np.random.default_rng(seed)
+    lda, ldc = K + pad, N + pad
+    ldb = (K if b_transposed else N) + pad
+    b_batches = 1 if bsb == 0 else batch
+    A = np.zeros((batch, M, lda), dtype=np.float32)
+    A[:, :, :K] = rng.standard_normal((batch, M, K), dtype=np.float32) * scale
+    Bshape = (b_batches, N, ldb) if b_transposed else (b_batches, K, ldb)
+    B = np.zeros(Bshape, dtype=np.float32)
+    if b_transposed:
+        B[:, :, :K] = rng.standard_normal((b_batches, N, K), dtype=np.float32) * scale
+    else:
+        B[:, :, :N] = rng.standard_normal((b_batches, K, N), dtype=np.float32) * scale
+    bias = rng.standard_normal(N, dtype=np.float32)
+    res = np.zeros((batch, M, ldc), dtype=np.float32)
+    res[:, :, :N] = rng.standard_normal((batch, M, N), dtype=np.float32)
+    As, Bs = O.to_storage(A, in_dt), O.to_storage(B, in_dt)
+    bs_, rs_ = O.to_storage(bias, out_dt), O.to_storage(res, out_dt)
+    kw = dict(epilogue=epilogue, batch=batch, b_transposed=b_transposed, lda=lda, ldb=ldb, ldc=ldc, bsb=bsb, alpha=alpha)
+    od = O.make_gemm_desc(M, N, K, in_dt, out_dt, **kw)
+    want = O.gemm(od, As, Bs, bias=bs_, residual=rs_, rows=rows)
+    want = O.to_f32(want, out_dt).reshape(batch * M, ldc)[:, :N]
+    gd = capi.make_gemm_desc(M, N, K, in_dt, out_dt, compute=compute, **kw)
+    Ad, Bd = _dev(ops, As, in_dt), _dev(ops, Bs, in_dt)
+    Cd = torch.zeros(batch * M * ldc, dtype=ops.TORCH_DTYPE[out_dt], device="cuda")
+    ops.gemm(gd, Ad, Bd, Cd, bias=_dev(ops, bs_, out_dt), residual=_dev(ops, rs_, out_dt))
+    assert ops.last_device_error() == 0, "a bounded device-side wait ran out"
+    got = _host_f32(O, Cd, out_dt).reshape(batch * M, ldc)[:, :N]
+    return got, want
+
+
+SHAPES = [(128, 256, 64), (128, 256, 256), (256, 512, 192), (128, 64, 64), (128, 128, 128),
+          (100, 200, 72), (1, 8, 8), (130, 264, 328), (384, 768, 1024)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("b_transposed", [0, 1])
+def test_bf16_gemm_plain(ops, cgb, oracle, M, N, K, b_transposed):
+    capi = cgb.capi
+    got, want = run_case(ops, cgb, oracle, M, N, K, capi.BF16, capi.BF16, b_transposed=b_transposed, seed=M + N + K)
+    assert_close(got, want, 1e-2, f"bf16 {M}x{N}x{K} bT={b_transposed}")
+
+
+@pytest.mark.parametrize("epilogue", ["bias", "bias_relu", "bias_gelu_tanh", "bias_residual", "residual", "scale"])
+@pytest.mark.parametrize("out_name", ["BF16", "F32"])
+def test_bf16_gemm_epilogues(ops, cgb, oracle, epilogue, out_name):
+    capi = cgb.capi
+    out_dt = getattr(capi, out_name)
+    got, want = run_case(ops, cgb, oracle, 200, 328, 136, capi.BF16, out_dt, epilogue=epilogue, scale=0.2, alpha=0.125)
+    assert_close(got, want, 1e-2 if out_name == "BF16" else 2e-3, f"{epilogue} -> {out_name}")
+
+
+def test_f16_gemm(ops, cgb, oracle):
+    capi = cgb.capi
+    got, want = run_case(ops, cgb, oracle, 256, 256, 256, capi.F16, capi.F16, epilogue="bias_gelu_tanh", scale=0.1)
+    assert_close(got, want, 1e-2, "f16 gelu")
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 32), (128, 128, 256), (200, 136, 100), (256, 384, 512), (5, 3, 7)])
+@pytest.mark.parametrize("b_transposed", [0, 1])
+def test_fp32_gemm_3xtf32(ops, cgb, oracle, M, N, K, b_transposed):
+    """fp32 in/out: hi/lo TF32 split. Inputs ~U[-1,1) as in the 1024^3 configuration."""
+    capi = cgb.capi
+    pad = (-N) % 4  # C rows must be 16-byte multiples
+    got, want = run_case(ops, cgb, oracle, M, N, K, capi.F32, capi.F32, b_transposed=b_transposed, scale=0.5,
+                         seed=K, pad=pad)
+    assert_close(got, want, 1e-4, f"fp32 {M}x{N}x{K} bT={b_transposed}")
+
+
+def test_fp32_gemm_matches_reference_golden(ops, cgb, oracle):
+    """The reference's own JIT matmul outputs (tests/golden) within the fp32 bound."""
+    import torch
+    capi = cgb.capi
+    gold = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_kernels.npz"))
+    A, B, Cref = gold["mm_sq_A"], gold["mm_sq_B"], gold["mm_sq_C"]
+    M, K = A.shape
+    N = B.shape[1]
+    gd = capi.make_gemm_desc(M, N, K, capi.F32, capi.F32)
+    Cd = torch.zeros(M, N, device="cuda")
+    ops.gemm(gd, torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda(), Cd)
+    assert ops.last_device_error() == 0
+    assert_close(Cd.cpu().numpy(), Cref, 1e-4, "golden mm_sq")
+
+
+def test_batched_and_broadcast(ops, cgb, oracle):
+    capi = cgb.capi
+    got, want = run_case(ops, cgb, oracle, 136, 72, 64, capi.BF16, capi.BF16, batch=5, epilogue="scale", alpha=0.5)
+    assert_close(got, want, 1e-2, "batched")
+    got, want = run_case(ops, cgb, oracle, 136, 264, 64, capi.BF16, capi.BF16, batch=3, bsb=0, b_transposed=1)
+    assert_close(got, want, 1e-2, "B broadcast over batch")
+
+
+def test_k_zero_gives_epilogue_of_zero(ops, cgb, oracle):
+    capi = cgb.capi
+    got, want = run_case(ops, cgb, oracle, 130, 72, 0, capi.BF16, capi.BF16, epilogue="bias")
+    assert_close(got, want, 1e-2, "K=0")
+
+
+def test_full_size_bf16_gemm_bias_gelu(ops, cgb, oracle):
+    """M=N=K=4096, bias + GELU(tanh): 48 sampled rows against the oracle (all columns), plus
+    linearity in A on the raw product, which holds at any size."""
+    import torch
+    capi = cgb.capi
+    O = oracle
+    M = N = K = 4096
+    rng = np.random.default_rng(2)
+    A = O.to_bf16(rng.standard_normal((M, K), dtype=np.float32) * 0.02)
+    B = O.to_bf16(rng.standard_normal((K, N), dtype=np.float32) * 0.02)
+    bias = O.to_bf16(rng.standard_normal(N, dtype=np.float32))
+    rows = np.sort(rng.choice(M, size=48, replace=False)).astype(np.int64)
+    od = O.make_gemm_desc(M, N, K, O.BF16, O.BF16, epilogue="bias_gelu_tanh")
+    want = O.from_bf16(O.gemm(od, A, B, bias=bias, rows=rows)).reshape(M, N)[rows]
+    gd = capi.make_gemm_desc(M, N, K, capi.BF16, capi.BF16, epilogue="bias_gelu_tanh")
+    Ad, Bd, bd = _dev(ops, A, capi.BF16), _dev(ops, B, capi.BF16), _dev(ops, bias, capi.BF16)
+    Cd = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    ops.gemm(gd, Ad, Bd, Cd, bias=bd)
+    assert ops.last_device_error() == 0
+    got = _host_f32(O, Cd, capi.BF16).reshape(M, N)[rows]
+    assert_close(got, want, 1e-2, "4096^3 bias+gelu sample")
+    # linearity: (2A) B == 2 (A B) exactly in bf16/fp32 arithmetic (power-of-two scaling)
+    gd0 = capi.make_gemm_desc(M, N, K, capi.BF16, capi.F32)
+    C1 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    C2 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    ops.gemm(gd0, Ad, Bd, C1)
+    ops.gemm(gd0, Ad * 2, Bd, C2)
+    torch.cuda.synchronize()
+    assert torch.equal(C1 * 2, C2)

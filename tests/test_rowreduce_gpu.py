@@ -1,0 +1,105 @@
+"""Parity of softmax / layernorm / layernorm(softmax) against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+
+from conftest import assert_close
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"F32": 1e-4, "BF16": 1e-2, "F16": 1e-2}   # the path's stated bounds: fp32 1e-4, 16-bit 1e-2
+
+
+def _to_dev(ops, store, dtype):
+    import torch
+    if store is None:
+        return None
+    raw = torch.from_numpy(store.view(np.int16) if store.dtype != np.float32 else store).cuda()
+    return raw.view(ops.TORCH_DTYPE[dtype]) if store.dtype != np.float32 else raw
+
+
+def _to_host_f32(O, t, dtype):
+    import torch
+    c = t.cpu()
+    if dtype == O.F32:
+        return c.numpy()
+    return O.to_f32(c.view(torch.int16).numpy().view(np.uint16 if dtype == O.BF16 else np.float16), dtype)
+
+
+SHAPES = [(1, 8), (3, 16), (17, 100), (5, 1000), (9, 4096), (4, 1024), (33, 2048), (2, 8192), (3, 20000), (7, 13)]
+
+
+@pytest.mark.parametrize("dtype_name", ["F32", "BF16", "F16"])
+@pytest.mark.parametrize("rows,cols", SHAPES)
+def test_row_ops_match_oracle(ops, cgb, oracle, dtype_name, rows, cols):
+    O = oracle
+    dtype = getattr(cgb.capi, dtype_name)
+    rng = np.random.default_rng(rows * 100003 + cols)
+    x = rng.standard_normal((rows, cols), dtype=np.float32)
+    g = rng.standard_normal(cols, dtype=np.float32)
+    b = rng.standard_normal(cols, dtype=np.float32)
+    xs, gs, bs = O.to_storage(x, dtype), O.to_storage(g, dtype), O.to_storage(b, dtype)
+    xd, gd, bd = _to_dev(ops, xs, dtype), _to_dev(ops, gs, dtype), _to_dev(ops, bs, dtype)
+    tol = TOL[dtype_name]
+    got = _to_host_f32(O, ops.softmax(xd), dtype)
+    assert_close(got, O.to_f32(O.softmax(xs, dtype), dtype), tol, "softmax")
+    got = _to_host_f32(O, ops.layernorm(xd, gd, bd, eps=1e-5), dtype)
+    assert_close(got, O.to_f32(O.layernorm(xs, dtype, gs, bs, 1e-5), dtype), tol, "layernorm")
+    got = _to_host_f32(O, ops.layernorm(xd, eps=1e-5), dtype)
+    assert_close(got, O.to_f32(O.layernorm(xs, dtype, None, None, 1e-5), dtype), tol, "layernorm plain")
+
+
+@pytest.mark.parametrize("dtype_name", ["F32", "BF16"])
+@pytest.mark.parametrize("rows,cols", [(6, 4096), (3, 520), (5, 77), (2, 20000)])
+def test_fused_softmax_layernorm(ops, cgb, oracle, dtype_name, rows, cols):
+    """The fused kernel equals the two-kernel sequence (storage-typed tensor in between). Softmax
+    rows have variance far below eps, so the output is compared with a floor on the reference."""
+    O = oracle
+    dtype = getattr(cgb.capi, dtype_name)
+    rng = np.random.default_rng(cols)
+    x = rng.standard_normal((rows, cols), dtype=np.float32)
+    xs = O.to_storage(x, dtype)
+    xd = _to_dev(ops, xs, dtype)
+    want = O.to_f32(O.softmax_layernorm(xs, dtype, None, None, 1e-5), dtype)
+    got = _to_host_f32(O, ops.softmax_layernorm(xd, eps=1e-5), dtype)
+    # bf16: the rounded softmax values feed a difference of nearly equal numbers; one ulp of the
+    # intermediate (2^-9 relative) is the resolution of the result
+    assert_close(got, want, 2e-2 if dtype_name == "BF16" else 1e-4, "softmax_layernorm")
+    two = _to_host_f32(O, ops.layernorm(ops.softmax(xd), eps=1e-5), dtype)
+    assert_close(got, two, 2e-2 if dtype_name == "BF16" else 1e-4, "fused vs two kernels")
+
+
+def test_in_place_and_empty(ops, cgb, oracle):
+    import torch
+    x = torch.randn(11, 1024, device="cuda")
+    want = ops.softmax(x)
+    y = x.clone()
+    ops.softmax(y, out=y)
+    torch.cuda.synchronize()
+    assert torch.equal(y, want)
+    e = torch.empty(0, 64, device="cuda")
+    assert ops.softmax(e).shape == (0, 64)
+    assert ops.layernorm(e).shape == (0, 64)
+
+
+def test_full_size_config_properties(ops, cgb, oracle):
+    """layernorm(softmax(x)) on bf16 [32768, 4096]: sampled rows against the oracle, and properties
+    that hold for every row: softmax rows sum to 1, layernorm rows have mean 0."""
+    import torch
+    O = oracle
+    rows, cols = 32768, 4096
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(rows, cols, device="cuda", generator=g).to(torch.bfloat16)
+    p = ops.softmax(x)
+    y = ops.softmax_layernorm(x, eps=1e-5)
+    torch.cuda.synchronize()
+    s = p.float().sum(dim=1)
+    assert float((s - 1).abs().max()) < 2e-2      # bf16 rounding of 4096 terms
+    assert float(y.float().mean(dim=1).abs().max()) < 2e-2
+    idx = torch.arange(0, rows, 1371, device="cuda")
+    xs = x[idx].cpu().view(torch.int16).numpy().view(np.uint16)
+    want = O.from_bf16(O.softmax_layernorm(xs, O.BF16, None, None, 1e-5))
+    got = O.from_bf16(y[idx].cpu().view(torch.int16).numpy().view(np.uint16))
+    assert_close(got, want, 2e-2, "cfg4 sample")
+    want_p = O.from_bf16(O.softmax(xs, O.BF16))
+    got_p = O.from_bf16(p[idx].cpu().view(torch.int16).numpy().view(np.uint16))
+    assert_close(got_p, want_p, 1e-2, "cfg4 softmax sample")
