@@ -461,15 +461,18 @@ def time_e2e(w, steps, warmup, world):
     return secs, h2d, d2h
 
 
-def run_workload(name, steps, warmup, rank, world, peaks, sample_clocks, with_cpu, cpu_budget):
+def run_workload(name, steps, warmup, rank, world, peaks, sample_clocks, with_cpu, cpu_budget, with_e2e=True):
     w = WORKLOADS[name]()
     w.setup(rank, world)
     secs, clocks = time_workload(w, steps, warmup, rank, world, sample_clocks)
     ms_per_step = secs / steps * 1e3
     value = w.work_per_step() * steps / secs
     e2e_steps = max(3, min(steps, 10))
-    e_secs, h2d, d2h = time_e2e(w, e2e_steps, warmup, world)
-    e2e_work = w.work_per_step() if name not in ("gemm", "matmul_f32") else w.work_per_step()
+    if with_e2e:
+        e_secs, h2d, d2h = time_e2e(w, e2e_steps, warmup, world)
+    else:
+        e_secs, h2d, d2h = float("inf"), 0, 0
+    e2e_work = w.work_per_step()
     if w.bound == "hbm":
         achieved = w.algorithmic_per_launch() / (secs / steps) / 1e9
         peak, unit = peaks["hbm_gbs"], "GB/s"
@@ -541,6 +544,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-also", action="store_true", help="skip the secondary workloads")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -566,14 +570,14 @@ def main():
     peaks = measured_peaks()
 
     line = run_workload(args.workload, args.steps, args.warmup, rank, world, peaks, sample_clocks=(rank == 0),
-                        with_cpu=(world == 1 and not args.no_cpu), cpu_budget=12.0)
+                        with_cpu=(world == 1 and not args.no_cpu), cpu_budget=12.0, with_e2e=not args.no_e2e)
     if not args.no_also and world == 1:
         also = []
         for other in ("eltwise", "rowreduce", "matmul_f32"):
             if other == args.workload:
                 continue
             r = run_workload(other, args.steps, args.warmup, rank, world, peaks, sample_clocks=True,
-                             with_cpu=not args.no_cpu, cpu_budget=5.0)
+                             with_cpu=not args.no_cpu, cpu_budget=5.0, with_e2e=not args.no_e2e)
             also.append({k: r[k] for k in ("value", "unit", "ms_per_step", "dtype", "config", "e2e", "roofline",
                                            "gpu_launches", "clocks", "cpu_baseline") if k in r})
         line["also"] = also

@@ -81,6 +81,64 @@ __device__ __forceinline__ void st_stream(T* p, const Vec16<T>& v) {
     __stcs(reinterpret_cast<int4*>(p), *reinterpret_cast<const int4*>(&v));
 }
 
+// 16-byte packet <-> fp32 lanes with the cheapest conversions the type allows: bf16 is the top
+// half of an fp32 (a shift or a mask per element), and two fp32 pack into one cvt.rn.*x2.
+template <typename T>
+__device__ __forceinline__ void unpack16(const Vec16<T>& v, float (&f)[Vec16<T>::N]) {
+    if constexpr (sizeof(T) == 4) {
+#pragma unroll
+        for (int l = 0; l < 4; ++l) f[l] = v.v[l];
+    } else if constexpr (Elem<T>::dtype == CG_B200_BF16) {
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+            f[2 * l] = __uint_as_float(w[l] << 16);
+            f[2 * l + 1] = __uint_as_float(w[l] & 0xffff0000u);
+        }
+    } else {
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+            const float2 t = __half22float2(h[l]);
+            f[2 * l] = t.x;
+            f[2 * l + 1] = t.y;
+        }
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ Vec16<T> pack16(const float (&f)[Vec16<T>::N]) {
+    Vec16<T> v;
+    if constexpr (sizeof(T) == 4) {
+#pragma unroll
+        for (int l = 0; l < 4; ++l) v.v[l] = f[l];
+    } else if constexpr (Elem<T>::dtype == CG_B200_BF16) {
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int l = 0; l < 4; ++l) h[l] = __floats2bfloat162_rn(f[2 * l], f[2 * l + 1]);
+    } else {
+        __half2* h = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+        for (int l = 0; l < 4; ++l) h[l] = __floats2half2_rn(f[2 * l], f[2 * l + 1]);
+    }
+    return v;
+}
+
+// Rounds fp32 lanes to T and back (what storing and reloading a tensor of type T does).
+template <typename T>
+__device__ __forceinline__ void round_through16(float (&f)[Vec16<T>::N]) {
+    if constexpr (sizeof(T) != 4) {
+        const Vec16<T> v = pack16<T>(f);
+        unpack16<T>(v, f);
+    }
+}
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // gelu, tanh form: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), every product rounded
 // separately so the value does not depend on contraction choices.
 __device__ __forceinline__ float gelu_tanh_f32(float x) {

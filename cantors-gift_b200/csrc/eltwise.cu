@@ -320,9 +320,13 @@ static int launch_typed(const EltParams& p, bool vector_ok, cudaStream_t s) {
         return CG_B200_OK;
     }
     constexpr int L = 16 / sizeof(T);
-    // whole multiples of the SM count: 8 resident blocks of 256 threads per SM
+    // One thread per two packets. Measured on B200: for this streaming pattern a grid that covers
+    // the whole array (tens of thousands of short-lived CTAs) sustains about 10 % more HBM
+    // bandwidth than a persistent grid of 8 CTAs per SM; the grid-stride loop only matters when
+    // the array exceeds the grid limit.
+    (void)sms;
     unsigned long long want = (p.n / L + 2 * 256 - 1) / (2 * 256);
-    unsigned long long cap = (unsigned long long)sms * 8;
+    const unsigned long long cap = 0x7fffffffull;
     int blocks = (int)(want < cap ? (want == 0 ? 1 : want) : cap);
     if (matches<ProgMulAddReluScale>(p)) launch_vec<T, ProgMulAddReluScale>(p, blocks, s);
     else if (matches<ProgAdd>(p)) launch_vec<T, ProgAdd>(p, blocks, s);

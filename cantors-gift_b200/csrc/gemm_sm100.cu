@@ -7,6 +7,13 @@
 // executable. The only matmul the reference runs is the scalar x86 FMA loop of
 // benchmarks/benchmark.py:326-438; parity is defined against that accumulation.
 //
+// Two tile shapes share one kernel template (kCta):
+//   kCta = 2  a cluster of two CTAs on two SMs computes one 256 x BN tile with cta_group::2
+//             MMAs issued by the even CTA: each CTA stages its own 128 rows of A and its own half
+//             of B's N range, so every byte of the tile's operands is fetched from L2 once per
+//             pair (no TMA multicast is used anywhere); each CTA's TMEM holds its 128 rows of the
+//             accumulator and its own epilogue warps drain them
+//   kCta = 1  one CTA computes a 128 x BN tile (small problems, fp32 split)
 // Structure (one CTA per SM, persistent over output tiles, 192 threads):
 //   warp 0      TMA producer: cp.async.bulk.tensor loads of A and B k-blocks (128 bytes of K
 //               per row, 128-byte swizzle) into a ring of shared-memory stages
@@ -22,6 +29,7 @@
 // wait runs out the kernel records an error word, stops waiting everywhere, drains its
 // copies, frees TMEM and returns.
 #include <cuda.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -104,23 +112,77 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// In the shared::cluster window bit 24 of an address selects the odd CTA of a pair; clearing it
+// names the even CTA's copy of the same barrier.
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;
+
+// Plain (non-multicast) tiled load into this CTA's shared memory. With kCta == 2 the byte count is
+// credited to the even CTA's barrier, which the MMA issuer waits on.
+template <int kCta>
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
-        : "memory");
+    if constexpr (kCta == 1) {
+        asm volatile(
+            "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+            ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
+            : "memory");
+    } else {
+        asm volatile(
+            "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+            ::"r"(dst), "l"(map), "r"(bar & kPeerBitMask), "r"(x), "r"(y), "r"(z)
+            : "memory");
+    }
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// Arrives on `bar` once every tcgen05.mma issued so far by this thread has completed. With two
+// CTAs the arrival is delivered to the barrier at the same offset in both CTAs of the pair.
+template <int kCta>
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    if constexpr (kCta == 1) {
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    } else {
+        const uint16_t both = 3;
+        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                     ::"r"(bar), "h"(both) : "memory");
+    }
 }
 
-template <bool kTF32>
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on the barrier at the same shared-memory offset in CTA `rank` of the cluster.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t bar, uint32_t rank) {
+    asm volatile(
+        "{\n\t.reg .b32 ra;\n\t"
+        "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}"
+        ::"r"(bar), "r"(rank) : "memory");
+}
+
+template <bool kTF32, int kCta>
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
-    if constexpr (kTF32) {
+    if constexpr (kCta == 2) {
+        if constexpr (kTF32) {
+            asm volatile(
+                "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+                : "memory");
+        } else {
+            asm volatile(
+                "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+                : "memory");
+        }
+    } else if constexpr (kTF32) {
         asm volatile(
             "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
             "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
@@ -183,21 +245,22 @@ __device__ __forceinline__ float gelu_epilogue(float x) {
 struct TileCoord {
     int b, m0, n0;
 };
-__device__ __forceinline__ TileCoord decode_tile(long long tile, const GemmParams& p, int bn) {
+__device__ __forceinline__ TileCoord decode_tile(long long tile, const GemmParams& p, int bm, int bn) {
     const long long per_batch = (long long)p.tiles_m * p.tiles_n;
     TileCoord t;
     t.b = (int)(tile / per_batch);
     const int r = (int)(tile - (long long)t.b * per_batch);
-    t.m0 = (r / p.tiles_n) * kBM;
+    t.m0 = (r / p.tiles_n) * bm;
     t.n0 = (r % p.tiles_n) * bn;
     return t;
 }
 
 // kCopies: operand copies per stage (1, or 2 = hi and lo halves of the fp32 split)
-template <int kCopies, int BN>
+// BNL: rows (N) of B staged by one CTA = BN / kCta
+template <int kCopies, int BNL>
 struct StageLayout {
     static constexpr int kABytes = kBM * kRowBytes;      // 16 KiB
-    static constexpr int kBBytes = BN * kRowBytes;
+    static constexpr int kBBytes = BNL * kRowBytes;
     static constexpr int kStageBytes = kCopies * (kABytes + kBBytes);
     static constexpr int kStagesFit = kSmemBudget / kStageBytes;
     static constexpr int kStages = kStagesFit > kMaxStages ? kMaxStages : kStagesFit;
@@ -205,14 +268,16 @@ struct StageLayout {
     static_assert(kStages >= 2, "at least a double buffer");
 };
 
-template <bool kTF32, bool kSplit, int BN, typename OutT>
+template <int kCta, bool kTF32, bool kSplit, int BN, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_lo,
                   const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b_lo,
                   const __grid_constant__ GemmParams p) {
     constexpr int kCopies = kSplit ? 2 : 1;
     constexpr int kPasses = kSplit ? 3 : 1;   // tcgen05.mma passes per k-step
-    using L = StageLayout<kCopies, BN>;
+    constexpr int BNL = BN / kCta;             // B rows this CTA stages
+    constexpr int kTileM = kBM * kCta;
+    using L = StageLayout<kCopies, BNL>;
     constexpr int kStages = L::kStages;
     constexpr int kElem = kTF32 ? 4 : 2;
     constexpr int kBKElems = kRowBytes / kElem;         // K elements per stage
@@ -231,6 +296,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = kCta == 2 ? cluster_ctarank() : 0u;
+    const long long tile_first = kCta == 2 ? (long long)(blockIdx.x >> 1) : (long long)blockIdx.x;
+    const long long tile_step = kCta == 2 ? (long long)(gridDim.x >> 1) : (long long)gridDim.x;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -239,19 +307,26 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&bar_acc_full[a]), 1);
-            mbar_init(smem_u32(&bar_acc_empty[a]), 4);
+            mbar_init(smem_u32(&bar_acc_empty[a]), 4 * kCta);
         }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (kCta == 1) {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if constexpr (kCta == 2) cluster_sync_all();   // the peer's barriers exist before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
 
@@ -262,8 +337,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             uint32_t phase = 0;
             long long issued = 0;
             bool ok = true;
-            for (long long tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-                const TileCoord t = decode_tile(tile, p, BN);
+            for (long long tile = tile_first; ok && tile < p.num_tiles; tile += tile_step) {
+                TileCoord t = decode_tile(tile, p, kTileM, BN);
+                t.m0 += (int)cta_rank * kBM;      // this CTA's rows of A
+                t.n0 += (int)cta_rank * BNL;      // this CTA's part of B's N range
                 const int za = p.a_batched ? t.b : 0, zb = p.b_batched ? t.b : 0;
                 for (int kb = 0; kb < p.num_kb; ++kb) {
                     if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag, p.err_word, 0x100u + stage)) {
@@ -271,7 +348,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                         break;
                     }
                     const uint32_t full = smem_u32(&bar_full[stage]);
-                    mbar_expect_tx(full, (uint32_t)L::kStageBytes);
+                    // the even CTA's barrier collects the bytes of both CTAs
+                    if (cta_rank == 0) mbar_expect_tx(full, (uint32_t)(kCta * L::kStageBytes));
                     const uint32_t sa = smem_base + stage * L::kStageBytes;
                     const uint32_t sb = sa + kCopies * L::kABytes;
                     const int k0 = kb * kBKElems;
@@ -279,13 +357,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     for (int ps = 0; ps < kCopies; ++ps) {
                         const CUtensorMap* ma = ps == 0 ? &tm_a : &tm_a_lo;
                         const CUtensorMap* mb = ps == 0 ? &tm_b : &tm_b_lo;
-                        tma_load_3d(sa + ps * L::kABytes, ma, full, k0, t.m0, za);
+                        tma_load_3d<kCta>(sa + ps * L::kABytes, ma, full, k0, t.m0, za);
                         if (p.b_mn_major) {
 #pragma unroll
-                            for (int j = 0; j < BN / kBBoxCols; ++j)
-                                tma_load_3d(sb + ps * L::kBBytes + j * kBBoxBytes, mb, full, t.n0 + j * kBBoxCols, k0, zb);
+                            for (int j = 0; j < BNL / kBBoxCols; ++j)
+                                tma_load_3d<kCta>(sb + ps * L::kBBytes + j * kBBoxBytes, mb, full, t.n0 + j * kBBoxCols, k0, zb);
                         } else {
-                            tma_load_3d(sb + ps * L::kBBytes, mb, full, k0, t.n0, zb);
+                            tma_load_3d<kCta>(sb + ps * L::kBBytes, mb, full, k0, t.n0, zb);
                         }
                     }
                     ++issued;
@@ -307,13 +385,15 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                         s = kStages - 1;
                         ph ^= 1u;
                     }
-                    mbar_wait(smem_u32(&bar_full[s]), ph, &never, nullptr, 0, 50000000ull);
+                    // (the odd CTA of a pair signals the even CTA's barrier: its own never completes and this
+                    // simply waits out the limit, which is the point of the drain)
+                    mbar_wait(smem_u32(&bar_full[s]), ph, &never, nullptr, 0, 20000000ull);
                 }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
+        if (lane == 0 && cta_rank == 0) {
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
@@ -324,7 +404,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             // bytes to advance the B descriptor per tcgen05.mma: one 32-byte K slice inside the swizzle
             // span when K is contiguous, kUmmaK rows of 128 bytes when N is contiguous
             const uint32_t b_kstep = p.b_mn_major ? (uint32_t)(kUmmaKBytes / kElem) * kRowBytes : (uint32_t)kUmmaKBytes;
-            for (long long tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+            for (long long tile = tile_first; ok && tile < p.num_tiles; tile += tile_step) {
                 if (!mbar_wait(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, &abort_flag, p.err_word, 0x200u + acc)) {
                     ok = false;
                     break;
@@ -349,19 +429,19 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                         const uint64_t db = make_smem_desc(sb + ib * L::kBBytes, b_lbo, b_sbo);
 #pragma unroll
                         for (int k = 0; k < kKSteps; ++k) {
-                            umma<kTF32>(tmem_d, da + (uint64_t)((k * kUmmaKBytes) >> 4), db + (uint64_t)((k * b_kstep) >> 4),
+                            umma<kTF32, kCta>(tmem_d, da + (uint64_t)((k * kUmmaKBytes) >> 4), db + (uint64_t)((k * b_kstep) >> 4),
                                         p.idesc, first);
                             first = 1;
                         }
                     }
-                    tc_commit(smem_u32(&bar_empty[stage]));
+                    tc_commit<kCta>(smem_u32(&bar_empty[stage]));
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
                 if (!ok) break;
-                tc_commit(smem_u32(&bar_acc_full[acc]));
+                tc_commit<kCta>(smem_u32(&bar_acc_full[acc]));
                 acc ^= 1;
                 if (acc == 0) acc_phase ^= 1u;
             }
@@ -381,13 +461,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         const bool has_res = epi == CG_B200_EPI_BIAS_RESIDUAL || epi == CG_B200_EPI_RESIDUAL;
         const bool bias_vec = has_bias && ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
         constexpr int kPack = 16 / sizeof(OutT);  // elements per 16-byte store
-        for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+        for (long long tile = tile_first; tile < p.num_tiles; tile += tile_step) {
             bool ok = mbar_wait(smem_u32(&bar_acc_full[acc]), acc_phase, &abort_flag, p.err_word, 0x400u + acc);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            const TileCoord t = decode_tile(tile, p, BN);
-            const long long m = (long long)t.m0 + row_in_tile;
+            const TileCoord t = decode_tile(tile, p, kTileM, BN);
+            const long long m = (long long)t.m0 + (long long)cta_rank * kBM + row_in_tile;
             const bool row_ok = m < p.M;
             const long long row_off = (long long)t.b * p.batch_stride_c + m * p.ldc;
 #pragma unroll 1
@@ -459,7 +539,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
+            if (lane == 0) {
+                // the issuer waits on the even CTA's barrier for the epilogue warps of both CTAs
+                if (cta_rank == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
+                else mbar_arrive_remote(smem_u32(&bar_acc_empty[acc]), 0);
+            }
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1u;
         }
@@ -468,14 +552,25 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     // ---------------- teardown ----------------
     tc_fence_before();
     __syncthreads();
+    if constexpr (kCta == 2) cluster_sync_all();   // neither CTA leaves while the other may still signal it
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+        if constexpr (kCta == 1)
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
 }
 
-// Splits fp32 x into hi = x with the low 13 mantissa bits cleared (exactly a tf32 value) and
-// lo = (x - hi) cleared the same way. rows x cols with source row stride ld_src, destination ld_dst.
+// fp32 operands are rewritten into a K-contiguous workspace before the GEMM: hi = x with the low
+// 13 mantissa bits cleared (exactly a tf32 value) and, for the 3xTF32 split, lo = (x - hi) cleared
+// the same way (lo == nullptr skips it). rows x cols, source row stride ld_src, destination row
+// stride ld_dst >= cols (the pad columns are written as zero).
+__device__ __forceinline__ void tf32_split(float x, float& h, float& l) {
+    h = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
+    l = __uint_as_float(__float_as_uint(x - h) & 0xffffe000u);
+}
+
 __global__ void __launch_bounds__(256)
 tf32_split_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo, long long rows,
                   long long cols, long long ld_src, long long ld_dst, long long batch, long long bs_src,
@@ -489,10 +584,35 @@ tf32_split_kernel(const float* __restrict__ src, float* __restrict__ hi, float* 
         const long long c = i - b * per - r * ld_dst;
         float x = 0.0f;
         if (c < cols) x = src[b * bs_src + r * ld_src + c];
-        const float h = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
-        const float l = __uint_as_float(__float_as_uint(x - h) & 0xffffe000u);
+        float h, l;
+        tf32_split(x, h, l);
         hi[b * bs_dst + r * ld_dst + c] = h;
-        lo[b * bs_dst + r * ld_dst + c] = l;
+        if (lo) lo[b * bs_dst + r * ld_dst + c] = l;
+    }
+}
+
+// Same, transposing: src is [rows, cols] (row stride ld_src), dst is [cols, ld_dst] with ld_dst >= rows.
+// 32 x 32 tiles through shared memory; grid = (ceil(cols/32), ceil(ld_dst/32), batch), block = (32, 8).
+__global__ void __launch_bounds__(256)
+tf32_split_transpose_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo,
+                            long long rows, long long cols, long long ld_src, long long ld_dst, long long bs_src,
+                            long long bs_dst) {
+    __shared__ float tile[32][33];
+    const long long b = blockIdx.z;
+    const long long c0 = (long long)blockIdx.x * 32, r0 = (long long)blockIdx.y * 32;
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        const long long r = r0 + j, c = c0 + threadIdx.x;
+        tile[j][threadIdx.x] = (r < rows && c < cols) ? src[b * bs_src + r * ld_src + c] : 0.0f;
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        const long long c = c0 + j, r = r0 + threadIdx.x;   // dst row = source column
+        if (c < cols && r < ld_dst) {
+            float h, l;
+            tf32_split(tile[threadIdx.x][j], h, l);
+            hi[b * bs_dst + c * ld_dst + r] = h;
+            if (lo) lo[b * bs_dst + c * ld_dst + r] = l;
+        }
     }
 }
 
@@ -536,7 +656,7 @@ static int make_map(CUtensorMap* map, const void* base, int dtype, uint64_t inne
     return CG_B200_OK;
 }
 
-static uint32_t make_idesc(int in_dtype, bool tf32, bool b_mn_major, int bn) {
+static uint32_t make_idesc(int in_dtype, bool tf32, bool b_mn_major, int bm, int bn) {
     uint32_t d = 0;
     d |= 1u << 4;                                                   // accumulator format: F32
     const uint32_t fmt = tf32 ? 2u : (in_dtype == CG_B200_BF16 ? 1u : 0u);
@@ -545,30 +665,33 @@ static uint32_t make_idesc(int in_dtype, bool tf32, bool b_mn_major, int bn) {
     d |= 0u << 15;                                                  // A: K-major
     d |= (b_mn_major ? 1u : 0u) << 16;                              // B: MN-major when N is contiguous
     d |= (uint32_t)(bn >> 3) << 17;                                 // N / 8
-    d |= (uint32_t)(kBM >> 4) << 24;                                // M / 16
+    d |= (uint32_t)(bm >> 4) << 24;                                 // M / 16 (256 for a CTA pair)
     return d;
 }
 
-struct SplitPlan {
-    bool split;            // 3xTF32 with workspace
-    long long lda_w, ldb_w;   // workspace row strides (elements)
-    long long a_elems, b_elems;  // per hi (or lo) array
+// fp32 inputs always go through the workspace: `copies` arrays (hi, or hi and lo) of A as [M, ldk]
+// and of B as [N, ldk], K contiguous, ldk = K rounded up to 4 elements (16 bytes).
+struct Fp32Plan {
+    bool active;
+    int copies;
+    long long ldk;
+    long long a_elems, b_elems;   // per copy
     size_t bytes;
 };
 
 static inline long long round_up(long long x, long long a) { return (x + a - 1) / a * a; }
 
-static SplitPlan plan_split(const cg_b200_gemm_desc* d) {
-    SplitPlan s{};
-    s.split = d->in_dtype == CG_B200_F32 && d->compute != CG_B200_COMPUTE_TF32;
-    if (!s.split) return s;
-    s.lda_w = round_up(d->K, 4);
-    s.ldb_w = round_up(d->b_transposed ? d->K : d->N, 4);
-    const long long a_batches = d->batch_stride_a == 0 ? 1 : d->batch;
-    const long long b_batches = d->batch_stride_b == 0 ? 1 : d->batch;
-    s.a_elems = round_up(a_batches * d->M * s.lda_w, 64);
-    s.b_elems = round_up(b_batches * (d->b_transposed ? d->N : d->K) * s.ldb_w, 64);
-    s.bytes = (size_t)(2 * (s.a_elems + s.b_elems)) * sizeof(float);
+static Fp32Plan plan_fp32(const cg_b200_gemm_desc* d) {
+    Fp32Plan s{};
+    s.active = d->in_dtype == CG_B200_F32;
+    if (!s.active) return s;
+    s.copies = d->compute == CG_B200_COMPUTE_TF32 ? 1 : 2;
+    s.ldk = round_up(d->K > 0 ? d->K : 1, 4);
+    const long long a_batches = (d->batch_stride_a == 0 || d->batch == 1) ? 1 : d->batch;
+    const long long b_batches = (d->batch_stride_b == 0 || d->batch == 1) ? 1 : d->batch;
+    s.a_elems = round_up(a_batches * d->M * s.ldk, 64);
+    s.b_elems = round_up(b_batches * d->N * s.ldk, 64);
+    s.bytes = (size_t)(s.copies * (s.a_elems + s.b_elems)) * sizeof(float);
     return s;
 }
 
@@ -589,36 +712,61 @@ static int validate_desc(const cg_b200_gemm_desc* d) {
     return CG_B200_OK;
 }
 
-template <bool kTF32, bool kSplit, int BN, typename OutT>
+template <int kCta, bool kTF32, bool kSplit, int BN, typename OutT>
 static int launch_variant(const CUtensorMap& ta, const CUtensorMap& ta_lo, const CUtensorMap& tb,
                           const CUtensorMap& tb_lo, GemmParams& p, cudaStream_t s) {
-    using L = StageLayout<kSplit ? 2 : 1, BN>;
-    auto kern = gemm_sm100_kernel<kTF32, kSplit, BN, OutT>;
+    using L = StageLayout<kSplit ? 2 : 1, BN / kCta>;
+    auto kern = gemm_sm100_kernel<kCta, kTF32, kSplit, BN, OutT>;
     // the attribute is per device; setting it again is cheap
     CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynSmem));
     const int elem = kTF32 ? 4 : 2;
-    p.tiles_m = (int)((p.M + kBM - 1) / kBM);
+    p.tiles_m = (int)((p.M + kBM * kCta - 1) / (kBM * kCta));
     p.tiles_n = (int)((p.N + BN - 1) / BN);
     p.num_tiles = (long long)p.tiles_m * p.tiles_n * p.batch;
     p.num_kb = (int)((p.K + (kRowBytes / elem) - 1) / (kRowBytes / elem));
-    const long long sms = sm_count();
-    const int grid = (int)(p.num_tiles < sms ? p.num_tiles : sms);
-    kern<<<grid, kThreads, L::kDynSmem, s>>>(ta, ta_lo, tb, tb_lo, p);
-    CGB_CUDA(cudaGetLastError());
+    // persistent: one CTA (or CTA pair) per SM (or SM pair), never more CTAs than tiles
+    const long long slots = sm_count() / kCta;
+    const int groups = (int)(p.num_tiles < slots ? p.num_tiles : slots);
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)(groups * kCta), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = L::kDynSmem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kCta;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CGB_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, ta_lo, tb, tb_lo, p));
     return CG_B200_OK;
 }
 
-template <bool kTF32, bool kSplit, typename OutT>
+template <int kCta, bool kTF32, bool kSplit, typename OutT>
 static int launch_bn(int bn, const CUtensorMap& ta, const CUtensorMap& ta_lo, const CUtensorMap& tb,
                      const CUtensorMap& tb_lo, GemmParams& p, cudaStream_t s) {
-    if constexpr (kSplit) {
+    if constexpr (kCta == 2) {
+        (void)bn;   // the pair variant is built for the 256-wide tile only
+        return launch_variant<2, kTF32, kSplit, 256, OutT>(ta, ta_lo, tb, tb_lo, p, s);
+    } else if constexpr (kSplit) {
         (void)bn;
-        return launch_variant<kTF32, true, 128, OutT>(ta, ta_lo, tb, tb_lo, p, s);
+        return launch_variant<1, kTF32, true, 128, OutT>(ta, ta_lo, tb, tb_lo, p, s);
     } else {
-        if (bn == 64) return launch_variant<kTF32, false, 64, OutT>(ta, ta_lo, tb, tb_lo, p, s);
-        if (bn == 128) return launch_variant<kTF32, false, 128, OutT>(ta, ta_lo, tb, tb_lo, p, s);
-        return launch_variant<kTF32, false, 256, OutT>(ta, ta_lo, tb, tb_lo, p, s);
+        if (bn == 64) return launch_variant<1, kTF32, false, 64, OutT>(ta, ta_lo, tb, tb_lo, p, s);
+        if (bn == 128) return launch_variant<1, kTF32, false, 128, OutT>(ta, ta_lo, tb, tb_lo, p, s);
+        return launch_variant<1, kTF32, false, 256, OutT>(ta, ta_lo, tb, tb_lo, p, s);
     }
+}
+
+// CG_B200_GEMM_PAIR=0 in the environment turns the CTA-pair variant off (a test and tuning knob).
+static bool pair_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("CG_B200_GEMM_PAIR");
+        return !(e && e[0] == '0');
+    }();
+    return on;
 }
 
 static int choose_bn(const cg_b200_gemm_desc* d, bool split) {
@@ -637,7 +785,7 @@ extern "C" int cg_b200_gemm_workspace_bytes(const cg_b200_gemm_desc* desc, size_
     *bytes = 0;
     int st = validate_desc(desc);
     if (st) return st;
-    *bytes = plan_split(desc).bytes;
+    *bytes = plan_fp32(desc).bytes;
     return CG_B200_OK;
 }
 
@@ -647,7 +795,7 @@ extern "C" int cg_b200_gemm(const cg_b200_gemm_desc* desc, const void* A, const 
     if (st) return st;
     const cg_b200_gemm_desc& d = *desc;
     if (d.M == 0 || d.N == 0) return CG_B200_OK;
-    if (!A || !B || !C) return CG_B200_ERR_NULL_POINTER;
+    if (!C || (d.K > 0 && (!A || !B))) return CG_B200_ERR_NULL_POINTER;   // K == 0: A and B are empty
     const int epi = d.epilogue;
     const bool need_bias = epi == CG_B200_EPI_BIAS || epi == CG_B200_EPI_BIAS_RELU ||
                            epi == CG_B200_EPI_BIAS_GELU_TANH || epi == CG_B200_EPI_BIAS_RESIDUAL;
@@ -655,14 +803,14 @@ extern "C" int cg_b200_gemm(const cg_b200_gemm_desc* desc, const void* A, const 
     if (need_bias && !bias) return CG_B200_ERR_NULL_POINTER;
     if (need_res && !residual) return CG_B200_ERR_NULL_POINTER;
     const size_t in_sz = dtype_bytes(d.in_dtype), out_sz = dtype_bytes(d.out_dtype);
-    const SplitPlan sp = plan_split(desc);
+    const Fp32Plan sp = plan_fp32(desc);
     // C rows are written with 16-byte stores
     if (!aligned_to(C, 16) || (d.ldc * out_sz) % 16 || (d.batch_stride_c * out_sz) % 16) return CG_B200_ERR_MISALIGNED;
     if (need_res && !aligned_to(residual, 16)) return CG_B200_ERR_MISALIGNED;
     if (need_bias && !aligned_to(bias, out_sz)) return CG_B200_ERR_MISALIGNED;
-    if (!sp.split) {
+    if (!sp.active) {
         // TMA reads A and B in place: 16-byte aligned bases and strides
-        if (!aligned_to(A, 16) || !aligned_to(B, 16)) return CG_B200_ERR_MISALIGNED;
+        if (d.K > 0 && (!aligned_to(A, 16) || !aligned_to(B, 16))) return CG_B200_ERR_MISALIGNED;
         if ((d.lda * in_sz) % 16 || (d.ldb * in_sz) % 16) return CG_B200_ERR_MISALIGNED;
         if ((d.batch_stride_a * in_sz) % 16 || (d.batch_stride_b * in_sz) % 16) return CG_B200_ERR_MISALIGNED;
     } else {
@@ -680,38 +828,51 @@ extern "C" int cg_b200_gemm(const cg_b200_gemm_desc* desc, const void* A, const 
     p.ldc = d.ldc; p.batch_stride_c = d.batch_stride_c;
     p.bias = bias; p.residual = residual; p.C = C;
     p.epilogue = epi; p.alpha = d.alpha;
-    p.b_mn_major = d.b_transposed ? 0 : 1;
+    p.b_mn_major = (d.b_transposed || sp.active) ? 0 : 1;   // the fp32 workspace copy of B is K-contiguous
     p.a_batched = d.batch_stride_a != 0 && d.batch > 1;
     p.b_batched = d.batch_stride_b != 0 && d.batch > 1;
     p.err_word = device_error_word();
 
     const bool tf32 = d.in_dtype == CG_B200_F32;
-    const int bn = choose_bn(desc, sp.split);
-    p.idesc = make_idesc(d.in_dtype, tf32, p.b_mn_major != 0, bn);
+    const int bn = choose_bn(desc, sp.active && sp.copies == 2);
+    // CTA pairs (256 x 256 tiles) for 16-bit inputs once the problem spans more than one such tile row
+    const int cta = (!tf32 && bn == 256 && d.M > kBM && pair_enabled()) ? 2 : 1;
+    p.idesc = make_idesc(d.in_dtype, tf32, p.b_mn_major != 0, kBM * cta, bn);
     const uint32_t box_k = (uint32_t)(kRowBytes / in_sz);
 
-    const void* a_hi = A;
-    const void* a_lo = A;
-    const void* b_hi = B;
-    const void* b_lo = B;
+    // with K == 0 no load is ever issued; the maps only need an encodable base address
+    const void* a_hi = d.K > 0 ? A : C;
+    const void* a_lo = a_hi;
+    const void* b_hi = d.K > 0 ? B : C;
+    const void* b_lo = b_hi;
     long long lda = d.lda, ldb = d.ldb, bsa = d.batch_stride_a, bsb = d.batch_stride_b;
-    const long long b_rows = d.b_transposed ? d.N : d.K, b_cols = d.b_transposed ? d.K : d.N;
-    if (sp.split) {
+    long long b_rows = d.b_transposed ? d.N : d.K;
+    if (sp.active) {
         float* w = static_cast<float*>(workspace);
         float* wa_hi = w;
-        float* wa_lo = w + sp.a_elems;
-        float* wb_hi = w + 2 * sp.a_elems;
-        float* wb_lo = wb_hi + sp.b_elems;
+        float* wa_lo = sp.copies == 2 ? w + sp.a_elems : nullptr;
+        float* wb_hi = w + sp.copies * sp.a_elems;
+        float* wb_lo = sp.copies == 2 ? wb_hi + sp.b_elems : nullptr;
         const long long a_batches = p.a_batched ? d.batch : 1, b_batches = p.b_batched ? d.batch : 1;
         const int blocks = sm_count() * 8;
-        tf32_split_kernel<<<blocks, 256, 0, s>>>(static_cast<const float*>(A), wa_hi, wa_lo, d.M, d.K, d.lda, sp.lda_w,
-                                                 a_batches, d.batch_stride_a, d.M * sp.lda_w);
-        tf32_split_kernel<<<blocks, 256, 0, s>>>(static_cast<const float*>(B), wb_hi, wb_lo, b_rows, b_cols, d.ldb,
-                                                 sp.ldb_w, b_batches, d.batch_stride_b, b_rows * sp.ldb_w);
-        CGB_CUDA(cudaGetLastError());
-        a_hi = wa_hi; a_lo = wa_lo; b_hi = wb_hi; b_lo = wb_lo;
-        lda = sp.lda_w; ldb = sp.ldb_w;
-        bsa = d.M * sp.lda_w; bsb = b_rows * sp.ldb_w;
+        if (d.K > 0) {
+            tf32_split_kernel<<<blocks, 256, 0, s>>>(static_cast<const float*>(A), wa_hi, wa_lo, d.M, d.K, d.lda,
+                                                     sp.ldk, a_batches, d.batch_stride_a, d.M * sp.ldk);
+            if (d.b_transposed) {
+                tf32_split_kernel<<<blocks, 256, 0, s>>>(static_cast<const float*>(B), wb_hi, wb_lo, d.N, d.K, d.ldb,
+                                                         sp.ldk, b_batches, d.batch_stride_b, d.N * sp.ldk);
+            } else {
+                dim3 grid((unsigned)((d.N + 31) / 32), (unsigned)((sp.ldk + 31) / 32), (unsigned)b_batches);
+                tf32_split_transpose_kernel<<<grid, dim3(32, 8), 0, s>>>(static_cast<const float*>(B), wb_hi, wb_lo,
+                                                                         d.K, d.N, d.ldb, sp.ldk, d.batch_stride_b,
+                                                                         d.N * sp.ldk);
+            }
+            CGB_CUDA(cudaGetLastError());
+        }
+        a_hi = wa_hi; a_lo = wa_lo ? wa_lo : wa_hi; b_hi = wb_hi; b_lo = wb_lo ? wb_lo : wb_hi;
+        lda = sp.ldk; ldb = sp.ldk;
+        bsa = d.M * sp.ldk; bsb = d.N * sp.ldk;
+        b_rows = d.N;
     }
     const uint64_t a_nb = p.a_batched ? (uint64_t)d.batch : 1, b_nb = p.b_batched ? (uint64_t)d.batch : 1;
     // a batch stride of 0 cannot be encoded; with one batch slice the value is never used
@@ -730,19 +891,26 @@ extern "C" int cg_b200_gemm(const cg_b200_gemm_desc* desc, const void* A, const 
         if (st) return st;
         st = make_map(&tb_lo, b_lo, d.in_dtype, d.N, k_dim, b_nb, ldb, bsb_enc, box_k, box_k);
     } else {
-        st = make_map(&tb, b_hi, d.in_dtype, k_dim, d.N, b_nb, ldb, bsb_enc, box_k, (uint32_t)bn);
+        st = make_map(&tb, b_hi, d.in_dtype, k_dim, d.N, b_nb, ldb, bsb_enc, box_k, (uint32_t)(bn / cta));
         if (st) return st;
-        st = make_map(&tb_lo, b_lo, d.in_dtype, k_dim, d.N, b_nb, ldb, bsb_enc, box_k, (uint32_t)bn);
+        st = make_map(&tb_lo, b_lo, d.in_dtype, k_dim, d.N, b_nb, ldb, bsb_enc, box_k, (uint32_t)(bn / cta));
     }
     if (st) return st;
 
     if (tf32) {
-        if (sp.split) return launch_bn<true, true, float>(bn, ta, ta_lo, tb, tb_lo, p, s);
-        return launch_bn<true, false, float>(bn, ta, ta_lo, tb, tb_lo, p, s);
+        if (sp.copies == 2) return launch_bn<1, true, true, float>(bn, ta, ta_lo, tb, tb_lo, p, s);
+        return launch_bn<1, true, false, float>(bn, ta, ta_lo, tb, tb_lo, p, s);
+    }
+    if (cta == 2) {
+        switch (d.out_dtype) {
+            case CG_B200_BF16: return launch_bn<2, false, false, __nv_bfloat16>(bn, ta, ta_lo, tb, tb_lo, p, s);
+            case CG_B200_F16: return launch_bn<2, false, false, __half>(bn, ta, ta_lo, tb, tb_lo, p, s);
+            default: return launch_bn<2, false, false, float>(bn, ta, ta_lo, tb, tb_lo, p, s);
+        }
     }
     switch (d.out_dtype) {
-        case CG_B200_BF16: return launch_bn<false, false, __nv_bfloat16>(bn, ta, ta_lo, tb, tb_lo, p, s);
-        case CG_B200_F16: return launch_bn<false, false, __half>(bn, ta, ta_lo, tb, tb_lo, p, s);
-        default: return launch_bn<false, false, float>(bn, ta, ta_lo, tb, tb_lo, p, s);
+        case CG_B200_BF16: return launch_bn<1, false, false, __nv_bfloat16>(bn, ta, ta_lo, tb, tb_lo, p, s);
+        case CG_B200_F16: return launch_bn<1, false, false, __half>(bn, ta, ta_lo, tb, tb_lo, p, s);
+        default: return launch_bn<1, false, false, float>(bn, ta, ta_lo, tb, tb_lo, p, s);
     }
 }

@@ -29,7 +29,7 @@ def _host_f32(O, t, dtype):
 
 
 def run_case(ops, cgb, O, M, N, K, in_dt, out_dt, epilogue="none", batch=1, b_transposed=0, bsb=None,
-             compute="default", scale=0.05, seed=0, alpha=1.0, rows=None, pad=0):
+             compute="default", scale=0.05, seed=0, alpha=1.0, rows=None, pad=0, return_operands=False):
     """Returns (gpu fp32 [batch*M, N], oracle fp32 [batch*M, N] (only `rows` valid when given))."""
     import torch
     capi = cgb.capi
@@ -52,7 +52,7 @@ def run_case(ops, cgb, O, M, N, K, in_dt, out_dt, epilogue="none", batch=1, b_tr
     bs_, rs_ = O.to_storage(bias, out_dt), O.to_storage(res, out_dt)
     kw = dict(epilogue=epilogue, batch=batch, b_transposed=b_transposed, lda=lda, ldb=ldb, ldc=ldc, bsb=bsb, alpha=alpha)
     od = O.make_gemm_desc(M, N, K, in_dt, out_dt, **kw)
-    want = O.gemm(od, As, Bs, bias=bs_, residual=rs_, rows=rows)
+    want = O.gemm(od, As, Bs, bias=bs_, residual=rs_, rows=rows, out=np.zeros(batch * M * ldc, dtype=O.NP_OF[out_dt]))
     want = O.to_f32(want, out_dt).reshape(batch * M, ldc)[:, :N]
     gd = capi.make_gemm_desc(M, N, K, in_dt, out_dt, compute=compute, **kw)
     Ad, Bd = _dev(ops, As, in_dt), _dev(ops, Bs, in_dt)
@@ -60,7 +60,23 @@ def run_case(ops, cgb, O, M, N, K, in_dt, out_dt, epilogue="none", batch=1, b_tr
     ops.gemm(gd, Ad, Bd, Cd, bias=_dev(ops, bs_, out_dt), residual=_dev(ops, rs_, out_dt))
     assert ops.last_device_error() == 0, "a bounded device-side wait ran out"
     got = _host_f32(O, Cd, out_dt).reshape(batch * M, ldc)[:, :N]
+    if return_operands:
+        return got, want, A[:, :, :K], (B[:, :, :K].transpose(0, 2, 1) if b_transposed else B[:, :, :N])
     return got, want
+
+
+def assert_dot_close(got, want, A, B, tol, what):
+    """Error bound for raw dot products: max|y-ref| / max|ref| <= tol and, componentwise,
+    |y-ref|_ij <= tol * (|A| |B|)_ij. The second is the scale on which any floating-point
+    summation of sum_k a_ik b_kj can be compared (results near zero by cancellation have no
+    meaningful relative error of their own: the reference's own fp32 FMA chain is 1e-6 * (|A||B|)
+    away from the exact sum)."""
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    scale = np.abs(A[0].astype(np.float64)) @ np.abs(B[0].astype(np.float64))
+    norm = np.abs(got - want).max() / max(np.abs(want).max(), 1e-30)
+    comp = (np.abs(got - want) / np.maximum(scale, 1e-30)).max()
+    assert norm <= tol and comp <= tol, f"{what}: max-normalised {norm:.3e}, componentwise {comp:.3e}, tol {tol}"
 
 
 SHAPES = [(128, 256, 64), (128, 256, 256), (256, 512, 192), (128, 64, 64), (128, 128, 128),
@@ -96,9 +112,9 @@ def test_fp32_gemm_3xtf32(ops, cgb, oracle, M, N, K, b_transposed):
     """fp32 in/out: hi/lo TF32 split. Inputs ~U[-1,1) as in the 1024^3 configuration."""
     capi = cgb.capi
     pad = (-N) % 4  # C rows must be 16-byte multiples
-    got, want = run_case(ops, cgb, oracle, M, N, K, capi.F32, capi.F32, b_transposed=b_transposed, scale=0.5,
-                         seed=K, pad=pad)
-    assert_close(got, want, 1e-4, f"fp32 {M}x{N}x{K} bT={b_transposed}")
+    got, want, A, B = run_case(ops, cgb, oracle, M, N, K, capi.F32, capi.F32, b_transposed=b_transposed, scale=0.5,
+                               seed=K, pad=pad, return_operands=True)
+    assert_dot_close(got, want, A, B, 1e-4, f"fp32 {M}x{N}x{K} bT={b_transposed}")
 
 
 def test_fp32_gemm_matches_reference_golden(ops, cgb, oracle):
@@ -113,7 +129,7 @@ def test_fp32_gemm_matches_reference_golden(ops, cgb, oracle):
     Cd = torch.zeros(M, N, device="cuda")
     ops.gemm(gd, torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda(), Cd)
     assert ops.last_device_error() == 0
-    assert_close(Cd.cpu().numpy(), Cref, 1e-4, "golden mm_sq")
+    assert_dot_close(Cd.cpu().numpy(), Cref, A[None], B[None], 1e-4, "golden mm_sq")
 
 
 def test_batched_and_broadcast(ops, cgb, oracle):
