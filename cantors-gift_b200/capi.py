@@ -24,6 +24,7 @@ EPILOGUE = {"none": 0, "bias": 1, "bias_relu": 2, "bias_gelu_tanh": 3, "bias_res
             "residual": 5, "scale": 6}
 COMPUTE = {"default": 0, "tf32x3": 1, "tf32": 2}
 COMM_ID_BYTES = 128
+GEMM_F32_STATIC_SCRATCH_BYTES = 16 << 20
 
 
 class CgB200Error(RuntimeError):
@@ -94,6 +95,7 @@ SIGNATURES = {
     "cg_b200_gemm_workspace_bytes": (_i, [C.POINTER(GemmDesc), C.POINTER(_sz)]),
     "cg_b200_gemm": (_i, [C.POINTER(GemmDesc), _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "cg_b200_last_device_error": (_i, [_vp, C.POINTER(C.c_uint32)]),
+    "cg_b200_gemm_f32_static": (_i, [C.POINTER(GemmDesc), _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cg_b200_comm_unique_id": (_i, [_vp]),
     "cg_b200_comm_init_rank": (_i, [_vpp, _i, _i, _vp]),
     "cg_b200_allgather_inplace": (_i, [_vp, _vp, _sz, _vp]),

@@ -789,8 +789,12 @@ extern "C" int cg_b200_gemm_workspace_bytes(const cg_b200_gemm_desc* desc, size_
     return CG_B200_OK;
 }
 
-extern "C" int cg_b200_gemm(const cg_b200_gemm_desc* desc, const void* A, const void* B, const void* bias,
-                            const void* residual, void* C, void* workspace, size_t workspace_bytes, void* stream) {
+// Shared body of the GEMM entry points. `shared_err_word`: report bounded-wait timeouts through
+// the library's per-device error word (allocated on first use); otherwise through `err_word`
+// (may be null).
+static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B, const void* bias,
+                    const void* residual, void* C, void* workspace, size_t workspace_bytes, void* stream,
+                    bool shared_err_word, uint32_t* err_word) {
     int st = validate_desc(desc);
     if (st) return st;
     const cg_b200_gemm_desc& d = *desc;
@@ -831,7 +835,7 @@ extern "C" int cg_b200_gemm(const cg_b200_gemm_desc* desc, const void* A, const 
     p.b_mn_major = (d.b_transposed || sp.active) ? 0 : 1;   // the fp32 workspace copy of B is K-contiguous
     p.a_batched = d.batch_stride_a != 0 && d.batch > 1;
     p.b_batched = d.batch_stride_b != 0 && d.batch > 1;
-    p.err_word = device_error_word();
+    p.err_word = shared_err_word ? device_error_word() : err_word;
 
     const bool tf32 = d.in_dtype == CG_B200_F32;
     const int bn = choose_bn(desc, sp.active && sp.copies == 2);
@@ -913,4 +917,56 @@ extern "C" int cg_b200_gemm(const cg_b200_gemm_desc* desc, const void* A, const 
         case CG_B200_F16: return launch_bn<1, false, false, __half>(bn, ta, ta_lo, tb, tb_lo, p, s);
         default: return launch_bn<1, false, false, float>(bn, ta, ta_lo, tb, tb_lo, p, s);
     }
+}
+
+extern "C" int cg_b200_gemm(const cg_b200_gemm_desc* desc, const void* A, const void* B, const void* bias,
+                            const void* residual, void* C, void* workspace, size_t workspace_bytes, void* stream) {
+    return gemm_run(desc, A, B, bias, residual, C, workspace, workspace_bytes, stream, true, nullptr);
+}
+
+// ---- fp32 GEMM for callers that cannot allocate -----------------------------------------------------
+// The scratch of the fp32 path (the tf32 hi/lo copies of A and B) lives in this file-scope device
+// array instead of a caller-provided workspace. Every device that loads the library holds these
+// bytes until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[CG_B200_GEMM_F32_STATIC_SCRATCH_BYTES];
+
+// Device address of g_static_scratch per device. In host code the array's name is only a handle
+// for the runtime, never a pointer a kernel could use; cudaGetSymbolAddress turns it into one, for
+// the device that is current at the time of the call.
+static void* g_static_scratch_addr[64];
+static std::mutex g_static_scratch_mu;
+
+static int static_scratch_for_current_device(void** out) {
+    int dev = -1;
+    CGB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return CG_B200_ERR_INVALID_ARG;
+    std::lock_guard<std::mutex> lk(g_static_scratch_mu);
+    if (!g_static_scratch_addr[dev]) {
+        void* ptr = nullptr;
+        CGB_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+        g_static_scratch_addr[dev] = ptr;
+    }
+    *out = g_static_scratch_addr[dev];
+    return CG_B200_OK;
+}
+
+extern "C" int cg_b200_gemm_f32_static(const cg_b200_gemm_desc* desc, const void* A, const void* B,
+                                       const void* bias, const void* residual, void* C,
+                                       uint32_t* dev_error_word, void* stream) {
+    int st = validate_desc(desc);
+    if (st) return st;
+    if (desc->in_dtype != CG_B200_F32) return CG_B200_ERR_UNSUPPORTED;   // only the fp32 path needs scratch
+    const Fp32Plan plan = plan_fp32(desc);
+    if (plan.bytes > (size_t)CG_B200_GEMM_F32_STATIC_SCRATCH_BYTES) return CG_B200_ERR_WORKSPACE;
+    if (dev_error_word && !aligned_to(dev_error_word, 4)) return CG_B200_ERR_MISALIGNED;
+    if (desc->M == 0 || desc->N == 0) return CG_B200_OK;
+    st = require_sm100();
+    if (st) return st;
+    void* scratch = nullptr;
+    st = static_scratch_for_current_device(&scratch);
+    if (st) return st;
+    // The split pre-pass rewrites every scratch byte the GEMM reads (pad columns included), so
+    // nothing left over from an earlier call can leak into this one.
+    return gemm_run(desc, A, B, bias, residual, C, scratch, (size_t)CG_B200_GEMM_F32_STATIC_SCRATCH_BYTES, stream,
+                    false, dev_error_word);
 }

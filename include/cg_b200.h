@@ -241,6 +241,29 @@ int cg_b200_gemm(const cg_b200_gemm_desc* desc, const void* A, const void* B,
  * (0 = none). Synchronises `stream`. */
 int cg_b200_last_device_error(void* stream, uint32_t* word);
 
+/* fp32 GEMM for callers that cannot allocate device memory (no counterpart in the reference).
+ * Who that is: code that runs where an allocation is not allowed or not possible - a launch
+ * routine that is handed only tensors and a stream (the shape of BoundExecutable::launch,
+ * include/cg/runtime/runtime.hpp:84-88, which carries no allocator), a service whose device
+ * memory was given out in full to its own pools at start-up, or a latency-critical loop that
+ * must not hit the implicit device synchronisation of cudaMalloc/cudaFree. cg_b200_gemm needs
+ * a caller-provided workspace for fp32 inputs; this entry point instead keeps that scratch in a
+ * fixed array of CG_B200_GEMM_F32_STATIC_SCRATCH_BYTES inside the library, held by every GPU
+ * that loads the library until the process exits. It calls no allocating routine.
+ *  - in_dtype must be fp32 (other types need no scratch: use cg_b200_gemm); problems whose
+ *    workspace (cg_b200_gemm_workspace_bytes) exceeds the array return CG_B200_ERR_WORKSPACE.
+ *  - dev_error_word: optional caller-owned device uint32 (zeroed by the caller) that receives a
+ *    non-zero code if a bounded device-side wait runs out; may be NULL.
+ *  - The first call on each device resolves the array's device address (set-up work); make it
+ *    before any stream capture starts on that device.
+ *  - All calls on a device share the one array: two calls whose kernels can overlap on the GPU
+ *    (different streams without ordering) race on it. Calls on one stream are safe. The array
+ *    keeps the previous call's bytes; each call overwrites everything it later reads. */
+#define CG_B200_GEMM_F32_STATIC_SCRATCH_BYTES (16u << 20)
+int cg_b200_gemm_f32_static(const cg_b200_gemm_desc* desc, const void* A, const void* B,
+                            const void* bias, const void* residual, void* C,
+                            uint32_t* dev_error_word, void* stream);
+
 /* ---- final all-gather for M- / batch-sharded outputs ------------------------------
  * The reference has no collective (its only parallel runtime is the std::thread fan-out
  * in include/cg/backend/parallel_executor.hpp:49-92). One communicator per process,
