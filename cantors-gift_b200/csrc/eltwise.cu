@@ -7,8 +7,7 @@
 // (benchmarks/benchmark_multithread.py:54-124): separately rounded mul / add / max.
 //
 // HBM-bound: algorithmic bytes per element = (number of full-size inputs + 1) * sizeof(T).
-// Layout: every operand is a flat row-major array; a thread owns 16-byte packets at a grid
-// stride, two packets per loop trip for memory-level parallelism.
+// Layout: every operand is a flat row-major array; a thread owns one 16-byte packet per operand.
 //
 // The chain is a postfix program. Two evaluators share one code path:
 //   - compile-time programs (a table of common chains): the evaluation loop unrolls and the
@@ -208,30 +207,18 @@ __device__ __forceinline__ void eval_lanes(const EltParams& p, const Prog& prog,
     for (int l = 0; l < L; ++l) res[l] = s0[l];
 }
 
-// Packets at a grid stride; the ragged tail (n % L elements) is done scalar by block 0.
+// One 16-byte packet per thread per trip; the ragged tail (n % L elements) is done scalar by
+// block 0. The grid normally covers the whole array (see launch_typed), so most threads make one
+// trip: with the registers of a single packet the kernel runs at full occupancy, which measured
+// faster on B200 than two packets per thread at half occupancy.
 template <typename T, typename Prog>
-__global__ void __launch_bounds__(256) eltwise_vec_kernel(const __grid_constant__ EltParams p) {
+__global__ void __launch_bounds__(256, 8) eltwise_vec_kernel(const __grid_constant__ EltParams p) {
     constexpr int L = 16 / sizeof(T);
     const Prog prog(p);
     T* out = static_cast<T*>(p.out);
     const unsigned long long n_pkt = p.n / L;
     const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
-    unsigned long long v = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
-    // two packets per trip
-    for (; v + stride < n_pkt; v += 2 * stride) {
-        float r0[L], r1[L];
-        eval_lanes<T, L, true>(p, prog, v * L, r0);
-        eval_lanes<T, L, true>(p, prog, (v + stride) * L, r1);
-        Vec16<T> o0, o1;
-#pragma unroll
-        for (int l = 0; l < L; ++l) {
-            o0.v[l] = Elem<T>::from_f32(r0[l]);
-            o1.v[l] = Elem<T>::from_f32(r1[l]);
-        }
-        st_stream(out + v * L, o0);
-        st_stream(out + (v + stride) * L, o1);
-    }
-    if (v < n_pkt) {
+    for (unsigned long long v = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; v < n_pkt; v += stride) {
         float r0[L];
         eval_lanes<T, L, true>(p, prog, v * L, r0);
         Vec16<T> o0;
@@ -320,12 +307,12 @@ static int launch_typed(const EltParams& p, bool vector_ok, cudaStream_t s) {
         return CG_B200_OK;
     }
     constexpr int L = 16 / sizeof(T);
-    // One thread per two packets. Measured on B200: for this streaming pattern a grid that covers
-    // the whole array (tens of thousands of short-lived CTAs) sustains about 10 % more HBM
-    // bandwidth than a persistent grid of 8 CTAs per SM; the grid-stride loop only matters when
-    // the array exceeds the grid limit.
+    // One thread per packet. Measured on B200: for this streaming pattern a grid that covers the
+    // whole array (tens of thousands of short-lived CTAs) sustains about 10 % more HBM bandwidth
+    // than a persistent grid of 8 CTAs per SM; the grid-stride loop only matters when the array
+    // exceeds the grid limit.
     (void)sms;
-    unsigned long long want = (p.n / L + 2 * 256 - 1) / (2 * 256);
+    unsigned long long want = (p.n / L + 255) / 256;
     const unsigned long long cap = 0x7fffffffull;
     int blocks = (int)(want < cap ? (want == 0 ? 1 : want) : cap);
     if (matches<ProgMulAddReluScale>(p)) launch_vec<T, ProgMulAddReluScale>(p, blocks, s);

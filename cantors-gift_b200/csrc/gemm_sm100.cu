@@ -42,8 +42,8 @@ constexpr int kBM = 128;            // rows per tile = TMEM lanes
 constexpr int kRowBytes = 128;      // bytes of K per row per stage (one swizzle span)
 constexpr int kUmmaKBytes = 32;     // bytes of K one tcgen05.mma consumes per row
 constexpr int kThreads = 192;
-constexpr int kMaxStages = 6;
-constexpr int kSmemBudget = 200 * 1024;
+constexpr int kMaxStages = 8;
+constexpr int kSmemBudget = 224 * 1024;
 constexpr uint32_t kTmemCols = 512;
 
 struct GemmParams {

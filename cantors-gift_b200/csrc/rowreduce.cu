@@ -172,6 +172,233 @@ __global__ void __launch_bounds__(THREADS) row_reg_kernel(const __grid_constant_
     }
 }
 
+// ---- fused layernorm(softmax(x)), register path, packed arithmetic ---------------------------------
+// This kernel is issue-bound before it is HBM-bound (the first version spent 23 instructions per
+// element), so its inner loops work on pairs: fp32x2 add / mul / fma (one issue slot for two
+// elements on sm_100), bf16x2 / f16x2 max on the raw input words, two-element pack/unpack.
+// The layernorm statistics are taken about c = 1/cols, the mean a softmax row has before rounding:
+// sum(p - c) and sum((p - c)^2) come out of ONE block reduction, and with the shift the one-pass
+// variance has no cancellation (the correction term (mean - c)^2 is rounding noise).
+struct Sum2Op {
+    __device__ static float2 apply(float2 a, float2 b) { return __fadd2_rn(a, b); }
+};
+
+template <int THREADS>
+__device__ __forceinline__ float2 block_reduce_sum2(float2 v, float2* scratch, int& phase) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float2 t;
+        t.x = __shfl_xor_sync(0xffffffffu, v.x, o);
+        t.y = __shfl_xor_sync(0xffffffffu, v.y, o);
+        v = __fadd2_rn(v, t);
+    }
+    if constexpr (THREADS == 32) {
+        return v;
+    } else {
+        constexpr int W = THREADS / 32;
+        float2* sc = scratch + (phase & 1) * 32;
+        phase ^= 1;
+        if ((threadIdx.x & 31) == 0) sc[threadIdx.x >> 5] = v;
+        __syncthreads();
+        float2 r = sc[threadIdx.x & (W - 1)];      // every lane reads one of the W partials
+#pragma unroll
+        for (int o = W / 2; o > 0; o >>= 1) {       // butterfly over W lanes: all lanes end with the total
+            float2 t;
+            t.x = __shfl_xor_sync(0xffffffffu, r.x, o);
+            t.y = __shfl_xor_sync(0xffffffffu, r.y, o);
+            r = __fadd2_rn(r, t);
+        }
+        return r;
+    }
+}
+
+template <typename Op, int THREADS>
+__device__ __forceinline__ float block_reduce_fast(float v, float* scratch, int& phase) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = Op::apply(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if constexpr (THREADS == 32) {
+        return v;
+    } else {
+        constexpr int W = THREADS / 32;
+        float* sc = scratch + (phase & 1) * 32;
+        phase ^= 1;
+        if ((threadIdx.x & 31) == 0) sc[threadIdx.x >> 5] = v;
+        __syncthreads();
+        float r = sc[threadIdx.x & (W - 1)];
+#pragma unroll
+        for (int o = W / 2; o > 0; o >>= 1) r = Op::apply(r, __shfl_xor_sync(0xffffffffu, r, o));
+        return r;
+    }
+}
+
+// packet -> L/2 fp32 pairs
+template <typename T>
+__device__ __forceinline__ void unpack_pairs(const Vec16<T>& v, float2 (&f)[Vec16<T>::N / 2]) {
+    if constexpr (sizeof(T) == 4) {
+        f[0] = make_float2(v.v[0], v.v[1]);
+        f[1] = make_float2(v.v[2], v.v[3]);
+    } else if constexpr (Elem<T>::dtype == CG_B200_BF16) {
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+        for (int l = 0; l < 4; ++l) f[l] = make_float2(__uint_as_float(w[l] << 16), __uint_as_float(w[l] & 0xffff0000u));
+    } else {
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int l = 0; l < 4; ++l) f[l] = __half22float2(h[l]);
+    }
+}
+
+// fp32 pair -> rounded to T and back
+template <typename T>
+__device__ __forceinline__ float2 round_pair(float2 a) {
+    if constexpr (sizeof(T) == 4) {
+        return a;
+    } else if constexpr (Elem<T>::dtype == CG_B200_BF16) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(a.x, a.y);
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(&h);
+        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+    } else {
+        return __half22float2(__floats2half2_rn(a.x, a.y));
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ Vec16<T> pack_pairs(const float2 (&f)[Vec16<T>::N / 2]) {
+    Vec16<T> v;
+    if constexpr (sizeof(T) == 4) {
+        v.v[0] = f[0].x; v.v[1] = f[0].y; v.v[2] = f[1].x; v.v[3] = f[1].y;
+    } else if constexpr (Elem<T>::dtype == CG_B200_BF16) {
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int l = 0; l < 4; ++l) h[l] = __floats2bfloat162_rn(f[l].x, f[l].y);
+    } else {
+        __half2* h = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+        for (int l = 0; l < 4; ++l) h[l] = __floats2half2_rn(f[l].x, f[l].y);
+    }
+    return v;
+}
+
+// max over the 16 bytes of a packet, on the packed words where the type allows it
+template <typename T>
+__device__ __forceinline__ float packet_max(const Vec16<T>& v) {
+    if constexpr (sizeof(T) == 4) {
+        return fmaxf(fmaxf(v.v[0], v.v[1]), fmaxf(v.v[2], v.v[3]));
+    } else if constexpr (Elem<T>::dtype == CG_B200_BF16) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+        const __nv_bfloat162 m = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
+        return fmaxf(__bfloat162float(m.x), __bfloat162float(m.y));
+    } else {
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
+        const __half2 m = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
+        return fmaxf(__half2float(m.x), __half2float(m.y));
+    }
+}
+
+template <typename T, int THREADS, int CHUNKS, int MIN_CTAS>
+__global__ void __launch_bounds__(THREADS, MIN_CTAS) softmax_layernorm_reg_kernel(const __grid_constant__ RowParams p) {
+    constexpr int L = 16 / sizeof(T);
+    constexpr int P = L / 2;   // pairs per packet
+    __shared__ float scratch[64];
+    __shared__ float2 scratch2[64];
+    int phase = 0, phase2 = 0;
+    const long long n_pkt = p.cols / L;
+    const float inv_cols = 1.0f / (float)p.cols;
+    const float2 log2e2 = make_float2(kLog2e, kLog2e);
+    const float2 neg_c2 = make_float2(-inv_cols, -inv_cols);
+    const T* gamma = static_cast<const T*>(p.gamma);
+    const T* beta = static_cast<const T*>(p.beta);
+
+    // Persistent over rows with a one-row software prefetch: as soon as a packet has been unpacked
+    // to fp32 its registers receive the same packet of the CTA's next row, so HBM requests stay in
+    // flight through the two later reductions and the store (without it the memory pipe idles
+    // while the CTA computes).
+    bool live[CHUNKS];
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) live[j] = (long long)j * THREADS + threadIdx.x < n_pkt;
+    Vec16<T> raw[CHUNKS];
+    long long row = blockIdx.x;
+    if (row < p.rows) {
+        const T* in0 = static_cast<const T*>(p.in) + row * p.cols;
+#pragma unroll
+        for (int j = 0; j < CHUNKS; ++j)
+            if (live[j]) raw[j] = ld_stream(in0 + ((long long)j * THREADS + threadIdx.x) * L);
+    }
+    for (; row < p.rows; row += gridDim.x) {
+        T* out = static_cast<T*>(p.out) + row * p.cols;
+        float m = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < CHUNKS; ++j)
+            if (live[j]) m = fmaxf(m, packet_max<T>(raw[j]));
+        m = block_reduce_fast<MaxOp, THREADS>(m, scratch, phase);
+
+        const float nm = -m * kLog2e;
+        const float2 neg_m2 = make_float2(nm, nm);
+        const long long row_next = row + gridDim.x;
+        const T* in_next = static_cast<const T*>(p.in) + row_next * p.cols;
+        float2 x[CHUNKS][P];
+        float2 s2 = make_float2(0.0f, 0.0f);
+#pragma unroll
+        for (int j = 0; j < CHUNKS; ++j)
+            if (live[j]) {
+                unpack_pairs<T>(raw[j], x[j]);
+                // the packed copy is dead now: its registers take the next row's packet
+                if (row_next < p.rows) raw[j] = ld_stream(in_next + ((long long)j * THREADS + threadIdx.x) * L);
+#pragma unroll
+                for (int l = 0; l < P; ++l) {
+                    const float2 t = __ffma2_rn(x[j][l], log2e2, neg_m2);
+                    x[j][l] = make_float2(ex2_approx(t.x), ex2_approx(t.y));
+                    s2 = __fadd2_rn(s2, x[j][l]);
+                }
+            }
+        const float ssum = block_reduce_fast<SumOp, THREADS>(s2.x + s2.y, scratch, phase);
+        const float inv = 1.0f / ssum;
+        const float2 inv2 = make_float2(inv, inv);
+
+        // p = e / sum rounded to the storage type; d = p - c; one reduction for sum(d), sum(d^2)
+        float2 sd = make_float2(0.0f, 0.0f), sq = make_float2(0.0f, 0.0f);
+#pragma unroll
+        for (int j = 0; j < CHUNKS; ++j)
+            if (live[j]) {
+#pragma unroll
+                for (int l = 0; l < P; ++l) {
+                    const float2 pr = round_pair<T>(__fmul2_rn(x[j][l], inv2));
+                    const float2 d = __fadd2_rn(pr, neg_c2);
+                    x[j][l] = d;
+                    sd = __fadd2_rn(sd, d);
+                    sq = __ffma2_rn(d, d, sq);
+                }
+            }
+        const float2 tot = block_reduce_sum2<THREADS>(make_float2(sd.x + sd.y, sq.x + sq.y), scratch2, phase2);
+        const float dm = tot.x * inv_cols;                       // mean - c
+        const float var = fmaxf(tot.y * inv_cols - dm * dm, 0.0f);
+        const float rstd = rsqrtf(var + p.eps);
+        const float2 rstd2 = make_float2(rstd, rstd);
+        const float sh = -dm * rstd;
+        const float2 shift2 = make_float2(sh, sh);
+#pragma unroll
+        for (int j = 0; j < CHUNKS; ++j)
+            if (live[j]) {
+                const long long pk = (long long)j * THREADS + threadIdx.x;
+#pragma unroll
+                for (int l = 0; l < P; ++l) x[j][l] = __ffma2_rn(x[j][l], rstd2, shift2);
+                if (gamma) {
+                    float2 g[P];
+                    unpack_pairs<T>(ld_keep(gamma + pk * L), g);
+#pragma unroll
+                    for (int l = 0; l < P; ++l) x[j][l] = __fmul2_rn(x[j][l], g[l]);
+                }
+                if (beta) {
+                    float2 b[P];
+                    unpack_pairs<T>(ld_keep(beta + pk * L), b);
+#pragma unroll
+                    for (int l = 0; l < P; ++l) x[j][l] = __fadd2_rn(x[j][l], b[l]);
+                }
+                st_stream(out + pk * L, pack_pairs<T>(x[j]));
+            }
+    }
+}
+
 // Streaming path: any cols, element-aligned. One CTA per row, several passes over the row.
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256) row_stream_kernel(const __grid_constant__ RowParams p) {
@@ -229,7 +456,17 @@ __global__ void __launch_bounds__(256) row_stream_kernel(const __grid_constant__
 
 template <typename T, int THREADS, int CHUNKS, int MODE>
 static void launch_reg(const RowParams& p, int blocks, cudaStream_t s) {
-    row_reg_kernel<T, THREADS, CHUNKS, MODE><<<blocks, THREADS, 0, s>>>(p);
+    if constexpr (MODE == kSoftmaxLayerNorm)
+        {
+        // persistent: the prefetching loop wants several rows per CTA
+        constexpr int kMinCtas = 640 / THREADS > 0 ? 640 / THREADS : 1;
+        const long long cap = (long long)sm_count() * kMinCtas;
+        const int g = (int)(p.rows < cap ? p.rows : cap);
+        (void)blocks;
+        softmax_layernorm_reg_kernel<T, THREADS, CHUNKS, kMinCtas><<<g, THREADS, 0, s>>>(p);
+    }
+    else
+        row_reg_kernel<T, THREADS, CHUNKS, MODE><<<blocks, THREADS, 0, s>>>(p);
 }
 
 template <typename T, int MODE>
