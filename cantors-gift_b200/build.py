@@ -65,5 +65,37 @@ def build_library(force=False, verbose=False):
     return LIB
 
 
+HOST = os.path.join(HERE, "host")
+HOST_LIB = os.path.join(LIB_DIR, "libcg_b200_host.so")
+HOST_TESTS = os.path.join(LIB_DIR, "host_tests")
+
+
+def build_host(force=False):
+    """Builds the C++ host layer (libcg_b200_host.so) and its test executable (lib/host_tests,
+    which also links the CPU oracle as its checker). Needs libcg_b200.so and oracle/libcg_oracle.so."""
+    cxx = os.environ.get("CXX", "g++")
+    srcs = sorted(os.path.join(HOST, "src", f) for f in os.listdir(os.path.join(HOST, "src")) if f.endswith(".cpp"))
+    hdr = os.path.join(HOST, "include", "cg", "b200_host.hpp")
+    newest = max([os.path.getmtime(p) for p in srcs + [hdr, os.path.join(ROOT, "include", "cg_b200.h")]])
+    common = ["-std=c++20", "-O2", "-Wall", "-Wextra", "-I" + os.path.join(HOST, "include"), "-I" + os.path.join(ROOT, "include")]
+    if force or not os.path.exists(HOST_LIB) or os.path.getmtime(HOST_LIB) < newest:
+        cmd = [cxx] + common + ["-fPIC", "-shared", "-o", HOST_LIB] + srcs + ["-L" + LIB_DIR, "-lcg_b200", "-Wl,-rpath,$ORIGIN"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"host library build failed:\n{r.stdout}\n{r.stderr}")
+    test_src = os.path.join(HOST, "tests", "host_tests.cpp")
+    oracle_dir = os.path.join(ROOT, "oracle")
+    if os.path.exists(os.path.join(oracle_dir, "libcg_oracle.so")) and (
+            force or not os.path.exists(HOST_TESTS) or os.path.getmtime(HOST_TESTS) < max(newest, os.path.getmtime(test_src))
+            or os.path.getmtime(HOST_TESTS) < os.path.getmtime(HOST_LIB)):
+        cmd = [cxx] + common + ["-ffp-contract=off", "-o", HOST_TESTS, test_src, "-L" + LIB_DIR, "-lcg_b200_host", "-lcg_b200",
+                                "-L" + oracle_dir, "-lcg_oracle", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,$ORIGIN/../../oracle"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"host tests build failed:\n{r.stdout}\n{r.stderr}")
+    return HOST_LIB
+
+
 if __name__ == "__main__":
     print(build_library(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_host(force="--force" in sys.argv))
