@@ -270,9 +270,10 @@ class GemmWorkload(Workload):
     def setup(self, rank, world):
         import torch
         from cantors_gift_b200 import capi
+        from cantors_gift_b200.sharding import padded_rows
         self.rank, self.world = rank, world
-        assert self.M % world == 0
-        self.Ms = self.M // world
+        self.Ms, padded = padded_rows(self.M, world)
+        assert padded == self.M, "the benchmark shapes divide evenly over 1/2/4/8 ranks"
         in_dt = getattr(capi, self.in_dtype_name)
         tdt = {"BF16": torch.bfloat16, "F32": torch.float32}[self.in_dtype_name]
         g = torch.Generator(device="cuda").manual_seed(2)          # same data on every rank

@@ -309,14 +309,14 @@ __global__ void __launch_bounds__(THREADS, MIN_CTAS) softmax_layernorm_reg_kerne
     const T* gamma = static_cast<const T*>(p.gamma);
     const T* beta = static_cast<const T*>(p.beta);
 
-    // Persistent over rows with a one-row software prefetch: as soon as a packet has been unpacked
-    // to fp32 its registers receive the same packet of the CTA's next row, so HBM requests stay in
-    // flight through the two later reductions and the store (without it the memory pipe idles
-    // while the CTA computes).
+    // Persistent over rows with a one-row software prefetch: the next row's packets are requested
+    // into their own registers before the current row's three dependent reductions, so the CTA
+    // always has HBM requests in flight (without it the memory pipe idles while the CTA computes;
+    // issuing the prefetch later, into the registers the unpack frees, measured far slower).
     bool live[CHUNKS];
 #pragma unroll
     for (int j = 0; j < CHUNKS; ++j) live[j] = (long long)j * THREADS + threadIdx.x < n_pkt;
-    Vec16<T> raw[CHUNKS];
+    Vec16<T> raw[CHUNKS], nxt[CHUNKS];
     long long row = blockIdx.x;
     if (row < p.rows) {
         const T* in0 = static_cast<const T*>(p.in) + row * p.cols;
@@ -326,6 +326,13 @@ __global__ void __launch_bounds__(THREADS, MIN_CTAS) softmax_layernorm_reg_kerne
     }
     for (; row < p.rows; row += gridDim.x) {
         T* out = static_cast<T*>(p.out) + row * p.cols;
+        const long long row_next = row + gridDim.x;
+        if (row_next < p.rows) {
+            const T* in_next = static_cast<const T*>(p.in) + row_next * p.cols;
+#pragma unroll
+            for (int j = 0; j < CHUNKS; ++j)
+                if (live[j]) nxt[j] = ld_stream(in_next + ((long long)j * THREADS + threadIdx.x) * L);
+        }
         float m = -INFINITY;
 #pragma unroll
         for (int j = 0; j < CHUNKS; ++j)
@@ -334,16 +341,12 @@ __global__ void __launch_bounds__(THREADS, MIN_CTAS) softmax_layernorm_reg_kerne
 
         const float nm = -m * kLog2e;
         const float2 neg_m2 = make_float2(nm, nm);
-        const long long row_next = row + gridDim.x;
-        const T* in_next = static_cast<const T*>(p.in) + row_next * p.cols;
         float2 x[CHUNKS][P];
         float2 s2 = make_float2(0.0f, 0.0f);
 #pragma unroll
         for (int j = 0; j < CHUNKS; ++j)
             if (live[j]) {
                 unpack_pairs<T>(raw[j], x[j]);
-                // the packed copy is dead now: its registers take the next row's packet
-                if (row_next < p.rows) raw[j] = ld_stream(in_next + ((long long)j * THREADS + threadIdx.x) * L);
 #pragma unroll
                 for (int l = 0; l < P; ++l) {
                     const float2 t = __ffma2_rn(x[j][l], log2e2, neg_m2);
@@ -396,6 +399,8 @@ __global__ void __launch_bounds__(THREADS, MIN_CTAS) softmax_layernorm_reg_kerne
                 }
                 st_stream(out + pk * L, pack_pairs<T>(x[j]));
             }
+#pragma unroll
+        for (int j = 0; j < CHUNKS; ++j) raw[j] = nxt[j];
     }
 }
 
@@ -459,8 +464,8 @@ static void launch_reg(const RowParams& p, int blocks, cudaStream_t s) {
     if constexpr (MODE == kSoftmaxLayerNorm)
         {
         // persistent: the prefetching loop wants several rows per CTA
-        constexpr int kMinCtas = 640 / THREADS > 0 ? 640 / THREADS : 1;
-        const long long cap = (long long)sm_count() * kMinCtas;
+        constexpr int kMinCtas = 512 / THREADS > 0 ? 512 / THREADS : 1;   // 4 CTAs of 128 threads: no spills
+        const long long cap = (long long)sm_count() * 8;
         const int g = (int)(p.rows < cap ? p.rows : cap);
         (void)blocks;
         softmax_layernorm_reg_kernel<T, THREADS, CHUNKS, kMinCtas><<<g, THREADS, 0, s>>>(p);
