@@ -416,16 +416,17 @@ def time_workload(w, steps, warmup, rank, world, sample_clocks):
     """Returns (seconds for `steps` steps, max over ranks; clocks dict)."""
     import torch
     import torch.distributed as dist
+    # the clock sampler starts first so that its start-up pause does not idle the GPU between the
+    # warm-up and the timed region
+    sampler = ClockSampler(torch.cuda.current_device()) if sample_clocks else None
+    if sampler:
+        sampler.start()
+        time.sleep(0.25)
     for i in range(warmup):
         w.step(i)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    sampler = ClockSampler(torch.cuda.current_device()) if sample_clocks else None
-    if sampler:
-        sampler.start()
-        time.sleep(0.25)
-    torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(steps):

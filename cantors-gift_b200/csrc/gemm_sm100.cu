@@ -60,6 +60,11 @@ struct GemmParams {
     long long num_tiles;
     int num_kb;
     uint32_t idesc;
+    // Tail balancing (CTA pairs only): work units [0, full_units) are whole tiles; the rest are
+    // half-width tiles (two per remaining tile), so that a last partial wave of r <= slots/2 tiles
+    // becomes 2r half-cost units spread over the machine. num_tiles counts units.
+    long long full_units;
+    uint32_t idesc_half;   // instruction descriptor with N = BN / 2
     uint32_t* err_word;
 };
 
@@ -93,14 +98,18 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 
 // Bounded wait. Returns false when the wait was abandoned: either this wait ran longer than
-// `limit_ns`, or another thread of the CTA already raised `*abort_flag`.
+// `limit_ns`, or another thread of the CTA already raised `*abort_flag`. `sleep_ns` > 0 makes a
+// thread that keeps missing back off with nanosleep: the four epilogue warps wait for a whole main
+// loop, and 128 threads spinning on try_wait for that long burn issue slots and power the tensor
+// pipe could use (the part is power-limited under a dense GEMM).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           uint32_t* err_word, uint32_t code,
-                                          unsigned long long limit_ns = 2000000000ull) {
+                                          unsigned long long limit_ns = 2000000000ull, uint32_t sleep_ns = 0) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (sleep_ns && it > 4) __nanosleep(sleep_ns);
         if ((it & 0xff) == 0) {
             if (*abort_flag) return false;
             if (global_ns() - t0 > limit_ns) {
@@ -244,14 +253,24 @@ __device__ __forceinline__ float gelu_epilogue(float x) {
 
 struct TileCoord {
     int b, m0, n0;
+    int width;   // columns of this unit: bn, or bn / 2 for a tail half
 };
-__device__ __forceinline__ TileCoord decode_tile(long long tile, const GemmParams& p, int bm, int bn) {
+__device__ __forceinline__ TileCoord decode_tile(long long unit, const GemmParams& p, int bm, int bn) {
     const long long per_batch = (long long)p.tiles_m * p.tiles_n;
+    long long tile = unit;
+    int n_off = 0;
     TileCoord t;
+    t.width = bn;
+    if (unit >= p.full_units) {
+        const long long h = unit - p.full_units;
+        tile = p.full_units + (h >> 1);
+        t.width = bn >> 1;
+        n_off = (int)(h & 1) * (bn >> 1);
+    }
     t.b = (int)(tile / per_batch);
     const int r = (int)(tile - (long long)t.b * per_batch);
     t.m0 = (r / p.tiles_n) * bm;
-    t.n0 = (r % p.tiles_n) * bn;
+    t.n0 = (r % p.tiles_n) * bn + n_off;
     return t;
 }
 
@@ -339,17 +358,21 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             bool ok = true;
             for (long long tile = tile_first; ok && tile < p.num_tiles; tile += tile_step) {
                 TileCoord t = decode_tile(tile, p, kTileM, BN);
+                const int bnl = t.width / kCta;   // B rows this CTA stages for this unit
+                const bool half = t.width != BN;
                 t.m0 += (int)cta_rank * kBM;      // this CTA's rows of A
-                t.n0 += (int)cta_rank * BNL;      // this CTA's part of B's N range
+                t.n0 += (int)cta_rank * bnl;      // this CTA's part of B's N range
                 const int za = p.a_batched ? t.b : 0, zb = p.b_batched ? t.b : 0;
+                const uint32_t stage_tx = (uint32_t)(kCta * kCopies * (L::kABytes + bnl * kRowBytes));
                 for (int kb = 0; kb < p.num_kb; ++kb) {
-                    if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag, p.err_word, 0x100u + stage)) {
+                    if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag, p.err_word, 0x100u + stage,
+                                   2000000000ull, 40)) {
                         ok = false;
                         break;
                     }
                     const uint32_t full = smem_u32(&bar_full[stage]);
                     // the even CTA's barrier collects the bytes of both CTAs
-                    if (cta_rank == 0) mbar_expect_tx(full, (uint32_t)(kCta * L::kStageBytes));
+                    if (cta_rank == 0) mbar_expect_tx(full, stage_tx);
                     const uint32_t sa = smem_base + stage * L::kStageBytes;
                     const uint32_t sb = sa + kCopies * L::kABytes;
                     const int k0 = kb * kBKElems;
@@ -357,13 +380,17 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     for (int ps = 0; ps < kCopies; ++ps) {
                         const CUtensorMap* ma = ps == 0 ? &tm_a : &tm_a_lo;
                         const CUtensorMap* mb = ps == 0 ? &tm_b : &tm_b_lo;
+                        // K-contiguous B, tail half: without the fp32 split the second B map is free and
+                        // holds the half-height box
+                        const CUtensorMap* mb_k = (half && !kSplit) ? &tm_b_lo : mb;
                         tma_load_3d<kCta>(sa + ps * L::kABytes, ma, full, k0, t.m0, za);
                         if (p.b_mn_major) {
 #pragma unroll
                             for (int j = 0; j < BNL / kBBoxCols; ++j)
-                                tma_load_3d<kCta>(sb + ps * L::kBBytes + j * kBBoxBytes, mb, full, t.n0 + j * kBBoxCols, k0, zb);
+                                if (j < bnl / kBBoxCols)
+                                    tma_load_3d<kCta>(sb + ps * L::kBBytes + j * kBBoxBytes, mb, full, t.n0 + j * kBBoxCols, k0, zb);
                         } else {
-                            tma_load_3d<kCta>(sb + ps * L::kBBytes, mb, full, k0, t.n0, zb);
+                            tma_load_3d<kCta>(sb + ps * L::kBBytes, mb_k, full, k0, t.n0, zb);
                         }
                     }
                     ++issued;
@@ -411,6 +438,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 }
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+                const uint32_t idesc = tile >= p.full_units ? p.idesc_half : p.idesc;
                 uint32_t first = 0;
                 for (int kb = 0; kb < p.num_kb; ++kb) {
                     if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag, p.err_word, 0x300u + stage)) {
@@ -430,7 +458,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #pragma unroll
                         for (int k = 0; k < kKSteps; ++k) {
                             umma<kTF32, kCta>(tmem_d, da + (uint64_t)((k * kUmmaKBytes) >> 4), db + (uint64_t)((k * b_kstep) >> 4),
-                                        p.idesc, first);
+                                        idesc, first);
                             first = 1;
                         }
                     }
@@ -462,7 +490,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         const bool bias_vec = has_bias && ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
         constexpr int kPack = 16 / sizeof(OutT);  // elements per 16-byte store
         for (long long tile = tile_first; tile < p.num_tiles; tile += tile_step) {
-            bool ok = mbar_wait(smem_u32(&bar_acc_full[acc]), acc_phase, &abort_flag, p.err_word, 0x400u + acc);
+            bool ok = mbar_wait(smem_u32(&bar_acc_full[acc]), acc_phase, &abort_flag, p.err_word, 0x400u + acc,
+                                2000000000ull, 200);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -471,7 +500,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             const bool row_ok = m < p.M;
             const long long row_off = (long long)t.b * p.batch_stride_c + m * p.ldc;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = 0; c0 < t.width; c0 += 32) {
                 float v[32];
                 __syncwarp();  // lanes that skipped stores rejoin before the warp-wide TMEM load
                 if (p.num_kb > 0) {
@@ -712,6 +741,15 @@ static int validate_desc(const cg_b200_gemm_desc* d) {
     return CG_B200_OK;
 }
 
+// CG_B200_GEMM_TAIL=0 turns the half-width tail units off (a test and tuning knob).
+static bool tail_split_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("CG_B200_GEMM_TAIL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 template <int kCta, bool kTF32, bool kSplit, int BN, typename OutT>
 static int launch_variant(const CUtensorMap& ta, const CUtensorMap& ta_lo, const CUtensorMap& tb,
                           const CUtensorMap& tb_lo, GemmParams& p, cudaStream_t s) {
@@ -726,6 +764,15 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& ta_lo, const
     p.num_kb = (int)((p.K + (kRowBytes / elem) - 1) / (kRowBytes / elem));
     // persistent: one CTA (or CTA pair) per SM (or SM pair), never more CTAs than tiles
     const long long slots = sm_count() / kCta;
+    p.full_units = p.num_tiles;
+    if (kCta == 2 && !kSplit && tail_split_enabled()) {
+        // a last partial wave of r <= slots / 2 tiles runs as 2r half-width units instead
+        const long long r = p.num_tiles % slots;
+        if (r > 0 && 2 * r <= slots) {
+            p.full_units = p.num_tiles - r;
+            p.num_tiles = p.full_units + 2 * r;
+        }
+    }
     const int groups = (int)(p.num_tiles < slots ? p.num_tiles : slots);
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
@@ -842,6 +889,7 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
     // CTA pairs (256 x 256 tiles) for 16-bit inputs once the problem spans more than one such tile row
     const int cta = (!tf32 && bn == 256 && d.M > kBM && pair_enabled()) ? 2 : 1;
     p.idesc = make_idesc(d.in_dtype, tf32, p.b_mn_major != 0, kBM * cta, bn);
+    p.idesc_half = make_idesc(d.in_dtype, tf32, p.b_mn_major != 0, kBM * cta, bn / 2);
     const uint32_t box_k = (uint32_t)(kRowBytes / in_sz);
 
     // with K == 0 no load is ever issued; the maps only need an encodable base address
@@ -897,7 +945,9 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
     } else {
         st = make_map(&tb, b_hi, d.in_dtype, k_dim, d.N, b_nb, ldb, bsb_enc, box_k, (uint32_t)(bn / cta));
         if (st) return st;
-        st = make_map(&tb_lo, b_lo, d.in_dtype, k_dim, d.N, b_nb, ldb, bsb_enc, box_k, (uint32_t)(bn / cta));
+        // pairs without the fp32 split: the second map stages the half-height box of a tail unit
+        const uint32_t lo_rows = (cta == 2 && !sp.active) ? (uint32_t)(bn / cta / 2) : (uint32_t)(bn / cta);
+        st = make_map(&tb_lo, b_lo, d.in_dtype, k_dim, d.N, b_nb, ldb, bsb_enc, box_k, lo_rows);
     }
     if (st) return st;
 

@@ -91,6 +91,16 @@ def test_bf16_gemm_plain(ops, cgb, oracle, M, N, K, b_transposed):
     assert_close(got, want, 1e-2, f"bf16 {M}x{N}x{K} bT={b_transposed}")
 
 
+@pytest.mark.parametrize("b_transposed", [0, 1])
+def test_bf16_gemm_tail_half_tiles(ops, cgb, oracle, b_transposed):
+    """80 tiles of 256x256 on 74 CTA pairs: the last 6 tiles run as 12 half-width units; the N tail
+    (2000 columns) also puts a half unit partly and one wholly out of range."""
+    capi = cgb.capi
+    got, want = run_case(ops, cgb, oracle, 2560, 2000, 192, capi.BF16, capi.BF16, b_transposed=b_transposed,
+                         epilogue="bias_relu", seed=77)
+    assert_close(got, want, 1e-2, f"tail halves bT={b_transposed}")
+
+
 @pytest.mark.parametrize("epilogue", ["bias", "bias_relu", "bias_gelu_tanh", "bias_residual", "residual", "scale"])
 @pytest.mark.parametrize("out_name", ["BF16", "F32"])
 def test_bf16_gemm_epilogues(ops, cgb, oracle, epilogue, out_name):
