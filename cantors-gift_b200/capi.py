@@ -59,7 +59,9 @@ class GemmDesc(C.Structure):
                 ("batch_stride_a", C.c_int64), ("batch_stride_b", C.c_int64),
                 ("batch_stride_c", C.c_int64),
                 ("in_dtype", C.c_int32), ("out_dtype", C.c_int32), ("compute", C.c_int32),
-                ("epilogue", C.c_int32), ("b_transposed", C.c_int32), ("alpha", C.c_float)]
+                ("epilogue", C.c_int32), ("b_transposed", C.c_int32), ("alpha", C.c_float),
+                ("batch_inner", C.c_int64), ("inner_stride_a", C.c_int64), ("inner_stride_b", C.c_int64),
+                ("inner_stride_c", C.c_int64)]
 
 
 _vp, _vpp, _sz, _i, _i64 = C.c_void_p, C.POINTER(C.c_void_p), C.c_size_t, C.c_int, C.c_int64
@@ -154,7 +156,7 @@ def make_eltwise_desc(dtype, prog, bcast=(), inner=1, round_each_op=0):
 
 def make_gemm_desc(M, N, K, in_dtype, out_dtype, epilogue="none", batch=1, b_transposed=0,
                    lda=None, ldb=None, ldc=None, bsa=None, bsb=None, bsc=None, compute="default",
-                   alpha=1.0):
+                   alpha=1.0, batch_inner=0, isa=0, isb=0, isc=0):
     d = GemmDesc()
     d.M, d.N, d.K, d.batch = M, N, K, batch
     d.lda = K if lda is None else lda
@@ -168,4 +170,5 @@ def make_gemm_desc(M, N, K, in_dtype, out_dtype, epilogue="none", batch=1, b_tra
     d.epilogue = EPILOGUE[epilogue] if isinstance(epilogue, str) else epilogue
     d.b_transposed = b_transposed
     d.alpha = alpha
+    d.batch_inner, d.inner_stride_a, d.inner_stride_b, d.inner_stride_c = batch_inner, isa, isb, isc
     return d

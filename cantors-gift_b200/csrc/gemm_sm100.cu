@@ -48,14 +48,16 @@ constexpr uint32_t kTmemCols = 512;
 
 struct GemmParams {
     long long M, N, K, batch;
-    long long ldc, batch_stride_c;
+    long long ldc;
+    long long c_stride_in, c_stride_out;   // elements between GEMMs of the inner / outer batch level
+    long long batch_in;                    // GEMMs per outer batch step (>= 1)
     const void* bias;
     const void* residual;
     void* C;
     int epilogue;
     float alpha;
     int b_mn_major;       // 1: B is [K, N] row-major (N contiguous); 0: B is [N, K]
-    int a_batched, b_batched;
+    int a_in, a_out, b_in, b_out;          // 0: the operand is broadcast along that batch level
     int tiles_m, tiles_n;
     long long num_tiles;
     int num_kb;
@@ -128,16 +130,17 @@ constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;
 // Plain (non-multicast) tiled load into this CTA's shared memory. With kCta == 2 the byte count is
 // credited to the even CTA's barrier, which the MMA issuer waits on.
 template <int kCta>
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z,
+                                            int w) {
     if constexpr (kCta == 1) {
         asm volatile(
-            "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-            ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
+            "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+            ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
             : "memory");
     } else {
         asm volatile(
-            "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-            ::"r"(dst), "l"(map), "r"(bar & kPeerBitMask), "r"(x), "r"(y), "r"(z)
+            "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+            ::"r"(dst), "l"(map), "r"(bar & kPeerBitMask), "r"(x), "r"(y), "r"(z), "r"(w)
             : "memory");
     }
 }
@@ -362,7 +365,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 const bool half = t.width != BN;
                 t.m0 += (int)cta_rank * kBM;      // this CTA's rows of A
                 t.n0 += (int)cta_rank * bnl;      // this CTA's part of B's N range
-                const int za = p.a_batched ? t.b : 0, zb = p.b_batched ? t.b : 0;
+                const int b_in = (int)(t.b % p.batch_in), b_out = (int)(t.b / p.batch_in);
+                const int za = p.a_in ? b_in : 0, wa = p.a_out ? b_out : 0;
+                const int zb = p.b_in ? b_in : 0, wb = p.b_out ? b_out : 0;
                 const uint32_t stage_tx = (uint32_t)(kCta * kCopies * (L::kABytes + bnl * kRowBytes));
                 for (int kb = 0; kb < p.num_kb; ++kb) {
                     if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag, p.err_word, 0x100u + stage,
@@ -383,14 +388,14 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                         // K-contiguous B, tail half: without the fp32 split the second B map is free and
                         // holds the half-height box
                         const CUtensorMap* mb_k = (half && !kSplit) ? &tm_b_lo : mb;
-                        tma_load_3d<kCta>(sa + ps * L::kABytes, ma, full, k0, t.m0, za);
+                        tma_load_4d<kCta>(sa + ps * L::kABytes, ma, full, k0, t.m0, za, wa);
                         if (p.b_mn_major) {
 #pragma unroll
                             for (int j = 0; j < BNL / kBBoxCols; ++j)
                                 if (j < bnl / kBBoxCols)
-                                    tma_load_3d<kCta>(sb + ps * L::kBBytes + j * kBBoxBytes, mb, full, t.n0 + j * kBBoxCols, k0, zb);
+                                    tma_load_4d<kCta>(sb + ps * L::kBBytes + j * kBBoxBytes, mb, full, t.n0 + j * kBBoxCols, k0, zb, wb);
                         } else {
-                            tma_load_3d<kCta>(sb + ps * L::kBBytes, mb_k, full, k0, t.n0, zb);
+                            tma_load_4d<kCta>(sb + ps * L::kBBytes, mb_k, full, k0, t.n0, zb, wb);
                         }
                     }
                     ++issued;
@@ -498,7 +503,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             const TileCoord t = decode_tile(tile, p, kTileM, BN);
             const long long m = (long long)t.m0 + (long long)cta_rank * kBM + row_in_tile;
             const bool row_ok = m < p.M;
-            const long long row_off = (long long)t.b * p.batch_stride_c + m * p.ldc;
+            const long long row_off = (long long)(t.b % p.batch_in) * p.c_stride_in + (long long)(t.b / p.batch_in) * p.c_stride_out + m * p.ldc;
 #pragma unroll 1
             for (int c0 = 0; c0 < t.width; c0 += 32) {
                 float v[32];
@@ -663,20 +668,28 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// 3-D map {inner, rows, batch}; box {box_inner, box_rows, 1}; 128-byte swizzle; OOB reads give zero.
-static int make_map(CUtensorMap* map, const void* base, int dtype, uint64_t inner, uint64_t rows, uint64_t batch,
-                    uint64_t ld_elems, uint64_t batch_stride_elems, uint32_t box_inner, uint32_t box_rows) {
+// Two batch levels of one operand: counts (1 = broadcast or unused) and strides in elements.
+struct BatchDims {
+    uint64_t n_in = 1, n_out = 1;
+    uint64_t s_in = 0, s_out = 0;
+};
+
+// 4-D map {inner, rows, batch_in, batch_out}; box {box_inner, box_rows, 1, 1}; 128-byte swizzle; OOB
+// reads give zero. A level with count 1 is never stepped, so its stride only has to be encodable.
+static int make_map(CUtensorMap* map, const void* base, int dtype, uint64_t inner, uint64_t rows, const BatchDims& bd,
+                    uint64_t ld_elems, uint32_t box_inner, uint32_t box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return CG_B200_ERR_CUDA;
     const uint64_t esz = dtype_bytes(dtype);
     CUtensorMapDataType dt = dtype == CG_B200_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                                   : (dtype == CG_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                                            : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
-    cuuint64_t dims[3] = {inner, rows, batch};
-    cuuint64_t strides[2] = {ld_elems * esz, batch_stride_elems * esz};
-    cuuint32_t box[3] = {box_inner, box_rows, 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = fn(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    const uint64_t fallback = rows * ld_elems * esz;   // any 16-byte multiple serves a count-1 level
+    cuuint64_t dims[4] = {inner, rows, bd.n_in, bd.n_out};
+    cuuint64_t strides[3] = {ld_elems * esz, bd.n_in > 1 ? bd.s_in * esz : fallback, bd.n_out > 1 ? bd.s_out * esz : fallback};
+    cuuint32_t box[4] = {box_inner, box_rows, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         note_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
@@ -735,7 +748,10 @@ static int validate_desc(const cg_b200_gemm_desc* d) {
     if (d->lda < d->K || d->ldc < d->N) return CG_B200_ERR_INVALID_ARG;
     if (d->ldb < (d->b_transposed ? d->K : d->N)) return CG_B200_ERR_INVALID_ARG;
     if (d->batch_stride_a < 0 || d->batch_stride_b < 0 || d->batch_stride_c < 0) return CG_B200_ERR_INVALID_ARG;
-    if (d->batch > 1 && d->batch_stride_c < d->M * d->ldc) return CG_B200_ERR_INVALID_ARG;
+    if (d->batch_inner < 0 || (d->batch_inner > 1 && d->batch % d->batch_inner != 0)) return CG_B200_ERR_INVALID_ARG;
+    if (d->batch_inner > 1 && (d->inner_stride_a < 0 || d->inner_stride_b < 0 || d->inner_stride_c <= 0))
+        return CG_B200_ERR_INVALID_ARG;
+    if (d->batch_inner <= 1 && d->batch > 1 && d->batch_stride_c < d->M * d->ldc) return CG_B200_ERR_INVALID_ARG;
     if (d->M > 0x7fffffffLL || d->N > 0x7fffffffLL || d->K > 0x7fffffffLL || d->batch > 0x7fffffffLL)
         return CG_B200_ERR_UNSUPPORTED;
     return CG_B200_OK;
@@ -857,6 +873,7 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
     const Fp32Plan sp = plan_fp32(desc);
     // C rows are written with 16-byte stores
     if (!aligned_to(C, 16) || (d.ldc * out_sz) % 16 || (d.batch_stride_c * out_sz) % 16) return CG_B200_ERR_MISALIGNED;
+    if (d.batch_inner > 1 && (d.inner_stride_c * out_sz) % 16) return CG_B200_ERR_MISALIGNED;
     if (need_res && !aligned_to(residual, 16)) return CG_B200_ERR_MISALIGNED;
     if (need_bias && !aligned_to(bias, out_sz)) return CG_B200_ERR_MISALIGNED;
     if (!sp.active) {
@@ -864,7 +881,10 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
         if (d.K > 0 && (!aligned_to(A, 16) || !aligned_to(B, 16))) return CG_B200_ERR_MISALIGNED;
         if ((d.lda * in_sz) % 16 || (d.ldb * in_sz) % 16) return CG_B200_ERR_MISALIGNED;
         if ((d.batch_stride_a * in_sz) % 16 || (d.batch_stride_b * in_sz) % 16) return CG_B200_ERR_MISALIGNED;
+        if (d.batch_inner > 1 && ((d.inner_stride_a * in_sz) % 16 || (d.inner_stride_b * in_sz) % 16))
+            return CG_B200_ERR_MISALIGNED;
     } else {
+        if (d.batch_inner > 1) return CG_B200_ERR_UNSUPPORTED;   // fp32 operands: one batch level only
         if (!aligned_to(A, 4) || !aligned_to(B, 4)) return CG_B200_ERR_MISALIGNED;
         if (!workspace || workspace_bytes < sp.bytes) return CG_B200_ERR_WORKSPACE;
         if (!aligned_to(workspace, 256)) return CG_B200_ERR_MISALIGNED;
@@ -876,12 +896,22 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
     GemmParams p;
     memset(&p, 0, sizeof(p));
     p.M = d.M; p.N = d.N; p.K = d.K; p.batch = d.batch;
-    p.ldc = d.ldc; p.batch_stride_c = d.batch_stride_c;
+    p.ldc = d.ldc;
+    // One batch level is the inner level with a single outer step.
+    const bool two = d.batch_inner > 1;
+    p.batch_in = two ? d.batch_inner : d.batch;
+    const long long n_out = d.batch / p.batch_in;
+    p.c_stride_in = two ? d.inner_stride_c : d.batch_stride_c;
+    p.c_stride_out = two ? d.batch_stride_c : 0;
     p.bias = bias; p.residual = residual; p.C = C;
     p.epilogue = epi; p.alpha = d.alpha;
     p.b_mn_major = (d.b_transposed || sp.active) ? 0 : 1;   // the fp32 workspace copy of B is K-contiguous
-    p.a_batched = d.batch_stride_a != 0 && d.batch > 1;
-    p.b_batched = d.batch_stride_b != 0 && d.batch > 1;
+    const long long a_s_in = two ? d.inner_stride_a : d.batch_stride_a, a_s_out = two ? d.batch_stride_a : 0;
+    const long long b_s_in = two ? d.inner_stride_b : d.batch_stride_b, b_s_out = two ? d.batch_stride_b : 0;
+    p.a_in = a_s_in != 0 && p.batch_in > 1;
+    p.a_out = a_s_out != 0 && n_out > 1;
+    p.b_in = b_s_in != 0 && p.batch_in > 1;
+    p.b_out = b_s_out != 0 && n_out > 1;
     p.err_word = shared_err_word ? device_error_word() : err_word;
 
     const bool tf32 = d.in_dtype == CG_B200_F32;
@@ -897,15 +927,19 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
     const void* a_lo = a_hi;
     const void* b_hi = d.K > 0 ? B : C;
     const void* b_lo = b_hi;
-    long long lda = d.lda, ldb = d.ldb, bsa = d.batch_stride_a, bsb = d.batch_stride_b;
-    long long b_rows = d.b_transposed ? d.N : d.K;
+    long long lda = d.lda, ldb = d.ldb;
+    BatchDims bda, bdb;
+    bda.n_in = p.a_in ? (uint64_t)p.batch_in : 1; bda.s_in = (uint64_t)a_s_in;
+    bda.n_out = p.a_out ? (uint64_t)n_out : 1;    bda.s_out = (uint64_t)a_s_out;
+    bdb.n_in = p.b_in ? (uint64_t)p.batch_in : 1; bdb.s_in = (uint64_t)b_s_in;
+    bdb.n_out = p.b_out ? (uint64_t)n_out : 1;    bdb.s_out = (uint64_t)b_s_out;
     if (sp.active) {
         float* w = static_cast<float*>(workspace);
         float* wa_hi = w;
         float* wa_lo = sp.copies == 2 ? w + sp.a_elems : nullptr;
         float* wb_hi = w + sp.copies * sp.a_elems;
         float* wb_lo = sp.copies == 2 ? wb_hi + sp.b_elems : nullptr;
-        const long long a_batches = p.a_batched ? d.batch : 1, b_batches = p.b_batched ? d.batch : 1;
+        const long long a_batches = p.a_in ? d.batch : 1, b_batches = p.b_in ? d.batch : 1;
         const int blocks = sm_count() * 8;
         if (d.K > 0) {
             tf32_split_kernel<<<blocks, 256, 0, s>>>(static_cast<const float*>(A), wa_hi, wa_lo, d.M, d.K, d.lda,
@@ -923,31 +957,27 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
         }
         a_hi = wa_hi; a_lo = wa_lo ? wa_lo : wa_hi; b_hi = wb_hi; b_lo = wb_lo ? wb_lo : wb_hi;
         lda = sp.ldk; ldb = sp.ldk;
-        bsa = d.M * sp.ldk; bsb = d.N * sp.ldk;
-        b_rows = d.N;
+        bda.s_in = (uint64_t)(d.M * sp.ldk);   // the workspace copies are dense, one batch level
+        bdb.s_in = (uint64_t)(d.N * sp.ldk);
     }
-    const uint64_t a_nb = p.a_batched ? (uint64_t)d.batch : 1, b_nb = p.b_batched ? (uint64_t)d.batch : 1;
-    // a batch stride of 0 cannot be encoded; with one batch slice the value is never used
-    const uint64_t bsa_enc = bsa > 0 ? (uint64_t)bsa : (uint64_t)d.M * lda;
-    const uint64_t bsb_enc = bsb > 0 ? (uint64_t)bsb : (uint64_t)b_rows * ldb;
     // K == 0: no k-blocks, the maps are never dereferenced but must still encode
     const uint64_t k_dim = d.K > 0 ? (uint64_t)d.K : 1;
 
     alignas(64) CUtensorMap ta, ta_lo, tb, tb_lo;
-    st = make_map(&ta, a_hi, d.in_dtype, k_dim, d.M, a_nb, lda, bsa_enc, box_k, kBM);
+    st = make_map(&ta, a_hi, d.in_dtype, k_dim, d.M, bda, lda, box_k, kBM);
     if (st) return st;
-    st = make_map(&ta_lo, a_lo, d.in_dtype, k_dim, d.M, a_nb, lda, bsa_enc, box_k, kBM);
+    st = make_map(&ta_lo, a_lo, d.in_dtype, k_dim, d.M, bda, lda, box_k, kBM);
     if (st) return st;
     if (p.b_mn_major) {
-        st = make_map(&tb, b_hi, d.in_dtype, d.N, k_dim, b_nb, ldb, bsb_enc, box_k, box_k);
+        st = make_map(&tb, b_hi, d.in_dtype, d.N, k_dim, bdb, ldb, box_k, box_k);
         if (st) return st;
-        st = make_map(&tb_lo, b_lo, d.in_dtype, d.N, k_dim, b_nb, ldb, bsb_enc, box_k, box_k);
+        st = make_map(&tb_lo, b_lo, d.in_dtype, d.N, k_dim, bdb, ldb, box_k, box_k);
     } else {
-        st = make_map(&tb, b_hi, d.in_dtype, k_dim, d.N, b_nb, ldb, bsb_enc, box_k, (uint32_t)(bn / cta));
+        st = make_map(&tb, b_hi, d.in_dtype, k_dim, d.N, bdb, ldb, box_k, (uint32_t)(bn / cta));
         if (st) return st;
         // pairs without the fp32 split: the second map stages the half-height box of a tail unit
         const uint32_t lo_rows = (cta == 2 && !sp.active) ? (uint32_t)(bn / cta / 2) : (uint32_t)(bn / cta);
-        st = make_map(&tb_lo, b_lo, d.in_dtype, k_dim, d.N, b_nb, ldb, bsb_enc, box_k, lo_rows);
+        st = make_map(&tb_lo, b_lo, d.in_dtype, k_dim, d.N, bdb, ldb, box_k, lo_rows);
     }
     if (st) return st;
 

@@ -1,0 +1,92 @@
+"""Pre-LN transformer encoder block out of the path's kernels (C-ABI calls only).
+
+    h = x + W_o . attn(LN(x))            attn: softmax(Q K^T / sqrt(d_h)) V per head
+    y = h + W_2 . gelu(W_1 . LN(h) + b_1) + b_2
+
+The dataflow is the reference's transformer benchmark graph (benchmarks/benchmark_transformer.py:98-119:
+layernorm eps 1e-5, GELU, no mask, no dropout); the reference only ever compiles that graph, it
+never executes it (benchmarks/REPORT_TRANSFORMER.md:53-57). Nine launches per block:
+  layernorm | QKV GEMM | Q K^T GEMM (heads as the inner batch level, scale in the epilogue) |
+  row softmax | P V GEMM (written straight into [B*S, d_model]) | out-proj GEMM + residual |
+  layernorm | FFN1 GEMM + bias + gelu | FFN2 GEMM + bias + residual
+Weights are [in, out] row-major (x @ W), all tensors bf16/f16/f32 of one dtype.
+"""
+import ctypes as C
+import math
+
+import torch
+
+from . import capi
+from .capi import check, lib
+from .ops import DTYPE_OF_TORCH
+
+
+class EncoderBlock:
+    def __init__(self, d_model, n_heads, d_ff, w_qkv, w_o, w_1, b_1, w_2, b_2, eps=1e-5):
+        assert d_model % n_heads == 0
+        self.D, self.H, self.F, self.dh, self.eps = d_model, n_heads, d_ff, d_model // n_heads, eps
+        self.w_qkv, self.w_o, self.w_1, self.b_1, self.w_2, self.b_2 = w_qkv, w_o, w_1, b_1, w_2, b_2
+        assert tuple(w_qkv.shape) == (d_model, 3 * d_model) and tuple(w_o.shape) == (d_model, d_model)
+        assert tuple(w_1.shape) == (d_model, d_ff) and tuple(w_2.shape) == (d_ff, d_model)
+        self.dtype = w_qkv.dtype
+        self.dt = DTYPE_OF_TORCH[self.dtype]
+        self._bufs = {}
+
+    def _buf(self, name, shape, device):
+        t = self._bufs.get(name)
+        if t is None or tuple(t.shape) != tuple(shape):
+            t = torch.empty(shape, dtype=self.dtype, device=device)
+            self._bufs[name] = t
+        return t
+
+    @staticmethod
+    def flops(B, S, D, H, F):
+        """Matmul FLOPs of one block, 2*batch*M*K*N per matmul as the reference counts them
+        (src/analysis/arithmetic_intensity.cpp:73-89)."""
+        return 2.0 * B * S * (3 * D * D + D * D + 2 * D * F) + 2.0 * 2 * B * H * S * S * (D // H)
+
+    def forward(self, x, out=None, stream=None):
+        """x: [B, S, D] contiguous CUDA tensor. Returns y of the same shape."""
+        B, S, D = x.shape
+        H, dh, F, dt = self.H, self.dh, self.F, self.dt
+        dev = x.device
+        L = lib()
+        st = C.c_void_p((torch.cuda.current_stream() if stream is None else stream).cuda_stream)
+        p = lambda t: None if t is None else C.c_void_p(t.data_ptr())  # noqa: E731
+        rows = B * S
+        x2 = x.view(rows, D)
+        ln1 = self._buf("ln1", (rows, D), dev)
+        qkv = self._buf("qkv", (rows, 3 * D), dev)
+        scores = self._buf("scores", (B * H, S, S), dev)
+        ctx = self._buf("ctx", (rows, D), dev)
+        h = self._buf("h", (rows, D), dev)
+        ln2 = self._buf("ln2", (rows, D), dev)
+        ff = self._buf("ff", (rows, F), dev)
+        y = torch.empty_like(x) if out is None else out
+
+        def gemm(desc, a, b, c, bias=None, res=None, a_off=0, b_off=0):
+            es = a.element_size()
+            check(L.cg_b200_gemm(C.byref(desc), C.c_void_p(a.data_ptr() + a_off * es), C.c_void_p(b.data_ptr() + b_off * es),
+                                 p(bias), p(res), p(c), None, 0, st), "gemm")
+
+        check(L.cg_b200_layernorm(dt, p(x2), None, None, self.eps, p(ln1), rows, D, st), "layernorm")
+        gemm(capi.make_gemm_desc(rows, 3 * D, D, dt, dt), ln1, self.w_qkv, qkv)
+        # scores[b, h] = Q_bh K_bh^T / sqrt(dh): Q, K are column blocks of the qkv rows (row stride 3D);
+        # heads are the inner batch level (stride dh), sequences the outer one (stride S * 3D)
+        d_qk = capi.make_gemm_desc(S, S, dh, dt, dt, epilogue="scale", alpha=1.0 / math.sqrt(dh), batch=B * H,
+                                   b_transposed=1, lda=3 * D, ldb=3 * D, ldc=S, batch_inner=H,
+                                   bsa=S * 3 * D, bsb=S * 3 * D, bsc=H * S * S, isa=dh, isb=dh, isc=S * S)
+        gemm(d_qk, qkv, qkv, scores, b_off=D)
+        check(L.cg_b200_softmax(dt, p(scores), p(scores), B * H * S, S, st), "softmax")
+        # ctx[b, :, h*dh:(h+1)*dh] = P_bh V_bh, V_bh = qkv[b, :, 2D + h*dh : ...] ([S, dh], N contiguous)
+        d_pv = capi.make_gemm_desc(S, dh, S, dt, dt, batch=B * H, lda=S, ldb=3 * D, ldc=D, batch_inner=H,
+                                   bsa=H * S * S, bsb=S * 3 * D, bsc=S * D, isa=S * S, isb=dh, isc=dh)
+        gemm(d_pv, scores, qkv, ctx, b_off=2 * D)
+        gemm(capi.make_gemm_desc(rows, D, D, dt, dt, epilogue="residual"), ctx, self.w_o, h, res=x2)
+        check(L.cg_b200_layernorm(dt, p(h), None, None, self.eps, p(ln2), rows, D, st), "layernorm")
+        gemm(capi.make_gemm_desc(rows, F, D, dt, dt, epilogue="bias_gelu_tanh"), ln2, self.w_1, ff, bias=self.b_1)
+        gemm(capi.make_gemm_desc(rows, D, F, dt, dt, epilogue="bias_residual"), ff, self.w_2, y.view(rows, D),
+             bias=self.b_2, res=h)
+        return y
+
+    LAUNCHES_PER_FORWARD = 9

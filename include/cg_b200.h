@@ -228,6 +228,12 @@ typedef struct cg_b200_gemm_desc {
     int32_t epilogue;                /* cg_b200_epilogue */
     int32_t b_transposed;            /* 0: B is [K, N] row-major; 1: B is stored [N, K] row-major */
     float   alpha;                   /* EPI_SCALE factor */
+    /* Optional second batch level (e.g. heads inside sequences). With batch_inner > 1 the batch
+     * index b in [0, batch) splits as outer = b / batch_inner, inner = b % batch_inner and operand X
+     * of GEMM b starts at outer * batch_stride_x + inner * inner_stride_x (elements). batch_inner
+     * must divide batch; 0 or 1 = single level. */
+    int64_t batch_inner;
+    int64_t inner_stride_a, inner_stride_b, inner_stride_c;
 } cg_b200_gemm_desc;
 
 /* Bytes of device scratch cg_b200_gemm needs for this problem (0 if none). */

@@ -274,6 +274,13 @@ int cgo_eltwise(const cg_b200_eltwise_desc* d, const void* const* inputs, int n_
  * B[k,n], acc) in fp32 (benchmarks/benchmark.py:326-438, vfmadd231ss on xmm0). acc64 != 0
  * accumulates in double instead (used to report error against exact arithmetic).
  * `rows` optionally limits the work to flat row indices b*M + m (C is written only there). */
+/* Element offset of operand X of GEMM `b`: one batch level, or outer/inner levels when
+ * batch_inner > 1 (include/cg_b200.h, cg_b200_gemm_desc). */
+static inline int64_t batch_offset(const cg_b200_gemm_desc* d, int64_t b, int64_t stride, int64_t inner_stride) {
+    if (d->batch_inner > 1) return (b / d->batch_inner) * stride + (b % d->batch_inner) * inner_stride;
+    return b * stride;
+}
+
 typedef struct {
     const void* src; int dt; int64_t cols, ld; int transposed; float* dst;
 } convert_ctx;
@@ -322,7 +329,7 @@ static void gemm_range(int64_t lo, int64_t hi, void* p) {
                 for (int64_t n = 0; n < N; ++n) accf[n] = fmaf(a, br[n], accf[n]);
             }
         }
-        size_t crow = (size_t)(c->b * d->batch_stride_c + m * d->ldc);
+        size_t crow = (size_t)(batch_offset(d, c->b, d->batch_stride_c, d->inner_stride_c) + m * d->ldc);
         for (int64_t n = 0; n < N; ++n) {
             float v = accf[n];
             if (epi == CG_B200_EPI_SCALE) v = v * d->alpha;
@@ -342,6 +349,7 @@ int cgo_gemm(const cg_b200_gemm_desc* d, const void* A, const void* B, const voi
     if (!d) return CG_B200_ERR_NULL_POINTER;
     if (!dtype_ok(d->in_dtype) || !dtype_ok(d->out_dtype)) return CG_B200_ERR_INVALID_ARG;
     if (d->M < 0 || d->N < 0 || d->K < 0 || d->batch < 1) return CG_B200_ERR_INVALID_ARG;
+    if (d->batch_inner > 1 && d->batch % d->batch_inner != 0) return CG_B200_ERR_INVALID_ARG;
     if (d->M == 0 || d->N == 0) return CG_B200_OK;
     if (!A || !B || !C) return CG_B200_ERR_NULL_POINTER;
     const int epi = d->epilogue;
@@ -363,14 +371,13 @@ int cgo_gemm(const cg_b200_gemm_desc* d, const void* A, const void* B, const voi
         int64_t b = flat0 / M;
         int64_t end = start;
         while (end < total_rows && (rows ? rows[end] : end) / M == b) ++end;
-        int64_t bb = d->batch_stride_b == 0 ? 0 : b;
+        int64_t bb = batch_offset(d, b, d->batch_stride_b, d->inner_stride_b);
         if (bb != cached_b) {
-            convert_ctx cc = {(const char*)B + (size_t)(bb * d->batch_stride_b) * in_sz, d->in_dtype,
-                              N, d->ldb, d->b_transposed, Bf};
+            convert_ctx cc = {(const char*)B + (size_t)bb * in_sz, d->in_dtype, N, d->ldb, d->b_transposed, Bf};
             parallel_for(K, 16, convert_range, &cc);
             cached_b = bb;
         }
-        gemm_ctx gc = {d, (const char*)A + (size_t)(b * d->batch_stride_a) * in_sz, Bf, bias,
+        gemm_ctx gc = {d, (const char*)A + (size_t)batch_offset(d, b, d->batch_stride_a, d->inner_stride_a) * in_sz, Bf, bias,
                        residual, C, rows, start, b, acc64};
         parallel_for(end - start, 1, gemm_range, &gc);
         start = end;

@@ -38,7 +38,9 @@ class GemmDesc(C.Structure):
                 ("batch_stride_a", C.c_int64), ("batch_stride_b", C.c_int64),
                 ("batch_stride_c", C.c_int64),
                 ("in_dtype", C.c_int32), ("out_dtype", C.c_int32), ("compute", C.c_int32),
-                ("epilogue", C.c_int32), ("b_transposed", C.c_int32), ("alpha", C.c_float)]
+                ("epilogue", C.c_int32), ("b_transposed", C.c_int32), ("alpha", C.c_float),
+                ("batch_inner", C.c_int64), ("inner_stride_a", C.c_int64), ("inner_stride_b", C.c_int64),
+                ("inner_stride_c", C.c_int64)]
 
 
 _lib = None
@@ -182,7 +184,7 @@ EPI = {"none": 0, "bias": 1, "bias_relu": 2, "bias_gelu_tanh": 3, "bias_residual
 
 def make_gemm_desc(M, N, K, in_dtype, out_dtype, epilogue="none", batch=1, b_transposed=0,
                    lda=None, ldb=None, ldc=None, bsa=None, bsb=None, bsc=None, compute=0, alpha=1.0,
-                   cls=GemmDesc):
+                   cls=GemmDesc, batch_inner=0, isa=0, isb=0, isc=0):
     d = cls()
     d.M, d.N, d.K, d.batch = M, N, K, batch
     d.lda = K if lda is None else lda
@@ -196,6 +198,7 @@ def make_gemm_desc(M, N, K, in_dtype, out_dtype, epilogue="none", batch=1, b_tra
     d.epilogue = EPI[epilogue] if isinstance(epilogue, str) else epilogue
     d.b_transposed = b_transposed
     d.alpha = alpha
+    d.batch_inner, d.inner_stride_a, d.inner_stride_b, d.inner_stride_c = batch_inner, isa, isb, isc
     return d
 
 
