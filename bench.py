@@ -1,6 +1,6 @@
 """Benchmark of the B200 execution path for cantors-gift Executables.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload gemm|eltwise|rowreduce|matmul_f32]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload gemm|eltwise|rowreduce|matmul_f32|block]
                     [--impl ours|reference] [--no-also]
 
 One JSON line on stdout (rank 0). The headline workload is the bf16 4096^3 GEMM with fused
@@ -391,7 +391,102 @@ class MatmulF32Workload(GemmWorkload):
                 "l2": f"rotating over {self.sets} buffer sets, 192 MiB > L2", "parallelism": f"x{world}"}
 
 
-WORKLOADS = {"gemm": GemmWorkload, "eltwise": EltwiseWorkload, "rowreduce": RowReduceWorkload,
+class BlockWorkload(Workload):
+    """Pre-LN encoder block, bf16, batch 32 x seq 2048, d_model 1024, 16 heads, FFN 4096; batch-sharded
+    over the ranks with one in-place all-gather of y."""
+    name, unit, bound, dtype = "block", "TFLOP/s", "tensor", "bf16"
+    B, S, D, H, F = 32, 2048, 1024, 16, 4096
+    launches_per_step = 9
+
+    def config(self, world):
+        return {"workload": "cfg5: pre-LN transformer encoder block, bf16, batch 32, seq 2048, d_model 1024, 16 heads, "
+                            "FFN 4096, GELU(tanh), weights ~N(0,0.02)",
+                "l2": "activations (over 6 GiB per step) larger than L2",
+                "parallelism": "1 GPU" if world == 1 else f"batch-sharded x{world}, in-place NCCL all-gather of y"}
+
+    def setup(self, rank, world):
+        import torch
+        from cantors_gift_b200.sharding import padded_rows
+        from cantors_gift_b200.transformer import EncoderBlock
+        self.rank, self.world = rank, world
+        self.Bs, padded = padded_rows(self.B, world)
+        assert padded == self.B
+        g = torch.Generator(device="cuda").manual_seed(4)
+        w = lambda *s: (torch.randn(*s, device="cuda", generator=g) * 0.02).to(torch.bfloat16)  # noqa: E731
+        D, F = self.D, self.F
+        self.block = EncoderBlock(D, self.H, F, w(D, 3 * D), w(D, D), w(D, F), w(F), w(F, D), w(D))
+        g2 = torch.Generator(device="cuda").manual_seed(5)
+        x = torch.randn(self.B, self.S, D, device="cuda", generator=g2).to(torch.bfloat16)
+        self.x = x[rank * self.Bs:(rank + 1) * self.Bs].contiguous()
+        self.y = torch.empty(self.B, self.S, D, device="cuda", dtype=torch.bfloat16)
+        self.comm = make_comm(rank, world) if world > 1 else None
+
+    def step(self, i):
+        import ctypes as C
+        import torch
+        from cantors_gift_b200 import capi
+        ys = self.y[self.rank * self.Bs:(self.rank + 1) * self.Bs]
+        self.block.forward(self.x, out=ys)
+        if self.comm is not None:
+            capi.check(capi.lib().cg_b200_allgather_inplace(self.comm, C.c_void_p(self.y.data_ptr()), ys.numel() * 2,
+                                                            C.c_void_p(torch.cuda.current_stream().cuda_stream)),
+                       "allgather_inplace")
+
+    def flops(self):
+        from cantors_gift_b200.transformer import EncoderBlock
+        return EncoderBlock.flops(self.B, self.S, self.D, self.H, self.F)
+
+    def work_per_step(self):
+        return self.flops() / 1e12
+
+    def algorithmic_per_launch(self):   # per step here: nine launches make one pass of the block
+        return self.flops() / self.world
+
+    def e2e_setup(self):
+        import torch
+        self.h_x = self.x.cpu().pin_memory()
+        self.h_y = torch.empty_like(self.h_x).pin_memory()
+        self.d_x = torch.empty_like(self.x)
+        self.d_y = torch.empty_like(self.x)
+
+        class _R:   # same close() protocol as HostRunner
+            def close(self_inner):
+                pass
+        self.runner = _R()
+        return self.h_x.numel() * 2, self.h_y.numel() * 2
+
+    def e2e_step(self):
+        import ctypes as C
+        import torch
+        from cantors_gift_b200 import capi
+        L = capi.lib()
+        st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        nb = self.h_x.numel() * 2
+        capi.check(L.cg_b200_memcpy_h2d(C.c_void_p(self.d_x.data_ptr()), C.c_void_p(self.h_x.data_ptr()), nb, st), "h2d")
+        self.block.forward(self.d_x, out=self.d_y)
+        capi.check(L.cg_b200_memcpy_d2h(C.c_void_p(self.h_y.data_ptr()), C.c_void_p(self.d_y.data_ptr()), nb, st), "d2h")
+        capi.check(L.cg_b200_stream_sync(st), "sync")
+
+    def cpu_baseline(self, budget_s, prefer_ref=True):
+        from oracle import oracle as O
+        from oracle import transformer as T
+        threads = os.cpu_count() or 1
+        O.set_num_threads(threads)
+        rng = np.random.default_rng(4)
+        D, F, S = self.D, self.F, self.S
+        w = lambda *s: O.to_bf16(rng.standard_normal(s, dtype=np.float32) * 0.02)  # noqa: E731
+        ws = dict(w_qkv=w(D, 3 * D), w_o=w(D, D), w_1=w(D, F), b_1=w(F), w_2=w(F, D), b_2=w(D))
+        x = O.to_bf16(rng.standard_normal((1, S, D), dtype=np.float32))
+        t0 = time.perf_counter()
+        T.encoder_block(x, n_heads=self.H, dtype=O.BF16, **ws)
+        dt_s = time.perf_counter() - t0
+        fl = self.flops() / self.B
+        return {"value": fl / dt_s / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                "sample": f"1 of {self.B} sequences (sequences are independent); the reference compiles this graph "
+                          "but never executes it"}, dt_s * self.B
+
+
+WORKLOADS = {"block": BlockWorkload, "gemm": GemmWorkload, "eltwise": EltwiseWorkload, "rowreduce": RowReduceWorkload,
              "matmul_f32": MatmulF32Workload}
 
 
@@ -484,7 +579,7 @@ def run_workload(name, steps, warmup, rank, world, peaks, sample_clocks, with_cp
     res = {
         "metric": METRIC, "value": value, "unit": w.unit, "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "strong" if name in ("gemm", "matmul_f32") else "weak", "vs_baseline": None,
+        "scaling": "strong" if name in ("gemm", "matmul_f32", "block") else "weak", "vs_baseline": None,
         "dtype": w.dtype, "data": "synthetic", "config": w.config(world),
         "e2e": {"value": e2e_work * e2e_steps / e_secs, "unit": w.unit, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "steps": e2e_steps,
@@ -494,7 +589,7 @@ def run_workload(name, steps, warmup, rank, world, peaks, sample_clocks, with_cp
                      "traffic": NCU_TRAFFIC_BYTES.get(name), "peak_source": peaks["source"] +
                      (" (sustained cuBLAS bf16)" if w.bound == "tensor" else " (copy bandwidth)"),
                      "note": "per rank; achieved = algorithmic work per launch / mean step time on the device"
-                             + (" (includes the all-gather)" if world > 1 and name in ("gemm", "matmul_f32") else "")},
+                             + (" (includes the all-gather)" if world > 1 and name in ("gemm", "matmul_f32", "block") else "")},
     }
     if clocks is not None:
         res["clocks"] = clocks
@@ -528,7 +623,7 @@ def run_reference_arm(args, rank, world):
     cpu["value"] = v
     line = {"impl": "reference", "metric": METRIC, "value": v, "unit": w.unit, "n_gpus": args.gpus,
             "steps": len(vals), "warmup": args.warmup, "ms_per_step": float(np.median(secs)) * 1e3,
-            "higher_is_better": True, "scaling": "strong" if args.workload in ("gemm", "matmul_f32") else "weak",
+            "higher_is_better": True, "scaling": "strong" if args.workload in ("gemm", "matmul_f32", "block") else "weak",
             "vs_baseline": None, "dtype": w.dtype, "data": "synthetic", "config": w.config(1),
             "cpu_baseline": cpu,
             "e2e": {"value": v, "unit": w.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -575,7 +670,7 @@ def main():
                         with_cpu=(world == 1 and not args.no_cpu), cpu_budget=12.0, with_e2e=not args.no_e2e)
     if not args.no_also and world == 1:
         also = []
-        for other in ("eltwise", "rowreduce", "matmul_f32"):
+        for other in ("eltwise", "rowreduce", "matmul_f32", "block"):
             if other == args.workload:
                 continue
             r = run_workload(other, args.steps, args.warmup, rank, world, peaks, sample_clocks=True,

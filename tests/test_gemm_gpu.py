@@ -150,6 +150,39 @@ def test_batched_and_broadcast(ops, cgb, oracle):
     assert_close(got, want, 1e-2, "B broadcast over batch")
 
 
+def test_two_level_batch_strided_operands(ops, cgb, oracle):
+    """Heads inside sequences: A and B are column blocks of one [rows, 3D] buffer (row stride 3D), the
+    inner batch level steps by the head width, the outer by a whole sequence; C is written into
+    column blocks of a [rows, D] buffer. The layout of the attention GEMMs."""
+    import torch
+    capi, O = cgb.capi, oracle
+    Bo, H, S, dh = 3, 4, 136, 64
+    D = H * dh
+    rng = np.random.default_rng(9)
+    qkv = O.to_bf16(rng.standard_normal((Bo * S, 3 * D), dtype=np.float32) * 0.3)
+    kw = dict(batch=Bo * H, batch_inner=H, lda=3 * D, ldb=3 * D, b_transposed=1, bsa=S * 3 * D, bsb=S * 3 * D, isa=dh, isb=dh)
+    # scores = Q K^T * 0.125 -> [Bo, H, S, S]
+    od = O.make_gemm_desc(S, S, dh, O.BF16, O.BF16, epilogue="scale", alpha=0.125, ldc=S, bsc=H * S * S, isc=S * S, **kw)
+    k_view = qkv.reshape(-1)[D:]
+    want = O.from_bf16(O.gemm(od, qkv, k_view, out=np.zeros(Bo * H * S * S, dtype=np.uint16)))
+    gd = capi.make_gemm_desc(S, S, dh, capi.BF16, capi.BF16, epilogue="scale", alpha=0.125, ldc=S, bsc=H * S * S, isc=S * S, **kw)
+    qd = torch.from_numpy(qkv.view(np.int16)).cuda().view(torch.bfloat16)
+    sc = torch.zeros(Bo * H * S * S, dtype=torch.bfloat16, device="cuda")
+    ops.gemm(gd, qd, qd.view(-1)[D:], sc)
+    assert ops.last_device_error() == 0
+    assert_close(_host_f32(O, sc, capi.BF16), want, 1e-2, "QK^T two-level batch")
+    # ctx[:, h*dh:(h+1)*dh] = P_bh V_bh with V = third column block, N contiguous
+    P = O.to_bf16(rng.random((Bo * H * S, S), dtype=np.float32) / S)
+    kw2 = dict(batch=Bo * H, batch_inner=H, lda=S, ldb=3 * D, ldc=D, bsa=H * S * S, bsb=S * 3 * D, bsc=S * D, isa=S * S, isb=dh, isc=dh)
+    od2 = O.make_gemm_desc(S, dh, S, O.BF16, O.BF16, **kw2)
+    want2 = O.from_bf16(O.gemm(od2, P, qkv.reshape(-1)[2 * D:], out=np.zeros(Bo * S * D, dtype=np.uint16)))
+    gd2 = capi.make_gemm_desc(S, dh, S, capi.BF16, capi.BF16, **kw2)
+    ctx = torch.zeros(Bo * S * D, dtype=torch.bfloat16, device="cuda")
+    ops.gemm(gd2, torch.from_numpy(P.view(np.int16)).cuda().view(torch.bfloat16), qd.view(-1)[2 * D:], ctx)
+    assert ops.last_device_error() == 0
+    assert_close(_host_f32(O, ctx, capi.BF16), want2, 1e-2, "PV two-level batch")
+
+
 def test_k_zero_gives_epilogue_of_zero(ops, cgb, oracle):
     capi = cgb.capi
     got, want = run_case(ops, cgb, oracle, 130, 72, 0, capi.BF16, capi.BF16, epilogue="bias")
