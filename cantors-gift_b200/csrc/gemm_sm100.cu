@@ -67,6 +67,7 @@ struct GemmParams {
     // becomes 2r half-cost units spread over the machine. num_tiles counts units.
     long long full_units;
     uint32_t idesc_half;   // instruction descriptor with N = BN / 2
+    int debug;             // tuning experiments only (CG_B200_GEMM_DEBUG): 1 = no operand loads, 2 = no epilogue work
     uint32_t* err_word;
 };
 
@@ -351,6 +352,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     if constexpr (kCta == 2) cluster_sync_all();   // the peer's barriers exist before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
+    // Programmatic dependent launch: everything above (barriers, TMEM) touched no global memory and
+    // may overlap the tail of the previous kernel in the stream; from here on operands are read and
+    // C is written, so wait for the previous grid to complete and flush. Letting the next grid's
+    // CTAs start their own prologue as soon as SMs free up hides its launch latency behind this
+    // grid's last wave.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -376,6 +384,12 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                         break;
                     }
                     const uint32_t full = smem_u32(&bar_full[stage]);
+                    if (p.debug & 1) {   // experiment: feed the MMAs stale shared memory, no loads
+                        if (cta_rank == 0) mbar_arrive(full);
+                        ++issued;
+                        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                        continue;
+                    }
                     // the even CTA's barrier collects the bytes of both CTAs
                     if (cta_rank == 0) mbar_expect_tx(full, stage_tx);
                     const uint32_t sa = smem_base + stage * L::kStageBytes;
@@ -515,7 +529,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     for (int j = 0; j < 32; ++j) v[j] = 0.0f;
                 }
                 const long long n0 = (long long)t.n0 + c0;
-                if (n0 >= p.N) continue;
+                if (n0 >= p.N || (p.debug & 2)) continue;
                 const bool full = n0 + 32 <= p.N;
                 if (epi == CG_B200_EPI_SCALE) {
 #pragma unroll
@@ -757,6 +771,15 @@ static int validate_desc(const cg_b200_gemm_desc* d) {
     return CG_B200_OK;
 }
 
+// CG_B200_GEMM_PDL=0 turns programmatic dependent launch off (a test and tuning knob).
+static bool pdl_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("CG_B200_GEMM_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 // CG_B200_GEMM_TAIL=0 turns the half-width tail units off (a test and tuning knob).
 static bool tail_split_enabled() {
     static const bool on = [] {
@@ -796,13 +819,15 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& ta_lo, const
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = L::kDynSmem;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = kCta;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
     CGB_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, ta_lo, tb, tb_lo, p));
     return CG_B200_OK;
 }
@@ -913,6 +938,10 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
     p.b_in = b_s_in != 0 && p.batch_in > 1;
     p.b_out = b_s_out != 0 && n_out > 1;
     p.err_word = shared_err_word ? device_error_word() : err_word;
+    {
+        static const int dbg = [] { const char* e = getenv("CG_B200_GEMM_DEBUG"); return e ? atoi(e) : 0; }();
+        p.debug = dbg;
+    }
 
     const bool tf32 = d.in_dtype == CG_B200_F32;
     const int bn = choose_bn(desc, sp.active && sp.copies == 2);
