@@ -265,7 +265,10 @@ class GemmWorkload(Workload):
         return {"workload": "cfg3: bf16 GEMM M=N=K=4096 + bias + GELU(tanh), fp32 accumulate",
                 "M": self.M, "N": self.N, "K": self.K,
                 "l2": f"rotating over {self.sets} (A, B, C) buffer sets, 384 MiB > L2",
-                "parallelism": "1 GPU" if world == 1 else f"M-sharded x{world}, in-place NCCL all-gather of C"}
+                "parallelism": "1 GPU" if world == 1 else
+                f"M-sharded x{world}; all-gather of C fused into the GEMM epilogue (peer stores over NVLink) + one barrier"
+                if os.environ.get("CG_B200_BENCH_ALLGATHER", "fused") == "fused" else
+                f"M-sharded x{world}, in-place NCCL all-gather of C"}
 
     def setup(self, rank, world):
         import torch
@@ -295,14 +298,28 @@ class GemmWorkload(Workload):
         from cantors_gift_b200 import ops
         self.ws, self.ws_bytes = ops.gemm_workspace(self.desc, self.A[0].device)
         self.comm = None
+        self.fused = world > 1 and os.environ.get("CG_B200_BENCH_ALLGATHER", "fused") == "fused"
         if world > 1:
             self.comm = make_comm(rank, world)
+        if self.fused:
+            # C buffers from the C ABI allocator (plain cudaMalloc, so they can be exported) and every
+            # peer's copy mapped here: the GEMM epilogue stores its rows into all of them
+            self.C_raw, self.peer_tables = share_buffers(rank, world, self.sets, self.M * self.N * self.C[0].element_size())
         self.launches_per_step = 1 if self.in_dtype_name == "BF16" else 3
 
     def step(self, i):
         import ctypes as C
         from cantors_gift_b200 import capi, ops
         s = i % self.sets
+        if self.fused:
+            import torch
+            st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+            p = lambda t: None if t is None else C.c_void_p(t.data_ptr())  # noqa: E731
+            capi.check(capi.lib().cg_b200_gemm_allgather(
+                C.byref(self.desc), p(self.A[s]), p(self.B[s]), p(self.bias) if self.epilogue != "none" else None, None,
+                self.C_raw[s], self.peer_tables[s], self.world, self.rank, p(self.ws), self.ws_bytes, st), "gemm_allgather")
+            capi.check(capi.lib().cg_b200_comm_barrier(self.comm, st), "comm_barrier")
+            return
         c_shard = self.C[s][self.rank * self.Ms:(self.rank + 1) * self.Ms]
         ops.gemm(self.desc, self.A[s], self.B[s], c_shard, bias=self.bias if self.epilogue != "none" else None,
                  workspace=self.ws)
@@ -488,6 +505,41 @@ class BlockWorkload(Workload):
 
 WORKLOADS = {"block": BlockWorkload, "gemm": GemmWorkload, "eltwise": EltwiseWorkload, "rowreduce": RowReduceWorkload,
              "matmul_f32": MatmulF32Workload}
+
+
+def share_buffers(rank, world, count, nbytes):
+    """Allocates `count` buffers through the C ABI on every rank and maps every peer's copies here.
+    Returns (local pointers, per-buffer tables of `world` pointers; entry `rank` is the local one)."""
+    import ctypes as C
+    import torch
+    import torch.distributed as dist
+    from cantors_gift_b200 import capi
+    L = capi.lib()
+    local, tables = [], []
+    for _ in range(count):
+        ptr = C.c_void_p()
+        capi.check(L.cg_b200_malloc(C.byref(ptr), nbytes), "malloc")
+        capi.check(L.cg_b200_memset(ptr, 0, nbytes, None), "memset")
+        h = (C.c_char * capi.IPC_HANDLE_BYTES)()
+        capi.check(L.cg_b200_ipc_export(ptr, h), "ipc_export")
+        mine = torch.frombuffer(bytearray(bytes(h)), dtype=torch.uint8).cuda()
+        allh = torch.empty(world * capi.IPC_HANDLE_BYTES, dtype=torch.uint8, device="cuda")
+        dist.all_gather_into_tensor(allh, mine)
+        allh = allh.cpu().numpy().tobytes()
+        table = (C.c_void_p * world)()
+        for r in range(world):
+            if r == rank:
+                table[r] = ptr.value
+            else:
+                peer = C.c_void_p()
+                capi.check(L.cg_b200_ipc_open(allh[r * capi.IPC_HANDLE_BYTES:(r + 1) * capi.IPC_HANDLE_BYTES], C.byref(peer)),
+                           "ipc_open")
+                table[r] = peer.value
+        local.append(ptr)
+        tables.append(table)
+    torch.cuda.synchronize()
+    dist.barrier()
+    return local, tables
 
 
 def make_comm(rank, world):

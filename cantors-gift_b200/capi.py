@@ -24,6 +24,7 @@ EPILOGUE = {"none": 0, "bias": 1, "bias_relu": 2, "bias_gelu_tanh": 3, "bias_res
             "residual": 5, "scale": 6}
 COMPUTE = {"default": 0, "tf32x3": 1, "tf32": 2}
 COMM_ID_BYTES = 128
+IPC_HANDLE_BYTES = 64
 GEMM_F32_STATIC_SCRATCH_BYTES = 16 << 20
 
 
@@ -101,7 +102,12 @@ SIGNATURES = {
     "cg_b200_comm_unique_id": (_i, [_vp]),
     "cg_b200_comm_init_rank": (_i, [_vpp, _i, _i, _vp]),
     "cg_b200_allgather_inplace": (_i, [_vp, _vp, _sz, _vp]),
+    "cg_b200_comm_barrier": (_i, [_vp, _vp]),
     "cg_b200_comm_destroy": (_i, [_vp]),
+    "cg_b200_ipc_export": (_i, [_vp, _vp]),
+    "cg_b200_ipc_open": (_i, [_vp, _vpp]),
+    "cg_b200_ipc_close": (_i, [_vp]),
+    "cg_b200_gemm_allgather": (_i, [C.POINTER(GemmDesc), _vp, _vp, _vp, _vp, _vp, _vpp, _i, _i, _vp, _sz, _vp]),
 }
 
 _lib = None

@@ -56,6 +56,7 @@ struct Comm {
     void* nccl_comm;
     int world;
     int rank;
+    void* token = nullptr;   // world * 8 bytes for cg_b200_comm_barrier
 };
 
 }  // namespace cgb
@@ -84,7 +85,13 @@ extern "C" int cg_b200_comm_init_rank(void** comm, int world, int rank, const vo
     memcpy(&id, host_unique_id, sizeof(id));
     void* c = nullptr;
     if (api.comm_init_rank(&c, world, id, rank) != 0) return CG_B200_ERR_COMM;
-    *comm = new Comm{c, world, rank};
+    Comm* out = new Comm{c, world, rank};
+    if (cudaMalloc(&out->token, (size_t)world * 8) != cudaSuccess || cudaMemset(out->token, 0, (size_t)world * 8) != cudaSuccess) {
+        api.comm_destroy(c);
+        delete out;
+        return CG_B200_ERR_CUDA;
+    }
+    *comm = out;
     return CG_B200_OK;
 }
 
@@ -99,9 +106,19 @@ extern "C" int cg_b200_allgather_inplace(void* comm, void* buf, size_t shard_byt
     return CG_B200_OK;
 }
 
+extern "C" int cg_b200_comm_barrier(void* comm, void* stream) {
+    if (!comm) return CG_B200_ERR_NULL_POINTER;
+    Comm* c = static_cast<Comm*>(comm);
+    // an 8-byte all-gather: it completes on a rank only after every rank has reached it in its stream
+    const char* send = static_cast<const char*>(c->token) + (size_t)c->rank * 8;
+    if (nccl().all_gather(send, c->token, 8, 0, c->nccl_comm, (cudaStream_t)stream) != 0) return CG_B200_ERR_COMM;
+    return CG_B200_OK;
+}
+
 extern "C" int cg_b200_comm_destroy(void* comm) {
     if (!comm) return CG_B200_OK;
     Comm* c = static_cast<Comm*>(comm);
+    if (c->token) cudaFree(c->token);
     int r = nccl().comm_destroy(c->nccl_comm);
     delete c;
     return r == 0 ? CG_B200_OK : CG_B200_ERR_COMM;

@@ -14,13 +14,15 @@
 //             pair (no TMA multicast is used anywhere); each CTA's TMEM holds its 128 rows of the
 //             accumulator and its own epilogue warps drain them
 //   kCta = 1  one CTA computes a 128 x BN tile (small problems, fp32 split)
-// Structure (one CTA per SM, persistent over output tiles, 192 threads):
+// Structure (one CTA per SM, persistent over output tiles, 320 threads):
 //   warp 0      TMA producer: cp.async.bulk.tensor loads of A and B k-blocks (128 bytes of K
 //               per row, 128-byte swizzle) into a ring of shared-memory stages
 //   warp 1      TMEM allocator + single-thread tcgen05.mma issuer; tcgen05.commit releases
 //               a stage / publishes an accumulator through mbarriers
-//   warps 2-5   epilogue: tcgen05.ld of the fp32 accumulator (one TMEM lane = one row),
-//               bias / activation / residual in registers, packed stores to C
+//   warps 2-9   epilogue: tcgen05.ld of the fp32 accumulator (one TMEM lane = one row; a warp may
+//               only touch the lane quarter (warp id mod 4), so two warps share each quarter and
+//               split the tile's columns), bias / activation / residual in registers, packed
+//               stores to C
 // Two accumulators of BN columns live in TMEM so the epilogue of tile i overlaps the
 // main loop of tile i+1. fp32 inputs use kind::tf32 on a hi/lo split prepared by a
 // pre-pass (3 MMAs per k-step: lo*hi, hi*lo, hi*hi).
@@ -41,7 +43,9 @@ namespace cgb {
 constexpr int kBM = 128;            // rows per tile = TMEM lanes
 constexpr int kRowBytes = 128;      // bytes of K per row per stage (one swizzle span)
 constexpr int kUmmaKBytes = 32;     // bytes of K one tcgen05.mma consumes per row
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;
+constexpr int kEpilogueWarps = 8;
+constexpr int kEpilogueStagingBytes = kEpilogueWarps * 4096;   // 32 rows x 128 bytes per epilogue warp
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 224 * 1024;
 constexpr uint32_t kTmemCols = 512;
@@ -54,6 +58,12 @@ struct GemmParams {
     const void* bias;
     const void* residual;
     void* C;
+    // Fused all-gather: every output tile is also stored into the same position of up to 7 peer
+    // buffers (other GPUs' copies of C, mapped into this process), at `dst_row_offset` elements from
+    // their base as in the local C. n_peer == 0 for a plain GEMM.
+    void* peer[7];
+    int n_peer;
+    long long dst_row_offset;
     int epilogue;
     float alpha;
     int b_mn_major;       // 1: B is [K, N] row-major (N contiguous); 0: B is [N, K]
@@ -285,9 +295,9 @@ struct StageLayout {
     static constexpr int kABytes = kBM * kRowBytes;      // 16 KiB
     static constexpr int kBBytes = BNL * kRowBytes;
     static constexpr int kStageBytes = kCopies * (kABytes + kBBytes);
-    static constexpr int kStagesFit = kSmemBudget / kStageBytes;
+    static constexpr int kStagesFit = (kSmemBudget - kEpilogueStagingBytes) / kStageBytes;
     static constexpr int kStages = kStagesFit > kMaxStages ? kMaxStages : kStagesFit;
-    static constexpr int kDynSmem = kStages * kStageBytes + 1024;   // + alignment slack
+    static constexpr int kDynSmem = kStages * kStageBytes + kEpilogueStagingBytes + 1024;   // + alignment slack
     static_assert(kStages >= 2, "at least a double buffer");
 };
 
@@ -330,7 +340,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&bar_acc_full[a]), 1);
-            mbar_init(smem_u32(&bar_acc_empty[a]), 4 * kCta);
+            mbar_init(smem_u32(&bar_acc_empty[a]), kEpilogueWarps * kCta);
         }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -494,8 +504,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             }
         }
     } else {
-        // ---------------- epilogue (warps 2..5; TMEM lane quarter = warp id mod 4) ----------------
+        // ---------------- epilogue (warps 2..9; TMEM lane quarter = warp id mod 4) ----------------
         const int q = warp & 3;
+        const int col_half = (warp - 2) >> 2;   // warps 2-5 take the first half of the columns, 6-9 the second
         const int row_in_tile = q * 32 + lane;
         int acc = 0;
         uint32_t acc_phase = 0;
@@ -508,6 +519,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         const bool has_res = epi == CG_B200_EPI_BIAS_RESIDUAL || epi == CG_B200_EPI_RESIDUAL;
         const bool bias_vec = has_bias && ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
         constexpr int kPack = 16 / sizeof(OutT);  // elements per 16-byte store
+        constexpr int kRowPieces = 32 / kPack;    // 16-byte pieces per row of a 32-column chunk
+        uint8_t* const stg = smem_raw + (smem_base - smem_u32(smem_raw)) + kStages * L::kStageBytes + (warp - 2) * 4096;
         for (long long tile = tile_first; tile < p.num_tiles; tile += tile_step) {
             bool ok = mbar_wait(smem_u32(&bar_acc_full[acc]), acc_phase, &abort_flag, p.err_word, 0x400u + acc,
                                 2000000000ull, 200);
@@ -518,8 +531,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             const long long m = (long long)t.m0 + (long long)cta_rank * kBM + row_in_tile;
             const bool row_ok = m < p.M;
             const long long row_off = (long long)(t.b % p.batch_in) * p.c_stride_in + (long long)(t.b / p.batch_in) * p.c_stride_out + m * p.ldc;
+            const int c_lo = col_half * (t.width >> 1), c_hi = c_lo + (t.width >> 1);
 #pragma unroll 1
-            for (int c0 = 0; c0 < t.width; c0 += 32) {
+            for (int c0 = c_lo; c0 < c_hi; c0 += 32) {
                 float v[32];
                 __syncwarp();  // lanes that skipped stores rejoin before the warp-wide TMEM load
                 if (p.num_kb > 0) {
@@ -556,10 +570,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = gelu_epilogue<OutT>(v[j]);
                 }
-                if (!row_ok) continue;
-                OutT* crow = Cbase + row_off + n0;
                 if (full) {
-                    if (has_res) {
+                    if (has_res && row_ok) {
                         const OutT* rrow = Rbase + row_off + n0;
 #pragma unroll
                         for (int g = 0; g < 32 / kPack; ++g) {
@@ -568,20 +580,44 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                             for (int j = 0; j < kPack; ++j) v[g * kPack + j] += Elem<OutT>::to_f32(rv.v[j]);
                         }
                     }
+                    // Transpose through shared memory so that global (and peer) stores are whole row
+                    // segments: lane = row writes its kRowPieces 16-byte pieces, then the warp reads the
+                    // pieces back in linear order, 32 consecutive pieces per store instruction. Piece P
+                    // sits at P ^ ((P >> 3) & 7): conflict-free in both directions.
 #pragma unroll
-                    for (int g = 0; g < 32 / kPack; ++g) {
+                    for (int g = 0; g < kRowPieces; ++g) {
                         Vec16<OutT> o;
 #pragma unroll
                         for (int j = 0; j < kPack; ++j) o.v[j] = Elem<OutT>::from_f32(v[g * kPack + j]);
-                        *reinterpret_cast<int4*>(crow + g * kPack) = *reinterpret_cast<const int4*>(&o);
+                        const int P = lane * kRowPieces + g;
+                        *reinterpret_cast<int4*>(stg + ((P ^ ((P >> 3) & 7)) << 4)) = *reinterpret_cast<const int4*>(&o);
                     }
-                } else {
+                    __syncwarp();
+                    const long long m_base = (long long)t.m0 + (long long)cta_rank * kBM + q * 32;
+                    const long long tile_off = row_off - m * p.ldc + p.dst_row_offset + n0;   // batch part + column
+#pragma unroll
+                    for (int i = 0; i < kRowPieces; ++i) {
+                        const int P = i * 32 + lane;
+                        const int r = P / kRowPieces, ch = P % kRowPieces;
+                        const int4 val = *reinterpret_cast<const int4*>(stg + ((P ^ ((P >> 3) & 7)) << 4));
+                        if (m_base + r < p.M) {
+                            const long long off = tile_off + (m_base + r) * p.ldc + ch * kPack;
+                            *reinterpret_cast<int4*>(Cbase + off) = val;
+                            for (int d = 0; d < p.n_peer; ++d)
+                                *reinterpret_cast<int4*>(static_cast<OutT*>(p.peer[d]) + off) = val;
+                        }
+                    }
+                    __syncwarp();   // the staging buffer is reused by the next chunk
+                } else if (row_ok) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
                         if (n0 + j < p.N) {
                             float r = v[j];
                             if (has_res) r += Elem<OutT>::to_f32(Rbase[row_off + n0 + j]);
-                            crow[j] = Elem<OutT>::from_f32(r);
+                            const OutT o = Elem<OutT>::from_f32(r);
+                            const long long off = row_off + p.dst_row_offset + n0 + j;
+                            Cbase[off] = o;
+                            for (int d = 0; d < p.n_peer; ++d) static_cast<OutT*>(p.peer[d])[off] = o;
                         }
                 }
             }
@@ -880,9 +916,14 @@ extern "C" int cg_b200_gemm_workspace_bytes(const cg_b200_gemm_desc* desc, size_
 // Shared body of the GEMM entry points. `shared_err_word`: report bounded-wait timeouts through
 // the library's per-device error word (allocated on first use); otherwise through `err_word`
 // (may be null).
+struct PeerSet {
+    void* const* peer_c = nullptr;   // `world` pointers to the peers' full C buffers (entry `rank` is skipped)
+    int world = 1, rank = 0;
+};
+
 static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B, const void* bias,
                     const void* residual, void* C, void* workspace, size_t workspace_bytes, void* stream,
-                    bool shared_err_word, uint32_t* err_word) {
+                    bool shared_err_word, uint32_t* err_word, const PeerSet* peers = nullptr) {
     int st = validate_desc(desc);
     if (st) return st;
     const cg_b200_gemm_desc& d = *desc;
@@ -929,6 +970,13 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
     p.c_stride_in = two ? d.inner_stride_c : d.batch_stride_c;
     p.c_stride_out = two ? d.batch_stride_c : 0;
     p.bias = bias; p.residual = residual; p.C = C;
+    if (peers && peers->world > 1) {
+        // C is the base of the full [world * M, N] buffer: this rank's rows start `rank * M` rows in,
+        // in the local buffer and in every peer's
+        p.dst_row_offset = (long long)peers->rank * d.M * d.ldc;
+        for (int r = 0; r < peers->world; ++r)
+            if (r != peers->rank) p.peer[p.n_peer++] = peers->peer_c[r];
+    }
     p.epilogue = epi; p.alpha = d.alpha;
     p.b_mn_major = (d.b_transposed || sp.active) ? 0 : 1;   // the fp32 workspace copy of B is K-contiguous
     const long long a_s_in = two ? d.inner_stride_a : d.batch_stride_a, a_s_out = two ? d.batch_stride_a : 0;
@@ -1078,4 +1126,23 @@ extern "C" int cg_b200_gemm_f32_static(const cg_b200_gemm_desc* desc, const void
     // nothing left over from an earlier call can leak into this one.
     return gemm_run(desc, A, B, bias, residual, C, scratch, (size_t)CG_B200_GEMM_F32_STATIC_SCRATCH_BYTES, stream,
                     false, dev_error_word);
+}
+
+// ---- GEMM fused with the all-gather of its M-sharded output ------------------------------------------
+extern "C" int cg_b200_gemm_allgather(const cg_b200_gemm_desc* desc, const void* A, const void* B, const void* bias,
+                                      const void* residual, void* C_full, void* const* peer_C, int world, int rank,
+                                      void* workspace, size_t workspace_bytes, void* stream) {
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return CG_B200_ERR_INVALID_ARG;
+    if (!desc) return CG_B200_ERR_NULL_POINTER;
+    if (desc->batch != 1) return CG_B200_ERR_UNSUPPORTED;   // the shards are row blocks of one matrix
+    if (world > 1) {
+        if (!peer_C) return CG_B200_ERR_NULL_POINTER;
+        for (int r = 0; r < world; ++r)
+            if (r != rank && (!peer_C[r] || !aligned_to(peer_C[r], 16))) return peer_C[r] ? CG_B200_ERR_MISALIGNED : CG_B200_ERR_NULL_POINTER;
+    }
+    PeerSet ps;
+    ps.peer_c = peer_C;
+    ps.world = world;
+    ps.rank = rank;
+    return gemm_run(desc, A, B, bias, residual, C_full, workspace, workspace_bytes, stream, true, nullptr, &ps);
 }

@@ -237,6 +237,30 @@ int cg_b200_event_elapsed_sec(void* earlier, void* later, double* seconds) {
     return CG_B200_OK;
 }
 
+int cg_b200_ipc_export(const void* dev_ptr, void* host_handle) {
+    if (!dev_ptr || !host_handle) return CG_B200_ERR_NULL_POINTER;
+    static_assert(sizeof(cudaIpcMemHandle_t) == CG_B200_IPC_HANDLE_BYTES, "handle size");
+    cudaIpcMemHandle_t h;
+    CGB_CUDA(cudaIpcGetMemHandle(&h, const_cast<void*>(dev_ptr)));
+    memcpy(host_handle, &h, sizeof(h));
+    return CG_B200_OK;
+}
+
+int cg_b200_ipc_open(const void* host_handle, void** peer_ptr) {
+    if (!host_handle || !peer_ptr) return CG_B200_ERR_NULL_POINTER;
+    *peer_ptr = nullptr;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, host_handle, sizeof(h));
+    CGB_CUDA(cudaIpcOpenMemHandle(peer_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return CG_B200_OK;
+}
+
+int cg_b200_ipc_close(void* peer_ptr) {
+    if (!peer_ptr) return CG_B200_OK;
+    CGB_CUDA(cudaIpcCloseMemHandle(peer_ptr));
+    return CG_B200_OK;
+}
+
 int cg_b200_last_device_error(void* stream, uint32_t* word) {
     if (!word) return CG_B200_ERR_NULL_POINTER;
     *word = 0;

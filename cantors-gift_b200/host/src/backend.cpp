@@ -206,7 +206,7 @@ std::unique_ptr<Executable> NvidiaBackend::compile(const CGModule& module) {
             std::memcpy(&r, rec->data(), sizeof(r));
             plan.records.push_back(r);
             if (r.kind == PlanRecord::Gemm) {
-                exe->threads_per_block = 192;
+                exe->threads_per_block = 320;
                 exe->shared_mem_bytes = 225 * 1024;
             } else if (exe->threads_per_block == 0) {
                 exe->threads_per_block = r.kind == PlanRecord::Eltwise ? 256 : 128;

@@ -163,7 +163,7 @@ static void test_backend_and_cache() {
     for (const char* tok : {".version", ".target sm_100a", ".entry mlp", "cg_b200_gemm"})
         CHECK(exe->ptx_text.find(tok) != std::string::npos);
     CHECK(backend.emit_text(cg)->find("mlp") != std::string::npos);
-    CHECK(exe->threads_per_block == 192 && exe->shared_mem_bytes > 0);
+    CHECK(exe->threads_per_block == 320 && exe->shared_mem_bytes > 0);
     auto plan = LaunchPlan::deserialize(exe->machine_code);
     CHECK(plan && plan->n_inputs == 5 && plan->n_outputs == 1 && plan->records.size() == 2 && plan->buffers.size() == 7);
     CHECK(plan->workspace_bytes > 0);   // fp32 GEMMs need the split workspace
@@ -204,7 +204,7 @@ static void test_backend_and_cache() {
         Runtime rt2(dir.string());   // cold memory cache: must come from disk
         auto hit = rt2.kernel_cache().lookup(key);
         CHECK(hit && (*hit)->machine_code == r1.executable->machine_code && (*hit)->ptx_text == r1.executable->ptx_text);
-        CHECK(hit && (*hit)->entrypoints == r1.executable->entrypoints && (*hit)->threads_per_block == 192);
+        CHECK(hit && (*hit)->entrypoints == r1.executable->entrypoints && (*hit)->threads_per_block == 320);
         CHECK(hit && (*hit)->target_device == DeviceId::cuda());
         CHECK(!rt2.kernel_cache().lookup(key + 1));
         // bind fails (null) without a registered device, and for a CPU device id

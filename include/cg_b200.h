@@ -280,7 +280,31 @@ int cg_b200_comm_unique_id(void* host_unique_id);
 int cg_b200_comm_init_rank(void** comm, int world, int rank, const void* host_unique_id);
 /* buf holds world * shard_bytes; rank r's shard already sits at buf + r * shard_bytes. */
 int cg_b200_allgather_inplace(void* comm, void* buf, size_t shard_bytes, void* stream);
+/* Stream-ordered barrier over the communicator: work enqueued after it on `stream` starts only
+ * once every rank's stream has reached its own call. */
+int cg_b200_comm_barrier(void* comm, void* stream);
 int cg_b200_comm_destroy(void* comm);
+
+/* ---- GEMM fused with the all-gather of its output ---------------------------------------------
+ * The M-sharded GEMM and the collective that follows it as ONE kernel: rank `rank` of `world`
+ * computes its desc->M rows and its epilogue stores every tile into rows [rank*M, (rank+1)*M) of
+ * the full [world*M, N] buffer - the local one (C_full) and, through peer mappings over NVLink,
+ * every other rank's (peer_C[r], r != rank; entry `rank` is ignored). The stores are whole row
+ * segments spread over the kernel's run time, so the transfer overlaps the math tile by tile;
+ * plain peer stores only (no multicast). When the kernel and a cg_b200_comm_barrier after it have
+ * completed on a rank, that rank's buffer holds all world*M rows. bias is [N]; residual, if
+ * used, is this rank's [M, N] block (row stride ldc). batch must be 1, world <= 8.
+ * Peer pointers come from cg_b200_ipc_export on the owning process (of memory allocated with
+ * cg_b200_malloc) and cg_b200_ipc_open here. No counterpart in the reference (it has no
+ * multi-device execution). */
+#define CG_B200_IPC_HANDLE_BYTES 64
+int cg_b200_ipc_export(const void* dev_ptr, void* host_handle);
+int cg_b200_ipc_open(const void* host_handle, void** peer_ptr);
+int cg_b200_ipc_close(void* peer_ptr);
+int cg_b200_gemm_allgather(const cg_b200_gemm_desc* desc, const void* A, const void* B,
+                           const void* bias, const void* residual, void* C_full,
+                           void* const* peer_C, int world, int rank, void* workspace,
+                           size_t workspace_bytes, void* stream);
 
 #if defined(__GNUC__)
 #pragma GCC visibility pop

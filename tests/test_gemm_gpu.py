@@ -183,6 +183,37 @@ def test_two_level_batch_strided_operands(ops, cgb, oracle):
     assert_close(_host_f32(O, ctx, capi.BF16), want2, 1e-2, "PV two-level batch")
 
 
+def test_fused_allgather_writes_every_destination(ops, cgb, oracle):
+    """cg_b200_gemm_allgather on one GPU, the two 'peers' being other local buffers: rank 1 of 3 must
+    put its rows into rows [M, 2M) of all three full-size buffers and touch nothing else."""
+    import ctypes as C
+    import torch
+    capi, O = cgb.capi, oracle
+    M, N, K, world, rank = 200, 328, 136, 3, 1   # ragged in M (tile tail) and N (partial 32-column chunk)
+    ldc = 336
+    rng = np.random.default_rng(12)
+    A = O.to_bf16(rng.standard_normal((M, K), dtype=np.float32) * 0.1)
+    B = O.to_bf16(rng.standard_normal((K, N), dtype=np.float32) * 0.1)
+    bias = O.to_bf16(rng.standard_normal(N, dtype=np.float32))
+    od = O.make_gemm_desc(M, N, K, O.BF16, O.BF16, epilogue="bias_gelu_tanh", ldc=ldc)
+    want = O.from_bf16(O.gemm(od, A, B, bias=bias, out=np.zeros(M * ldc, dtype=np.uint16))).reshape(M, ldc)[:, :N]
+    dev = lambda h: torch.from_numpy(h.view(np.int16)).cuda().view(torch.bfloat16)  # noqa: E731
+    bufs = [torch.zeros(world * M, ldc, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    peers = (C.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    gd = capi.make_gemm_desc(M, N, K, capi.BF16, capi.BF16, epilogue="bias_gelu_tanh", ldc=ldc)
+    Ad, Bd, bd = dev(A), dev(B), dev(bias)
+    st = cgb.lib().cg_b200_gemm_allgather(C.byref(gd), C.c_void_p(Ad.data_ptr()), C.c_void_p(Bd.data_ptr()),
+                                          C.c_void_p(bd.data_ptr()), None, C.c_void_p(bufs[rank].data_ptr()), peers,
+                                          world, rank, None, 0, C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    capi.check(st, "gemm_allgather")
+    assert ops.last_device_error() == 0
+    for b in bufs:
+        full = _host_f32(O, b.view(-1), capi.BF16).reshape(world * M, ldc)
+        assert_close(full[rank * M:(rank + 1) * M, :N], want, 1e-2, "fused all-gather rows")
+        assert not full[:rank * M].any() and not full[(rank + 1) * M:].any() and not full[:, N:].any()
+    assert torch.equal(bufs[0], bufs[1]) and torch.equal(bufs[1], bufs[2])
+
+
 def test_k_zero_gives_epilogue_of_zero(ops, cgb, oracle):
     capi = cgb.capi
     got, want = run_case(ops, cgb, oracle, 130, 72, 0, capi.BF16, capi.BF16, epilogue="bias")
