@@ -271,6 +271,7 @@ class GemmWorkload(Workload):
                 f"M-sharded x{world}, in-place NCCL all-gather of C"}
 
     def setup(self, rank, world):
+        import ctypes as C
         import torch
         from cantors_gift_b200 import capi
         from cantors_gift_b200.sharding import padded_rows
@@ -305,6 +306,10 @@ class GemmWorkload(Workload):
             # C buffers from the C ABI allocator (plain cudaMalloc, so they can be exported) and every
             # peer's copy mapped here: the GEMM epilogue stores its rows into all of them
             self.C_raw, self.peer_tables = share_buffers(rank, world, self.sets, self.M * self.N * self.C[0].element_size())
+            _, flag_tables = share_buffers(rank, world, 1, 256)
+            self.barrier = C.c_void_p()
+            capi.check(capi.lib().cg_b200_peer_barrier_create(C.byref(self.barrier), flag_tables[0], world, rank),
+                       "peer_barrier_create")
         self.launches_per_step = 1 if self.in_dtype_name == "BF16" else 3
 
     def step(self, i):
@@ -318,7 +323,7 @@ class GemmWorkload(Workload):
             capi.check(capi.lib().cg_b200_gemm_allgather(
                 C.byref(self.desc), p(self.A[s]), p(self.B[s]), p(self.bias) if self.epilogue != "none" else None, None,
                 self.C_raw[s], self.peer_tables[s], self.world, self.rank, p(self.ws), self.ws_bytes, st), "gemm_allgather")
-            capi.check(capi.lib().cg_b200_comm_barrier(self.comm, st), "comm_barrier")
+            capi.check(capi.lib().cg_b200_peer_barrier(self.barrier, st), "peer_barrier")
             return
         c_shard = self.C[s][self.rank * self.Ms:(self.rank + 1) * self.Ms]
         ops.gemm(self.desc, self.A[s], self.B[s], c_shard, bias=self.bias if self.epilogue != "none" else None,

@@ -104,6 +104,9 @@ SIGNATURES = {
     "cg_b200_allgather_inplace": (_i, [_vp, _vp, _sz, _vp]),
     "cg_b200_comm_barrier": (_i, [_vp, _vp]),
     "cg_b200_comm_destroy": (_i, [_vp]),
+    "cg_b200_peer_barrier_create": (_i, [_vpp, _vpp, _i, _i]),
+    "cg_b200_peer_barrier": (_i, [_vp, _vp]),
+    "cg_b200_peer_barrier_destroy": (_i, [_vp]),
     "cg_b200_ipc_export": (_i, [_vp, _vp]),
     "cg_b200_ipc_open": (_i, [_vp, _vpp]),
     "cg_b200_ipc_close": (_i, [_vp]),

@@ -59,9 +59,84 @@ struct Comm {
     void* token = nullptr;   // world * 8 bytes for cg_b200_comm_barrier
 };
 
+// ---- flag barrier over peer memory ------------------------------------------------------------------
+// One 64-bit slot per rank in every rank's flag buffer. A barrier is one tiny kernel: lane r
+// publishes this rank's epoch into rank r's buffer (release at system scope, after a system fence
+// that orders the preceding kernel's peer stores before it) and then waits, bounded, until rank r's
+// epoch has arrived in the local buffer. The kernels that wait on each other run on different GPUs.
+struct PeerBarrier {
+    unsigned long long* table_dev = nullptr;   // device copy of the `world` flag-buffer pointers
+    int world = 1, rank = 0;
+    unsigned long long epoch = 0;
+};
+
+__global__ void peer_barrier_kernel(unsigned long long* const* flags, int world, int rank, unsigned long long epoch,
+                                    uint32_t* err_word) {
+    const int r = threadIdx.x;
+    if (r >= world || r == rank) return;
+    __threadfence_system();
+    unsigned long long* remote = flags[r] + rank;
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(remote), "l"(epoch) : "memory");
+    const unsigned long long* mine = flags[rank] + r;
+    unsigned long long t0 = 0, seen = 0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (uint32_t it = 0;; ++it) {
+        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(mine) : "memory");
+        if (seen >= epoch) break;
+        if ((it & 0x3f) == 0x3f) {
+            unsigned long long t1;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (t1 - t0 > 2000000000ull) {   // a peer never arrived: report and return
+                if (err_word) atomicCAS(err_word, 0u, 0x500u + (uint32_t)r);
+                break;
+            }
+            __nanosleep(100);
+        }
+    }
+}
+
 }  // namespace cgb
 
 using namespace cgb;
+
+extern "C" int cg_b200_peer_barrier_create(void** barrier, void* const* flag_buffers, int world, int rank) {
+    if (!barrier || !flag_buffers) return CG_B200_ERR_NULL_POINTER;
+    *barrier = nullptr;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return CG_B200_ERR_INVALID_ARG;
+    for (int r = 0; r < world; ++r)
+        if (!flag_buffers[r] || !aligned_to(flag_buffers[r], 8)) return flag_buffers[r] ? CG_B200_ERR_MISALIGNED : CG_B200_ERR_NULL_POINTER;
+    int st = require_sm100();
+    if (st) return st;
+    PeerBarrier* b = new PeerBarrier;
+    b->world = world;
+    b->rank = rank;
+    if (cudaMalloc(&b->table_dev, 8 * sizeof(void*)) != cudaSuccess ||
+        cudaMemcpy(b->table_dev, flag_buffers, (size_t)world * sizeof(void*), cudaMemcpyHostToDevice) != cudaSuccess) {
+        delete b;
+        return CG_B200_ERR_CUDA;
+    }
+    *barrier = b;
+    return CG_B200_OK;
+}
+
+extern "C" int cg_b200_peer_barrier(void* barrier, void* stream) {
+    if (!barrier) return CG_B200_ERR_NULL_POINTER;
+    PeerBarrier* b = static_cast<PeerBarrier*>(barrier);
+    ++b->epoch;
+    if (b->world == 1) return CG_B200_OK;
+    peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(reinterpret_cast<unsigned long long* const*>(b->table_dev), b->world,
+                                                             b->rank, b->epoch, device_error_word());
+    CGB_CUDA(cudaGetLastError());
+    return CG_B200_OK;
+}
+
+extern "C" int cg_b200_peer_barrier_destroy(void* barrier) {
+    if (!barrier) return CG_B200_OK;
+    PeerBarrier* b = static_cast<PeerBarrier*>(barrier);
+    if (b->table_dev) cudaFree(b->table_dev);
+    delete b;
+    return CG_B200_OK;
+}
 
 extern "C" int cg_b200_comm_unique_id(void* host_unique_id) {
     if (!host_unique_id) return CG_B200_ERR_NULL_POINTER;

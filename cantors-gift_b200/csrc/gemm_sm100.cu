@@ -840,7 +840,7 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& ta_lo, const
     // persistent: one CTA (or CTA pair) per SM (or SM pair), never more CTAs than tiles
     const long long slots = sm_count() / kCta;
     p.full_units = p.num_tiles;
-    if (kCta == 2 && !kSplit && tail_split_enabled()) {
+    if (kCta == 2 && BN == 256 && !kSplit && tail_split_enabled()) {
         // a last partial wave of r <= slots / 2 tiles runs as 2r half-width units instead
         const long long r = p.num_tiles % slots;
         if (r > 0 && 2 * r <= slots) {
@@ -872,7 +872,7 @@ template <int kCta, bool kTF32, bool kSplit, typename OutT>
 static int launch_bn(int bn, const CUtensorMap& ta, const CUtensorMap& ta_lo, const CUtensorMap& tb,
                      const CUtensorMap& tb_lo, GemmParams& p, cudaStream_t s) {
     if constexpr (kCta == 2) {
-        (void)bn;   // the pair variant is built for the 256-wide tile only
+        if (bn == 128) return launch_variant<2, kTF32, kSplit, 128, OutT>(ta, ta_lo, tb, tb_lo, p, s);
         return launch_variant<2, kTF32, kSplit, 256, OutT>(ta, ta_lo, tb, tb_lo, p, s);
     } else if constexpr (kSplit) {
         (void)bn;
@@ -992,9 +992,15 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
     }
 
     const bool tf32 = d.in_dtype == CG_B200_F32;
-    const int bn = choose_bn(desc, sp.active && sp.copies == 2);
+    int bn = choose_bn(desc, sp.active && sp.copies == 2);
     // CTA pairs (256 x 256 tiles) for 16-bit inputs once the problem spans more than one such tile row
     const int cta = (!tf32 && bn == 256 && d.M > kBM && pair_enabled()) ? 2 : 1;
+    if (cta == 2) {
+        // too few 256 x 256 tiles to occupy half of the SM pairs (a small shard of a sharded GEMM):
+        // halve the tile width so that twice as many pairs have work
+        const long long tiles = ((d.M + 2 * kBM - 1) / (2 * kBM)) * ((d.N + 255) / 256) * d.batch;
+        if (2 * tiles <= sm_count() / 2) bn = 128;
+    }
     p.idesc = make_idesc(d.in_dtype, tf32, p.b_mn_major != 0, kBM * cta, bn);
     p.idesc_half = make_idesc(d.in_dtype, tf32, p.b_mn_major != 0, kBM * cta, bn / 2);
     const uint32_t box_k = (uint32_t)(kRowBytes / in_sz);

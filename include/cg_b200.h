@@ -301,6 +301,14 @@ int cg_b200_comm_destroy(void* comm);
 int cg_b200_ipc_export(const void* dev_ptr, void* host_handle);
 int cg_b200_ipc_open(const void* host_handle, void** peer_ptr);
 int cg_b200_ipc_close(void* peer_ptr);
+/* Stream-ordered barrier through flags in peer memory (a few microseconds; the NCCL barrier above
+ * costs a small collective). flag_buffers[r] is rank r's flag buffer (at least 8 * world bytes,
+ * zeroed once before the first barrier; entry `rank` is the local one, the others are peer
+ * mappings). Every rank must call the barrier the same number of times. A peer that does not arrive
+ * within 2 s is reported through cg_b200_last_device_error (code 0x500 + rank) and the wait ends. */
+int cg_b200_peer_barrier_create(void** barrier, void* const* flag_buffers, int world, int rank);
+int cg_b200_peer_barrier(void* barrier, void* stream);
+int cg_b200_peer_barrier_destroy(void* barrier);
 int cg_b200_gemm_allgather(const cg_b200_gemm_desc* desc, const void* A, const void* B,
                            const void* bias, const void* residual, void* C_full,
                            void* const* peer_C, int world, int rank, void* workspace,
