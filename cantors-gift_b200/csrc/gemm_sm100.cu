@@ -520,6 +520,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         const bool bias_vec = has_bias && ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
         constexpr int kPack = 16 / sizeof(OutT);  // elements per 16-byte store
         constexpr int kRowPieces = 32 / kPack;    // 16-byte pieces per row of a 32-column chunk
+        constexpr int kSub = 8 / kRowPieces;      // chunks per 128-byte staging row (2 for 16-bit outputs)
         uint8_t* const stg = smem_raw + (smem_base - smem_u32(smem_raw)) + kStages * L::kStageBytes + (warp - 2) * 4096;
         for (long long tile = tile_first; tile < p.num_tiles; tile += tile_step) {
             bool ok = mbar_wait(smem_u32(&bar_acc_full[acc]), acc_phase, &abort_flag, p.err_word, 0x400u + acc,
@@ -532,6 +533,28 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             const bool row_ok = m < p.M;
             const long long row_off = (long long)(t.b % p.batch_in) * p.c_stride_in + (long long)(t.b / p.batch_in) * p.c_stride_out + m * p.ldc;
             const int c_lo = col_half * (t.width >> 1), c_hi = c_lo + (t.width >> 1);
+            int staged = 0;            // 32-column chunks waiting in the staging rows
+            long long staged_n0 = 0;   // first column of the staged data
+            const long long m_base = (long long)t.m0 + (long long)cta_rank * kBM + q * 32;
+            const long long tile_off = row_off - m * p.ldc + p.dst_row_offset;   // batch part of the offset
+            auto flush = [&]() {
+                if (staged == 0) return;
+                __syncwarp();
+                const int sh = staged * kRowPieces == 8 ? 3 : 2;   // pieces per row present: 8 or 4
+                const int total = 32 << sh;
+                for (int idx = lane; idx < total; idx += 32) {
+                    const int r = idx >> sh, c = idx & ((1 << sh) - 1);
+                    const int4 val = *reinterpret_cast<const int4*>(stg + ((r * 8 + (c ^ (r & 7))) << 4));
+                    if (m_base + r < p.M) {
+                        const long long off = tile_off + (m_base + r) * p.ldc + staged_n0 + c * kPack;
+                        *reinterpret_cast<int4*>(Cbase + off) = val;
+                        for (int d = 0; d < p.n_peer; ++d)
+                            *reinterpret_cast<int4*>(static_cast<OutT*>(p.peer[d]) + off) = val;
+                    }
+                }
+                __syncwarp();   // the staging rows are free again
+                staged = 0;
+            };
 #pragma unroll 1
             for (int c0 = c_lo; c0 < c_hi; c0 += 32) {
                 float v[32];
@@ -581,34 +604,24 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                         }
                     }
                     // Transpose through shared memory so that global (and peer) stores are whole row
-                    // segments: lane = row writes its kRowPieces 16-byte pieces, then the warp reads the
-                    // pieces back in linear order, 32 consecutive pieces per store instruction. Piece P
-                    // sits at P ^ ((P >> 3) & 7): conflict-free in both directions.
+                    // segments: lane = row writes its 16-byte pieces into a 128-byte staging row (two
+                    // 32-column chunks side by side for 16-bit outputs), flush() then moves the pieces out
+                    // in linear order, 128 contiguous bytes of a row per 8 lanes. Piece c of row r sits at
+                    // slot c ^ (r & 7): conflict-free in both directions.
+                    if (staged == 0) staged_n0 = n0;
 #pragma unroll
                     for (int g = 0; g < kRowPieces; ++g) {
                         Vec16<OutT> o;
 #pragma unroll
                         for (int j = 0; j < kPack; ++j) o.v[j] = Elem<OutT>::from_f32(v[g * kPack + j]);
-                        const int P = lane * kRowPieces + g;
-                        *reinterpret_cast<int4*>(stg + ((P ^ ((P >> 3) & 7)) << 4)) = *reinterpret_cast<const int4*>(&o);
+                        const int c = staged * kRowPieces + g;
+                        *reinterpret_cast<int4*>(stg + ((lane * 8 + (c ^ (lane & 7))) << 4)) = *reinterpret_cast<const int4*>(&o);
                     }
-                    __syncwarp();
-                    const long long m_base = (long long)t.m0 + (long long)cta_rank * kBM + q * 32;
-                    const long long tile_off = row_off - m * p.ldc + p.dst_row_offset + n0;   // batch part + column
-#pragma unroll
-                    for (int i = 0; i < kRowPieces; ++i) {
-                        const int P = i * 32 + lane;
-                        const int r = P / kRowPieces, ch = P % kRowPieces;
-                        const int4 val = *reinterpret_cast<const int4*>(stg + ((P ^ ((P >> 3) & 7)) << 4));
-                        if (m_base + r < p.M) {
-                            const long long off = tile_off + (m_base + r) * p.ldc + ch * kPack;
-                            *reinterpret_cast<int4*>(Cbase + off) = val;
-                            for (int d = 0; d < p.n_peer; ++d)
-                                *reinterpret_cast<int4*>(static_cast<OutT*>(p.peer[d]) + off) = val;
-                        }
-                    }
-                    __syncwarp();   // the staging buffer is reused by the next chunk
-                } else if (row_ok) {
+                    ++staged;
+                    if (staged == kSub || c0 + 32 >= c_hi) flush();
+                } else {
+                    flush();   // a staged full chunk goes out before the ragged one
+                    if (row_ok) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
                         if (n0 + j < p.N) {
@@ -619,8 +632,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                             Cbase[off] = o;
                             for (int d = 0; d < p.n_peer; ++d) static_cast<OutT*>(p.peer[d])[off] = o;
                         }
+                    }
                 }
             }
+            flush();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
