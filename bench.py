@@ -442,6 +442,7 @@ class BlockWorkload(Workload):
         self.x = x[rank * self.Bs:(rank + 1) * self.Bs].contiguous()
         self.y = torch.empty(self.B, self.S, D, device="cuda", dtype=torch.bfloat16)
         self.comm = make_comm(rank, world) if world > 1 else None
+        self.launches_per_step = self.block.launches_per_forward
 
     def step(self, i):
         import ctypes as C

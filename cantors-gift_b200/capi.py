@@ -65,6 +65,16 @@ class GemmDesc(C.Structure):
                 ("inner_stride_c", C.c_int64)]
 
 
+class AttentionDesc(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("head_dim", C.c_int32), ("batch", C.c_int64), ("heads", C.c_int64),
+                ("seq_q", C.c_int64), ("seq_kv", C.c_int64),
+                ("ldq", C.c_int64), ("ldk", C.c_int64), ("ldv", C.c_int64), ("ldo", C.c_int64),
+                ("head_stride_q", C.c_int64), ("head_stride_k", C.c_int64), ("head_stride_v", C.c_int64),
+                ("head_stride_o", C.c_int64), ("batch_stride_q", C.c_int64), ("batch_stride_k", C.c_int64),
+                ("batch_stride_v", C.c_int64), ("batch_stride_o", C.c_int64), ("scale", C.c_float),
+                ("reserved", C.c_int32)]
+
+
 _vp, _vpp, _sz, _i, _i64 = C.c_void_p, C.POINTER(C.c_void_p), C.c_size_t, C.c_int, C.c_int64
 
 # name -> (restype, argtypes); exactly the declarations of include/cg_b200.h
@@ -95,6 +105,7 @@ SIGNATURES = {
     "cg_b200_softmax": (_i, [_i, _vp, _vp, _i64, _i64, _vp]),
     "cg_b200_layernorm": (_i, [_i, _vp, _vp, _vp, C.c_float, _vp, _i64, _i64, _vp]),
     "cg_b200_softmax_layernorm": (_i, [_i, _vp, _vp, _vp, C.c_float, _vp, _i64, _i64, _vp]),
+    "cg_b200_attention": (_i, [C.POINTER(AttentionDesc), _vp, _vp, _vp, _vp, _vp]),
     "cg_b200_gemm_workspace_bytes": (_i, [C.POINTER(GemmDesc), C.POINTER(_sz)]),
     "cg_b200_gemm": (_i, [C.POINTER(GemmDesc), _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "cg_b200_last_device_error": (_i, [_vp, C.POINTER(C.c_uint32)]),

@@ -1,0 +1,379 @@
+// attention_sm100.cu - softmax(Q K^T * scale) V per head in one kernel (tcgen05 + TMEM).
+//
+// The reference only annotates this pattern (pattern:"attention",
+// src/optimization/graph/graph_pattern.cpp:61-85) and executes nothing; unfused it is three ops of
+// the path - matmul, softmax, matmul (src/ir/ops.cpp) - whose [B, H, S, S] intermediate makes three
+// trips through HBM. Here the scores never leave the SM.
+//
+// One CTA per (batch, head, 128 query rows), 192 threads:
+//   warp 0     TMA: the Q tile once, then K and V tiles of 128 key rows through a 3-stage ring
+//   warp 1     one thread issues S_j = Q K_j^T (128 x 128 x 64) into one of two TMEM score buffers and
+//              T_j = P_j V_j (128 x 64 x 128) into one of two TMEM output-tile buffers; S_{j+1} is
+//              issued before T_j so the tensor pipe works while the softmax warps do
+//   warps 2-5  thread = query row: two passes over S_j in TMEM (row max, then p = 2^(s - m), row sum),
+//              P_j written as bf16/f16 into 128-byte-swizzled shared memory (the A operand of T_j),
+//              running output in registers: O = O * 2^(m_old - m_new) + T_{j-1}
+// Q, K, V are read in place from strided buffers (head = 64 contiguous columns of a row), so the
+// packed [rows, 3*d_model] output of a QKV projection needs no reshuffle. head_dim is 64.
+// The exponentials are the bound at this head size (one MUFU.EX2 per score).
+// Every wait is bounded as in the GEMM kernel; on timeout an error word is set and the CTA leaves.
+#include <math.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "tc_sm100.cuh"
+
+namespace cgb {
+
+constexpr int kAttnThreads = 192;
+constexpr int kAttnBM = 128;          // query rows per CTA = TMEM lanes
+constexpr int kAttnBN = 128;          // key rows per step
+constexpr int kAttnD = 64;            // head dim: 128 bytes of bf16 = one swizzle span
+constexpr int kAttnKVStages = 3;
+constexpr int kAttnTileBytes = 128 * 128;                 // a 128-row x 128-byte tile (Q, K or V)
+constexpr int kAttnPBytes = 2 * kAttnTileBytes;           // P: 128 rows x 128 keys, two 64-key swizzle spans
+constexpr int kAttnSmem = kAttnTileBytes + kAttnKVStages * 2 * kAttnTileBytes + 2 * kAttnPBytes + 1024;
+constexpr uint32_t kAttnTmemCols = 512;
+constexpr uint32_t kAttnSCol = 0;     // two score buffers of 128 columns
+constexpr uint32_t kAttnTCol = 256;   // two output-tile buffers of 64 columns
+
+struct AttnParams {
+    long long S_q, S_kv;
+    int H;
+    long long B;
+    long long ldo, o_stride_h, o_stride_b;
+    void* O;
+    float scale_log2e;
+    int q_tiles, kv_tiles;
+    uint32_t idesc_s, idesc_t;
+    uint32_t* err_word;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_q;
+    __shared__ __align__(8) uint64_t bar_kv_full[kAttnKVStages], bar_kv_empty[kAttnKVStages];
+    __shared__ __align__(8) uint64_t bar_s_full[2], bar_s_empty[2], bar_p_full[2], bar_p_empty[2];
+    __shared__ __align__(8) uint64_t bar_t_full[2], bar_t_empty[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile uint32_t abort_flag;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t s_q = smem_base;
+    const uint32_t s_kv = s_q + kAttnTileBytes;                         // stage s: K at +s*2T, V at +s*2T + T
+    const uint32_t s_p = s_kv + kAttnKVStages * 2 * kAttnTileBytes;     // two P buffers
+    uint8_t* const p_gen = smem_raw + (s_p - smem_u32(smem_raw));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // work item: query tile fastest so that the CTAs of one head run together and share K, V in L2
+    const long long item = blockIdx.x;
+    const int qt = (int)(item % p.q_tiles);
+    const int h = (int)((item / p.q_tiles) % p.H);
+    const int b = (int)(item / ((long long)p.q_tiles * p.H));
+    const int q0 = qt * kAttnBM;
+    const int n_tiles = p.kv_tiles;
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar_q), 1);
+        for (int s = 0; s < kAttnKVStages; ++s) {
+            mbar_init(smem_u32(&bar_kv_full[s]), 1);
+            mbar_init(smem_u32(&bar_kv_empty[s]), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&bar_s_full[i]), 1);
+            mbar_init(smem_u32(&bar_s_empty[i]), 4);
+            mbar_init(smem_u32(&bar_p_full[i]), 4);
+            mbar_init(smem_u32(&bar_p_empty[i]), 1);
+            mbar_init(smem_u32(&bar_t_full[i]), 1);
+            mbar_init(smem_u32(&bar_t_empty[i]), 4);
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_slot)), "r"(kAttnTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            mbar_expect_tx(smem_u32(&bar_q), kAttnTileBytes);
+            tma_load_4d<1>(s_q, &tm_q, smem_u32(&bar_q), 0, q0, h, b);
+            for (int j = 0; j < n_tiles; ++j) {
+                const int st = j % kAttnKVStages;
+                const uint32_t use = (uint32_t)(j / kAttnKVStages);
+                if (!mbar_wait(smem_u32(&bar_kv_empty[st]), (use & 1u) ^ 1u, &abort_flag, p.err_word, 0x600u + st)) break;
+                const uint32_t full = smem_u32(&bar_kv_full[st]);
+                mbar_expect_tx(full, 2 * kAttnTileBytes);
+                tma_load_4d<1>(s_kv + st * 2 * kAttnTileBytes, &tm_k, full, 0, j * kAttnBN, h, b);
+                tma_load_4d<1>(s_kv + st * 2 * kAttnTileBytes + kAttnTileBytes, &tm_v, full, 0, j * kAttnBN, h, b);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            bool ok = mbar_wait(smem_u32(&bar_q), 0, &abort_flag, p.err_word, 0x610u);
+            // T_i = P_i V_i: A = P_i (K-major, two 64-key spans), B = V_i ([key, d] with d contiguous: MN-major)
+            auto issue_t = [&](int i) -> bool {
+                const int buf = i & 1;
+                const uint32_t use = (uint32_t)(i >> 1);
+                if (!mbar_wait(smem_u32(&bar_p_full[buf]), use & 1u, &abort_flag, p.err_word, 0x620u + buf)) return false;
+                if (!mbar_wait(smem_u32(&bar_t_empty[buf]), (use & 1u) ^ 1u, &abort_flag, p.err_word, 0x630u + buf)) return false;
+                tc_fence_after();
+                const int st = i % kAttnKVStages;
+                const uint32_t pa = s_p + buf * kAttnPBytes;
+                const uint32_t vb = s_kv + st * 2 * kAttnTileBytes + kAttnTileBytes;
+                const uint32_t tmem_t = tmem_base + kAttnTCol + (uint32_t)(buf * kAttnD);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {   // 16 keys per MMA
+                    const uint64_t da = make_smem_desc(pa + (k >> 2) * kAttnTileBytes + (k & 3) * 32, 16, 1024);
+                    const uint64_t db = make_smem_desc(vb + k * 2048, kAttnTileBytes, 1024);
+                    umma<false, 1>(tmem_t, da, db, p.idesc_t, k > 0 ? 1u : 0u);
+                }
+                tc_commit<1>(smem_u32(&bar_t_full[buf]));
+                tc_commit<1>(smem_u32(&bar_kv_empty[st]));
+                tc_commit<1>(smem_u32(&bar_p_empty[buf]));
+                return true;
+            };
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                const int st = j % kAttnKVStages, buf = j & 1;
+                const uint32_t kv_use = (uint32_t)(j / kAttnKVStages), s_use = (uint32_t)(j >> 1);
+                if (!mbar_wait(smem_u32(&bar_kv_full[st]), kv_use & 1u, &abort_flag, p.err_word, 0x640u + st)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&bar_s_empty[buf]), (s_use & 1u) ^ 1u, &abort_flag, p.err_word, 0x650u + buf)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t kb = s_kv + st * 2 * kAttnTileBytes;
+                const uint32_t tmem_s = tmem_base + kAttnSCol + (uint32_t)(buf * kAttnBN);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {   // 16 of the 64 head dims per MMA
+                    const uint64_t da = make_smem_desc(s_q + k * 32, 16, 1024);
+                    const uint64_t db = make_smem_desc(kb + k * 32, 16, 1024);
+                    umma<false, 1>(tmem_s, da, db, p.idesc_s, k > 0 ? 1u : 0u);
+                }
+                tc_commit<1>(smem_u32(&bar_s_full[buf]));
+                if (j > 0) ok = issue_t(j - 1);
+            }
+            if (ok && n_tiles > 0) issue_t(n_tiles - 1);
+        }
+    } else {
+        // ---------------- softmax + output accumulation (thread = query row) ----------------
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+        float o[kAttnD];
+#pragma unroll
+        for (int i = 0; i < kAttnD; ++i) o[i] = 0.0f;
+        float m = -INFINITY, l = 0.0f, alpha_prev = 0.0f;
+        bool ok = true;
+        auto add_tile = [&](int i, float alpha) -> bool {   // o = o * alpha + T_i
+            const int buf = i & 1;
+            const uint32_t use = (uint32_t)(i >> 1);
+            bool w = mbar_wait(smem_u32(&bar_t_full[buf]), use & 1u, &abort_flag, p.err_word, 0x660u + buf, 2000000000ull, 100);
+            w = __all_sync(0xffffffffu, w);
+            if (!w) return false;
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < kAttnD; c += 32) {
+                float t[32];
+                tmem_ld32(tmem_base + lane_base + kAttnTCol + (uint32_t)(buf * kAttnD + c), t);
+#pragma unroll
+                for (int i2 = 0; i2 < 32; ++i2) o[c + i2] = fmaf(o[c + i2], alpha, t[i2]);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_t_empty[buf]));
+            return true;
+        };
+        for (int j = 0; ok && j < n_tiles; ++j) {
+            const int buf = j & 1;
+            const uint32_t use = (uint32_t)(j >> 1);
+            bool w = mbar_wait(smem_u32(&bar_s_full[buf]), use & 1u, &abort_flag, p.err_word, 0x670u + buf, 2000000000ull, 100);
+            w = __all_sync(0xffffffffu, w);
+            if (!w) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t s_addr = tmem_base + lane_base + kAttnSCol + (uint32_t)(buf * kAttnBN);
+            const long long kv0 = (long long)j * kAttnBN;
+            const bool ragged = kv0 + kAttnBN > p.S_kv;   // last tile: keys past S_kv are zero-filled rows
+            // pass 1: row maximum of the scaled scores
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < kAttnBN; c += 32) {
+                float s[32];
+                tmem_ld32(s_addr + c, s);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float v = s[i];
+                    if (ragged && kv0 + c + i >= p.S_kv) v = -INFINITY;
+                    mx = fmaxf(mx, v);
+                }
+            }
+            const float m_new = fmaxf(m, mx * p.scale_log2e);
+            const float alpha = (m == -INFINITY) ? 0.0f : ex2_approx(m - m_new);
+            // the P buffer is free once T_{j-2} has consumed it
+            w = mbar_wait(smem_u32(&bar_p_empty[buf]), (use & 1u) ^ 1u, &abort_flag, p.err_word, 0x680u + buf, 2000000000ull, 100);
+            w = __all_sync(0xffffffffu, w);
+            if (!w) { ok = false; break; }
+            // pass 2: p = 2^(s * scale * log2e - m_new), row sum, P into swizzled shared memory
+            float l_tile = 0.0f;
+            uint8_t* prow = p_gen + buf * kAttnPBytes + row * 128;
+#pragma unroll 1
+            for (int c = 0; c < kAttnBN; c += 32) {
+                float s[32];
+                tmem_ld32(s_addr + c, s);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float v = ex2_approx(fmaf(s[i], p.scale_log2e, -m_new));
+                    if (ragged && kv0 + c + i >= p.S_kv) v = 0.0f;
+                    s[i] = v;
+                    l_tile += v;
+                }
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {   // four 16-byte pieces of 8 keys
+                    Vec16<T> o8;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) o8.v[i] = Elem<T>::from_f32(s[g * 8 + i]);
+                    const int piece = (c >> 3) + g;            // 0..15 along the 128 keys
+                    const int span = piece >> 3, slot = (piece & 7) ^ (row & 7);
+                    *reinterpret_cast<int4*>(prow + span * kAttnTileBytes + slot * 16) = *reinterpret_cast<const int4*>(&o8);
+                }
+            }
+            // scores consumed; P written through the generic proxy must be visible to the tensor pipe
+            tc_fence_before();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(smem_u32(&bar_s_empty[buf]));
+                mbar_arrive(smem_u32(&bar_p_full[buf]));
+            }
+            l = fmaf(l, alpha, l_tile);
+            if (j > 0) ok = add_tile(j - 1, alpha_prev);
+            alpha_prev = alpha;
+            m = m_new;
+        }
+        if (ok && n_tiles > 0) ok = add_tile(n_tiles - 1, alpha_prev);
+        if (ok && q0 + row < p.S_q) {
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            T* orow = static_cast<T*>(p.O) + (long long)b * p.o_stride_b + (long long)h * p.o_stride_h + (long long)(q0 + row) * p.ldo;
+#pragma unroll
+            for (int g = 0; g < kAttnD / 8; ++g) {
+                Vec16<T> o8;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o8.v[i] = Elem<T>::from_f32(o[g * 8 + i] * inv);
+                *reinterpret_cast<int4*>(orow + g * 8) = *reinterpret_cast<const int4*>(&o8);
+            }
+        }
+    }
+
+    if (abort_flag) {
+        // a wait ran out: give copies that may still be in flight time to land before the CTA's shared
+        // memory is released
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kAttnTmemCols) : "memory");
+    }
+}
+
+static int make_head_map(CUtensorMap* map, const void* base, int dtype, long long rows, int H, long long B, long long ld,
+                         long long stride_h, long long stride_b) {
+    EncodeTiledFn fn = tensor_map_encoder();
+    if (!fn) return CG_B200_ERR_CUDA;
+    const cuuint64_t esz = 2;
+    cuuint64_t dims[4] = {(cuuint64_t)kAttnD, (cuuint64_t)rows, (cuuint64_t)H, (cuuint64_t)B};
+    const cuuint64_t fallback = (cuuint64_t)rows * ld * esz;
+    cuuint64_t strides[3] = {(cuuint64_t)ld * esz, H > 1 ? (cuuint64_t)stride_h * esz : fallback,
+                             B > 1 ? (cuuint64_t)stride_b * esz : fallback};
+    cuuint32_t box[4] = {(cuuint32_t)kAttnD, 128, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(map, dtype == CG_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        note_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled (attention)");
+        return CG_B200_ERR_CUDA;
+    }
+    return CG_B200_OK;
+}
+
+static uint32_t attn_idesc(int dtype, bool b_mn_major, int n) {
+    uint32_t d = 0;
+    d |= 1u << 4;                                            // fp32 accumulator
+    const uint32_t fmt = dtype == CG_B200_BF16 ? 1u : 0u;
+    d |= fmt << 7;
+    d |= fmt << 10;
+    d |= (b_mn_major ? 1u : 0u) << 16;
+    d |= (uint32_t)(n >> 3) << 17;
+    d |= (uint32_t)(kAttnBM >> 4) << 24;
+    return d;
+}
+
+}  // namespace cgb
+
+using namespace cgb;
+
+extern "C" int cg_b200_attention(const cg_b200_attention_desc* desc, const void* Q, const void* K, const void* V,
+                                 void* O, void* stream) {
+    if (!desc) return CG_B200_ERR_NULL_POINTER;
+    const cg_b200_attention_desc& d = *desc;
+    if (d.dtype != CG_B200_BF16 && d.dtype != CG_B200_F16) return CG_B200_ERR_UNSUPPORTED;
+    if (d.head_dim != kAttnD) return CG_B200_ERR_UNSUPPORTED;
+    if (d.batch < 0 || d.heads < 1 || d.seq_q < 0 || d.seq_kv < 0) return CG_B200_ERR_INVALID_ARG;
+    if (d.batch > 0x7fffffffLL || d.heads > 65535 || d.seq_q > 0x7fffffffLL || d.seq_kv > 0x7fffffffLL) return CG_B200_ERR_UNSUPPORTED;
+    if (d.ldq < kAttnD || d.ldk < kAttnD || d.ldv < kAttnD || d.ldo < kAttnD) return CG_B200_ERR_INVALID_ARG;
+    if (d.batch == 0 || d.seq_q == 0) return CG_B200_OK;
+    if (d.seq_kv == 0 || !(d.scale > 0.0f)) return CG_B200_ERR_INVALID_ARG;   // softmax over an empty set; the row max assumes scale > 0
+    if (!Q || !K || !V || !O) return CG_B200_ERR_NULL_POINTER;
+    const long long strides[] = {d.ldq, d.ldk, d.ldv, d.ldo, d.head_stride_q, d.head_stride_k, d.head_stride_v, d.head_stride_o,
+                                 d.batch_stride_q, d.batch_stride_k, d.batch_stride_v, d.batch_stride_o};
+    for (long long s : strides)
+        if (s < 0 || (s * 2) % 16) return s < 0 ? CG_B200_ERR_INVALID_ARG : CG_B200_ERR_MISALIGNED;
+    if (!aligned_to(Q, 16) || !aligned_to(K, 16) || !aligned_to(V, 16) || !aligned_to(O, 16)) return CG_B200_ERR_MISALIGNED;
+    int st = require_sm100();
+    if (st) return st;
+
+    alignas(64) CUtensorMap tq, tk, tv;
+    st = make_head_map(&tq, Q, d.dtype, d.seq_q, (int)d.heads, d.batch, d.ldq, d.head_stride_q, d.batch_stride_q);
+    if (st) return st;
+    st = make_head_map(&tk, K, d.dtype, d.seq_kv, (int)d.heads, d.batch, d.ldk, d.head_stride_k, d.batch_stride_k);
+    if (st) return st;
+    st = make_head_map(&tv, V, d.dtype, d.seq_kv, (int)d.heads, d.batch, d.ldv, d.head_stride_v, d.batch_stride_v);
+    if (st) return st;
+
+    AttnParams p;
+    memset(&p, 0, sizeof(p));
+    p.S_q = d.seq_q; p.S_kv = d.seq_kv; p.H = (int)d.heads; p.B = d.batch;
+    p.ldo = d.ldo; p.o_stride_h = d.head_stride_o; p.o_stride_b = d.batch_stride_o;
+    p.O = O;
+    p.scale_log2e = d.scale * 1.4426950408889634f;
+    p.q_tiles = (int)((d.seq_q + kAttnBM - 1) / kAttnBM);
+    p.kv_tiles = (int)((d.seq_kv + kAttnBN - 1) / kAttnBN);
+    p.idesc_s = attn_idesc(d.dtype, false, kAttnBN);
+    p.idesc_t = attn_idesc(d.dtype, true, kAttnD);
+    p.err_word = device_error_word();
+    const long long items = (long long)p.q_tiles * p.H * p.B;
+    if (items > 0x7fffffffLL) return CG_B200_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (d.dtype == CG_B200_BF16) {
+        auto kern = attention_sm100_kernel<__nv_bfloat16>;
+        CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
+        kern<<<(unsigned)items, kAttnThreads, kAttnSmem, s>>>(tq, tk, tv, p);
+    } else {
+        auto kern = attention_sm100_kernel<__half>;
+        CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
+        kern<<<(unsigned)items, kAttnThreads, kAttnSmem, s>>>(tq, tk, tv, p);
+    }
+    CGB_CUDA(cudaGetLastError());
+    return CG_B200_OK;
+}

@@ -5,10 +5,12 @@
 
 The dataflow is the reference's transformer benchmark graph (benchmarks/benchmark_transformer.py:98-119:
 layernorm eps 1e-5, GELU, no mask, no dropout); the reference only ever compiles that graph, it
-never executes it (benchmarks/REPORT_TRANSFORMER.md:53-57). Nine launches per block:
-  layernorm | QKV GEMM | Q K^T GEMM (heads as the inner batch level, scale in the epilogue) |
-  row softmax | P V GEMM (written straight into [B*S, d_model]) | out-proj GEMM + residual |
-  layernorm | FFN1 GEMM + bias + gelu | FFN2 GEMM + bias + residual
+never executes it (benchmarks/REPORT_TRANSFORMER.md:53-57). Seven launches per block:
+  layernorm | QKV GEMM | fused attention (reads Q, K, V in place from the QKV rows, writes
+  [B*S, d_model]) | out-proj GEMM + residual | layernorm | FFN1 GEMM + bias + gelu |
+  FFN2 GEMM + bias + residual
+Without the fused kernel (head_dim != 64, fp32) attention is three launches: Q K^T GEMM (heads as the
+inner batch level, scale in the epilogue), row softmax, P V GEMM.
 Weights are [in, out] row-major (x @ W), all tensors bf16/f16/f32 of one dtype.
 """
 import ctypes as C
@@ -22,7 +24,7 @@ from .ops import DTYPE_OF_TORCH
 
 
 class EncoderBlock:
-    def __init__(self, d_model, n_heads, d_ff, w_qkv, w_o, w_1, b_1, w_2, b_2, eps=1e-5):
+    def __init__(self, d_model, n_heads, d_ff, w_qkv, w_o, w_1, b_1, w_2, b_2, eps=1e-5, fused_attention=True):
         assert d_model % n_heads == 0
         self.D, self.H, self.F, self.dh, self.eps = d_model, n_heads, d_ff, d_model // n_heads, eps
         self.w_qkv, self.w_o, self.w_1, self.b_1, self.w_2, self.b_2 = w_qkv, w_o, w_1, b_1, w_2, b_2
@@ -31,6 +33,8 @@ class EncoderBlock:
         self.dtype = w_qkv.dtype
         self.dt = DTYPE_OF_TORCH[self.dtype]
         self._bufs = {}
+        # the fused kernel covers head_dim 64 and 16-bit types; otherwise three launches
+        self.fused_attention = fused_attention and self.dh == 64 and self.dtype in (torch.bfloat16, torch.float16)
 
     def _buf(self, name, shape, device):
         t = self._bufs.get(name)
@@ -57,7 +61,7 @@ class EncoderBlock:
         x2 = x.view(rows, D)
         ln1 = self._buf("ln1", (rows, D), dev)
         qkv = self._buf("qkv", (rows, 3 * D), dev)
-        scores = self._buf("scores", (B * H, S, S), dev)
+        scores = None if self.fused_attention else self._buf("scores", (B * H, S, S), dev)
         ctx = self._buf("ctx", (rows, D), dev)
         h = self._buf("h", (rows, D), dev)
         ln2 = self._buf("ln2", (rows, D), dev)
@@ -71,6 +75,27 @@ class EncoderBlock:
 
         check(L.cg_b200_layernorm(dt, p(x2), None, None, self.eps, p(ln1), rows, D, st), "layernorm")
         gemm(capi.make_gemm_desc(rows, 3 * D, D, dt, dt), ln1, self.w_qkv, qkv)
+        if self.fused_attention:
+            es = qkv.element_size()
+            ad = capi.AttentionDesc(dtype=dt, head_dim=dh, batch=B, heads=H, seq_q=S, seq_kv=S, ldq=3 * D, ldk=3 * D,
+                                    ldv=3 * D, ldo=D, head_stride_q=dh, head_stride_k=dh, head_stride_v=dh, head_stride_o=dh,
+                                    batch_stride_q=S * 3 * D, batch_stride_k=S * 3 * D, batch_stride_v=S * 3 * D,
+                                    batch_stride_o=S * D, scale=1.0 / math.sqrt(dh))
+            base = qkv.data_ptr()
+            check(L.cg_b200_attention(C.byref(ad), C.c_void_p(base), C.c_void_p(base + D * es),
+                                      C.c_void_p(base + 2 * D * es), p(ctx), st), "attention")
+        else:
+            self._unfused_attention(qkv, scores, ctx, B, S, gemm, p, st)
+        gemm(capi.make_gemm_desc(rows, D, D, dt, dt, epilogue="residual"), ctx, self.w_o, h, res=x2)
+        check(L.cg_b200_layernorm(dt, p(h), None, None, self.eps, p(ln2), rows, D, st), "layernorm")
+        gemm(capi.make_gemm_desc(rows, F, D, dt, dt, epilogue="bias_gelu_tanh"), ln2, self.w_1, ff, bias=self.b_1)
+        gemm(capi.make_gemm_desc(rows, D, F, dt, dt, epilogue="bias_residual"), ff, self.w_2, y.view(rows, D),
+             bias=self.b_2, res=h)
+        return y
+
+    def _unfused_attention(self, qkv, scores, ctx, B, S, gemm, p, st):
+        D, H, dh, dt = self.D, self.H, self.dh, self.dt
+        L = lib()
         # scores[b, h] = Q_bh K_bh^T / sqrt(dh): Q, K are column blocks of the qkv rows (row stride 3D);
         # heads are the inner batch level (stride dh), sequences the outer one (stride S * 3D)
         d_qk = capi.make_gemm_desc(S, S, dh, dt, dt, epilogue="scale", alpha=1.0 / math.sqrt(dh), batch=B * H,
@@ -82,11 +107,7 @@ class EncoderBlock:
         d_pv = capi.make_gemm_desc(S, dh, S, dt, dt, batch=B * H, lda=S, ldb=3 * D, ldc=D, batch_inner=H,
                                    bsa=H * S * S, bsb=S * 3 * D, bsc=S * D, isa=S * S, isb=dh, isc=dh)
         gemm(d_pv, scores, qkv, ctx, b_off=2 * D)
-        gemm(capi.make_gemm_desc(rows, D, D, dt, dt, epilogue="residual"), ctx, self.w_o, h, res=x2)
-        check(L.cg_b200_layernorm(dt, p(h), None, None, self.eps, p(ln2), rows, D, st), "layernorm")
-        gemm(capi.make_gemm_desc(rows, F, D, dt, dt, epilogue="bias_gelu_tanh"), ln2, self.w_1, ff, bias=self.b_1)
-        gemm(capi.make_gemm_desc(rows, D, F, dt, dt, epilogue="bias_residual"), ff, self.w_2, y.view(rows, D),
-             bias=self.b_2, res=h)
-        return y
 
-    LAUNCHES_PER_FORWARD = 9
+    @property
+    def launches_per_forward(self):
+        return 7 if self.fused_attention else 9

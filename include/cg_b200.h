@@ -247,6 +247,29 @@ int cg_b200_gemm(const cg_b200_gemm_desc* desc, const void* A, const void* B,
  * (0 = none). Synchronises `stream`. */
 int cg_b200_last_device_error(void* stream, uint32_t* word);
 
+/* ---- fused attention ---------------------------------------------------------------------
+ * O[b, h] = softmax(Q[b, h] K[b, h]^T * scale) V[b, h] over the last axis, no mask: the pattern
+ * the reference annotates as "attention" (src/optimization/graph/graph_pattern.cpp:61-85) and
+ * never executes; as separate ops it is matmul, softmax, matmul (src/ir/ops.cpp). Scores and
+ * probabilities stay on chip in fp32 (probabilities enter the second product rounded to
+ * `dtype`), so results differ from the three-op sequence by its intermediate roundings only.
+ * Q/O are [batch, heads, seq_q, head_dim], K/V [batch, heads, seq_kv, head_dim], each given by a
+ * base pointer and row / head / batch strides in elements, so heads may be column blocks of a
+ * packed [rows, 3 * d_model] projection. head_dim must be 64, dtype bf16 or f16, scale > 0;
+ * bases 16-byte aligned, strides multiples of 8 elements. */
+typedef struct cg_b200_attention_desc {
+    int32_t dtype;
+    int32_t head_dim;
+    int64_t batch, heads, seq_q, seq_kv;
+    int64_t ldq, ldk, ldv, ldo;                                        /* row strides */
+    int64_t head_stride_q, head_stride_k, head_stride_v, head_stride_o;
+    int64_t batch_stride_q, batch_stride_k, batch_stride_v, batch_stride_o;
+    float   scale;
+    int32_t reserved;
+} cg_b200_attention_desc;
+int cg_b200_attention(const cg_b200_attention_desc* desc, const void* Q, const void* K, const void* V,
+                      void* O, void* stream);
+
 /* fp32 GEMM for callers that cannot allocate device memory (no counterpart in the reference).
  * Who that is: code that runs where an allocation is not allowed or not possible - a launch
  * routine that is handed only tensors and a stream (the shape of BoundExecutable::launch,

@@ -256,3 +256,24 @@ def ref_matmul(A, B):
     out = np.empty((M, N), dtype=np.float32)
     _check(ref().cgref_matmul(_p(A), _p(B), _p(out), M, K, N), "ref_matmul")
     return out
+
+
+# ---- attention (restatement: matmul, softmax, matmul with fp32 intermediates) --------------------
+def attention(q, k, v, dtype, scale):
+    """q: [B, H, Sq, d], k/v: [B, H, Skv, d] in storage representation. Scores and probabilities stay
+    fp32 (no rounding between the three ops); the result is rounded to `dtype`. PARITY UNPINNED:
+    the reference defines the ops (src/ir/ops.cpp) and annotates the pattern
+    (src/optimization/graph/graph_pattern.cpp:61-85) but executes neither."""
+    B, H, Sq, d = q.shape
+    Skv = k.shape[2]
+    out = np.empty((B, H, Sq, d), dtype=NP_OF[dtype])
+    for b in range(B):
+        for h in range(H):
+            qf = np.ascontiguousarray(q[b, h])
+            kf = np.ascontiguousarray(k[b, h])
+            s = gemm(make_gemm_desc(Sq, Skv, d, dtype, F32, epilogue="scale", alpha=scale, b_transposed=1), qf, kf)
+            p = softmax(s.reshape(Sq, Skv), F32)
+            vf = to_f32(np.ascontiguousarray(v[b, h]), dtype)
+            o = gemm(make_gemm_desc(Sq, d, Skv, F32, F32), p, vf).reshape(Sq, d)
+            out[b, h] = to_storage(o, dtype)
+    return out

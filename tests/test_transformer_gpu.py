@@ -32,9 +32,10 @@ def _check(got, want, tol, what):
     assert norm <= tol and rms <= tol, f"{what}: max-normalised {norm:.3e}, rms ratio {rms:.3e}, tol {tol}"
 
 
+@pytest.mark.parametrize("fused_attention", [True, False])
 @pytest.mark.parametrize("dtype_name", ["BF16", "F16"])
 @pytest.mark.parametrize("B,S,D,H,F", [(2, 128, 128, 2, 512), (3, 200, 256, 4, 384), (1, 64, 64, 1, 64)])
-def test_block_matches_oracle(ops, cgb, oracle, dtype_name, B, S, D, H, F):
+def test_block_matches_oracle(ops, cgb, oracle, dtype_name, B, S, D, H, F, fused_attention):
     import torch
     from cantors_gift_b200.transformer import EncoderBlock
     from oracle import transformer as T
@@ -43,11 +44,12 @@ def test_block_matches_oracle(ops, cgb, oracle, dtype_name, B, S, D, H, F):
     rng = np.random.default_rng(B * 1000 + S)
     x, w = _make(O, rng, B, S, D, F, dtype)
     want = O.to_f32(T.encoder_block(x, n_heads=H, dtype=dtype, **w), dtype)
-    blk = EncoderBlock(D, H, F, **{k: _dev(ops, v, dtype) for k, v in w.items()})
+    blk = EncoderBlock(D, H, F, fused_attention=fused_attention, **{k: _dev(ops, v, dtype) for k, v in w.items()})
+    assert blk.launches_per_forward == (7 if fused_attention else 9)
     y = blk.forward(_dev(ops, x, dtype))
     torch.cuda.synchronize()
     assert ops.last_device_error() == 0
-    _check(_host(O, y, dtype), want, 1e-2, f"block {dtype_name} B{B} S{S} D{D} H{H} F{F}")
+    _check(_host(O, y, dtype), want, 1e-2, f"block {dtype_name} B{B} S{S} D{D} H{H} F{F} fused={fused_attention}")
 
 
 def test_full_size_block_sequences_are_independent_and_match(ops, cgb, oracle):
