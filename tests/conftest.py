@@ -52,3 +52,15 @@ def assert_close(y, ref, tol, what=""):
     """Both metrics must be within `tol` (1e-4 for fp32 paths, 1e-2 for bf16/f16 paths)."""
     norm, p999 = error_metrics(y, ref)
     assert norm <= tol and p999 <= tol, f"{what}: max-normalised {norm:.3e}, p99.9 relative {p999:.3e}, tol {tol}"
+
+
+def assert_close_rms(y, ref, tol, what=""):
+    """max|y-ref| / max|ref| <= tol and rms(y-ref) / rms(ref) <= tol. For results that are sums of
+    many rounded terms of mixed sign (attention outputs, whole blocks): elements near zero carry the
+    absolute rounding noise of the terms, so a per-element relative error says nothing there."""
+    y = np.asarray(y, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    err = np.abs(y - ref)
+    norm = err.max() / max(np.abs(ref).max(), 1e-30)
+    rms = np.sqrt((err ** 2).mean()) / max(np.sqrt((ref ** 2).mean()), 1e-30)
+    assert norm <= tol and rms <= tol, f"{what}: max-normalised {norm:.3e}, rms ratio {rms:.3e}, tol {tol}"

@@ -1,11 +1,11 @@
 """Fused attention (tcgen05) against the CPU oracle, through the C ABI. Tolerance: the path's 16-bit
-bound, 1e-2 (max-normalised and 99.9th-percentile relative, conftest.assert_close)."""
+bound, 1e-2, on the max-normalised error and the RMS ratio (conftest.assert_close_rms)."""
 import ctypes as C
 
 import numpy as np
 import pytest
 
-from conftest import assert_close
+from conftest import assert_close_rms as assert_close
 
 pytestmark = pytest.mark.gpu
 
