@@ -5,14 +5,15 @@
 // the path - matmul, softmax, matmul (src/ir/ops.cpp) - whose [B, H, S, S] intermediate makes three
 // trips through HBM. Here the scores never leave the SM.
 //
-// One CTA per (batch, head, 128 query rows), 192 threads:
+// One CTA per (batch, head, 128 query rows), 320 threads:
 //   warp 0     TMA: the Q tile once, then K and V tiles of 128 key rows through a 3-stage ring
 //   warp 1     one thread issues S_j = Q K_j^T (128 x 128 x 64) into one of two TMEM score buffers and
 //              T_j = P_j V_j (128 x 64 x 128) into one of two TMEM output-tile buffers; S_{j+1} is
 //              issued before T_j so the tensor pipe works while the softmax warps do
-//   warps 2-5  thread = query row: two passes over S_j in TMEM (row max, then p = 2^(s - m), row sum),
-//              P_j written as bf16/f16 into 128-byte-swizzled shared memory (the A operand of T_j),
-//              running output in registers: O = O * 2^(m_old - m_new) + T_{j-1}
+//   warps 2-9  two threads per query row (64 keys and 32 output columns each): scores from TMEM to
+//              registers, row max exchanged through shared memory, p = 2^(s - m) and row sum, P_j written
+//              as bf16/f16 into 128-byte-swizzled shared memory (the A operand of T_j), running output
+//              in registers: O = O * 2^(m_old - m_new) + T_{j-1}
 // Q, K, V are read in place from strided buffers (head = 64 contiguous columns of a row), so the
 // packed [rows, 3*d_model] output of a QKV projection needs no reshuffle. head_dim is 64.
 // The exponentials are the bound at this head size (one MUFU.EX2 per score).
@@ -25,7 +26,7 @@
 
 namespace cgb {
 
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 320;
 constexpr int kAttnBM = 128;          // query rows per CTA = TMEM lanes
 constexpr int kAttnBN = 128;          // key rows per step
 constexpr int kAttnD = 64;            // head dim: 128 bytes of bf16 = one swizzle span
@@ -60,6 +61,8 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     __shared__ __align__(8) uint64_t bar_t_full[2], bar_t_empty[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile uint32_t abort_flag;
+    __shared__ float xval[2][2][128];          // row exchange between the two halves: [parity][half][row]
+    __shared__ volatile int xtag[2][2][128];
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t s_q = smem_base;
@@ -84,16 +87,17 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&bar_s_full[i]), 1);
-            mbar_init(smem_u32(&bar_s_empty[i]), 4);
-            mbar_init(smem_u32(&bar_p_full[i]), 4);
+            mbar_init(smem_u32(&bar_s_empty[i]), 8);
+            mbar_init(smem_u32(&bar_p_full[i]), 8);
             mbar_init(smem_u32(&bar_p_empty[i]), 1);
             mbar_init(smem_u32(&bar_t_full[i]), 1);
-            mbar_init(smem_u32(&bar_t_empty[i]), 4);
+            mbar_init(smem_u32(&bar_t_empty[i]), 8);
         }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    for (int i = threadIdx.x; i < 2 * 2 * 128; i += kAttnThreads) (&xtag[0][0][0])[i] = 0;
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_u32(&tmem_base_slot)), "r"(kAttnTmemCols) : "memory");
@@ -165,29 +169,51 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             if (ok && n_tiles > 0) issue_t(n_tiles - 1);
         }
     } else {
-        // ---------------- softmax + output accumulation (thread = query row) ----------------
+        // ---------------- softmax + output accumulation ----------------
+        // Eight warps: two per TMEM lane quarter. Thread = (query row, half): it owns 64 of the 128 keys
+        // of each score tile and 32 of the 64 output columns. The two threads of a row exchange their
+        // partial row maxima (and, at the end, row sums) through shared memory.
         const int q = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int row = q * 32 + lane;
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
-        float o[kAttnD];
+        float o[32];
 #pragma unroll
-        for (int i = 0; i < kAttnD; ++i) o[i] = 0.0f;
+        for (int i = 0; i < 32; ++i) o[i] = 0.0f;
         float m = -INFINITY, l = 0.0f, alpha_prev = 0.0f;
         bool ok = true;
-        auto add_tile = [&](int i, float alpha) -> bool {   // o = o * alpha + T_i
+        // partner exchange: value + tag (tile number + 1), double-buffered by tile parity. Bounded.
+        auto exchange = [&](float mine, int seq, bool& good) -> float {
+            const int par = seq & 1;
+            xval[par][half][row] = mine;
+            __threadfence_block();
+            xtag[par][half][row] = seq;
+            const volatile int* tag = &xtag[par][half ^ 1][row];
+            for (uint32_t it = 0; *tag != seq; ++it) {
+                if ((it & 0xff) == 0xff) {
+                    if (abort_flag) { good = false; return mine; }
+                    if (it > (1u << 26)) {   // about a second of polling
+                        abort_flag = 1;
+                        if (p.err_word) atomicCAS(p.err_word, 0u, 0x690u);
+                        good = false;
+                        return mine;
+                    }
+                }
+            }
+            __threadfence_block();
+            return xval[par][half ^ 1][row];
+        };
+        auto add_tile = [&](int i, float alpha) -> bool {   // o = o * alpha + T_i (this thread's 32 columns)
             const int buf = i & 1;
             const uint32_t use = (uint32_t)(i >> 1);
-            bool w = mbar_wait(smem_u32(&bar_t_full[buf]), use & 1u, &abort_flag, p.err_word, 0x660u + buf, 2000000000ull, 100);
+            bool w = mbar_wait(smem_u32(&bar_t_full[buf]), use & 1u, &abort_flag, p.err_word, 0x660u + buf);
             w = __all_sync(0xffffffffu, w);
             if (!w) return false;
             tc_fence_after();
+            float t[32];
+            tmem_ld32(tmem_base + lane_base + kAttnTCol + (uint32_t)(buf * kAttnD + half * 32), t);
 #pragma unroll
-            for (int c = 0; c < kAttnD; c += 32) {
-                float t[32];
-                tmem_ld32(tmem_base + lane_base + kAttnTCol + (uint32_t)(buf * kAttnD + c), t);
-#pragma unroll
-                for (int i2 = 0; i2 < 32; ++i2) o[c + i2] = fmaf(o[c + i2], alpha, t[i2]);
-            }
+            for (int i2 = 0; i2 < 32; ++i2) o[i2] = fmaf(o[i2], alpha, t[i2]);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bar_t_empty[buf]));
@@ -196,79 +222,78 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         for (int j = 0; ok && j < n_tiles; ++j) {
             const int buf = j & 1;
             const uint32_t use = (uint32_t)(j >> 1);
-            bool w = mbar_wait(smem_u32(&bar_s_full[buf]), use & 1u, &abort_flag, p.err_word, 0x670u + buf, 2000000000ull, 100);
+            bool w = mbar_wait(smem_u32(&bar_s_full[buf]), use & 1u, &abort_flag, p.err_word, 0x670u + buf);
             w = __all_sync(0xffffffffu, w);
             if (!w) { ok = false; break; }
             tc_fence_after();
-            const uint32_t s_addr = tmem_base + lane_base + kAttnSCol + (uint32_t)(buf * kAttnBN);
-            const long long kv0 = (long long)j * kAttnBN;
-            const bool ragged = kv0 + kAttnBN > p.S_kv;   // last tile: keys past S_kv are zero-filled rows
-            // pass 1: row maximum of the scaled scores
+            const uint32_t s_addr = tmem_base + lane_base + kAttnSCol + (uint32_t)(buf * kAttnBN + half * 64);
+            const long long kv0 = (long long)j * kAttnBN + half * 64;
+            const bool ragged = kv0 + 64 > p.S_kv;   // keys past S_kv are zero-filled rows of K
+            float s[64];
+            tmem_ld32(s_addr, *reinterpret_cast<float(*)[32]>(&s[0]));
+            tmem_ld32(s_addr + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+            // the scores are in registers: the TMEM buffer can take S_{j+2}
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_s_empty[buf]));
             float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < kAttnBN; c += 32) {
-                float s[32];
-                tmem_ld32(s_addr + c, s);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float v = s[i];
-                    if (ragged && kv0 + c + i >= p.S_kv) v = -INFINITY;
-                    mx = fmaxf(mx, v);
-                }
+            for (int i = 0; i < 64; ++i) {
+                if (ragged && kv0 + i >= p.S_kv) s[i] = -INFINITY;
+                mx = fmaxf(mx, s[i]);
             }
-            const float m_new = fmaxf(m, mx * p.scale_log2e);
+            bool good = true;
+            const float mx_other = exchange(mx, j + 1, good);
+            good = __all_sync(0xffffffffu, good);
+            if (!good) { ok = false; break; }
+            const float m_new = fmaxf(m, fmaxf(mx, mx_other) * p.scale_log2e);
             const float alpha = (m == -INFINITY) ? 0.0f : ex2_approx(m - m_new);
             // the P buffer is free once T_{j-2} has consumed it
-            w = mbar_wait(smem_u32(&bar_p_empty[buf]), (use & 1u) ^ 1u, &abort_flag, p.err_word, 0x680u + buf, 2000000000ull, 100);
+            w = mbar_wait(smem_u32(&bar_p_empty[buf]), (use & 1u) ^ 1u, &abort_flag, p.err_word, 0x680u + buf);
             w = __all_sync(0xffffffffu, w);
             if (!w) { ok = false; break; }
-            // pass 2: p = 2^(s * scale * log2e - m_new), row sum, P into swizzled shared memory
+            // p = 2^(s * scale * log2e - m_new); this half's 64 keys are one 128-byte swizzle span of P
             float l_tile = 0.0f;
-            uint8_t* prow = p_gen + buf * kAttnPBytes + row * 128;
-#pragma unroll 1
-            for (int c = 0; c < kAttnBN; c += 32) {
-                float s[32];
-                tmem_ld32(s_addr + c, s);
+            uint8_t* prow = p_gen + buf * kAttnPBytes + half * kAttnTileBytes + row * 128;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float v = ex2_approx(fmaf(s[i], p.scale_log2e, -m_new));
-                    if (ragged && kv0 + c + i >= p.S_kv) v = 0.0f;
-                    s[i] = v;
-                    l_tile += v;
+            for (int g = 0; g < 8; ++g) {   // eight 16-byte pieces of 8 keys
+                float e[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    e[i] = ex2_approx(fmaf(s[g * 8 + i], p.scale_log2e, -m_new));   // 2^-inf = 0 for masked keys
+                    l_tile += e[i];
                 }
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {   // four 16-byte pieces of 8 keys
-                    Vec16<T> o8;
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) o8.v[i] = Elem<T>::from_f32(s[g * 8 + i]);
-                    const int piece = (c >> 3) + g;            // 0..15 along the 128 keys
-                    const int span = piece >> 3, slot = (piece & 7) ^ (row & 7);
-                    *reinterpret_cast<int4*>(prow + span * kAttnTileBytes + slot * 16) = *reinterpret_cast<const int4*>(&o8);
-                }
+                // packed two-at-a-time conversion: single-value cvt instructions share the MUFU pipe with
+                // the exponentials, which is the pipe that bounds this kernel
+                const Vec16<T> o8 = pack16<T>(e);
+                *reinterpret_cast<int4*>(prow + ((g ^ (row & 7)) << 4)) = *reinterpret_cast<const int4*>(&o8);
             }
-            // scores consumed; P written through the generic proxy must be visible to the tensor pipe
-            tc_fence_before();
+            // P written through the generic proxy must be visible to the tensor pipe
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(smem_u32(&bar_s_empty[buf]));
-                mbar_arrive(smem_u32(&bar_p_full[buf]));
-            }
+            if (lane == 0) mbar_arrive(smem_u32(&bar_p_full[buf]));
             l = fmaf(l, alpha, l_tile);
             if (j > 0) ok = add_tile(j - 1, alpha_prev);
             alpha_prev = alpha;
             m = m_new;
         }
         if (ok && n_tiles > 0) ok = add_tile(n_tiles - 1, alpha_prev);
-        if (ok && q0 + row < p.S_q) {
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            T* orow = static_cast<T*>(p.O) + (long long)b * p.o_stride_b + (long long)h * p.o_stride_h + (long long)(q0 + row) * p.ldo;
+        if (ok) {
+            bool good = true;
+            const float l_other = exchange(l, n_tiles + 1, good);
+            if (good && q0 + row < p.S_q) {
+                const float lt = l + l_other;
+                const float inv = lt > 0.0f ? 1.0f / lt : 0.0f;
+                T* orow = static_cast<T*>(p.O) + (long long)b * p.o_stride_b + (long long)h * p.o_stride_h +
+                          (long long)(q0 + row) * p.ldo + half * 32;
 #pragma unroll
-            for (int g = 0; g < kAttnD / 8; ++g) {
-                Vec16<T> o8;
+                for (int g = 0; g < 4; ++g) {
+                    float e[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) o8.v[i] = Elem<T>::from_f32(o[g * 8 + i] * inv);
-                *reinterpret_cast<int4*>(orow + g * 8) = *reinterpret_cast<const int4*>(&o8);
+                    for (int i = 0; i < 8; ++i) e[i] = o[g * 8 + i] * inv;
+                    const Vec16<T> o8 = pack16<T>(e);
+                    *reinterpret_cast<int4*>(orow + g * 8) = *reinterpret_cast<const int4*>(&o8);
+                }
             }
         }
     }

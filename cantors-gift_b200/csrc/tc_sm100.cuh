@@ -21,14 +21,18 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One potentially blocking probe: the hardware suspends the thread until the phase completes or
+// the time hint (nanoseconds) runs out, so a waiting thread issues a handful of instructions per
+// probe instead of spinning - a spinning lane steals issue slots and power from the warps that work.
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t done;
+    const uint32_t hint_ns = 1000000u;   // 1 ms per probe; the caller loops with its own deadline
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
         : "memory");
     return done;
 }
@@ -39,25 +43,22 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 
 // Bounded wait. Returns false when the wait was abandoned: either this wait ran longer than
-// `limit_ns`, or another thread of the CTA already raised `*abort_flag`. `sleep_ns` > 0 makes a
-// thread that keeps missing back off with nanosleep: the four epilogue warps wait for a whole main
-// loop, and 128 threads spinning on try_wait for that long burn issue slots and power the tensor
-// pipe could use (the part is power-limited under a dense GEMM).
+// `limit_ns`, or another thread of the CTA already raised `*abort_flag`. Each probe may suspend the
+// thread for up to a millisecond in hardware (see mbar_try_wait), so an abort raised by another
+// thread is noticed within that time.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           uint32_t* err_word, uint32_t code,
                                           unsigned long long limit_ns = 2000000000ull, uint32_t sleep_ns = 0) {
+    (void)sleep_ns;   // the probe itself suspends the thread; no blind sleeping
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
-    for (uint32_t it = 1;; ++it) {
+    for (;;) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (sleep_ns && it > 4) __nanosleep(sleep_ns);
-        if ((it & 0xff) == 0) {
-            if (*abort_flag) return false;
-            if (global_ns() - t0 > limit_ns) {
-                *abort_flag = 1;
-                if (err_word) atomicCAS(err_word, 0u, code);
-                return false;
-            }
+        if (*abort_flag) return false;
+        if (global_ns() - t0 > limit_ns) {
+            *abort_flag = 1;
+            if (err_word) atomicCAS(err_word, 0u, code);
+            return false;
         }
     }
 }
