@@ -5,7 +5,7 @@
 // the path - matmul, softmax, matmul (src/ir/ops.cpp) - whose [B, H, S, S] intermediate makes three
 // trips through HBM. Here the scores never leave the SM.
 //
-// One CTA per (batch, head, 128 query rows), 320 threads:
+// One CTA per (batch, head, 128 query rows), 320 threads (576 with four threads per row):
 //   warp 0     TMA: the Q tile once, then K and V tiles of 128 key rows through a 3-stage ring
 //   warp 1     one thread issues S_j = Q K_j^T (128 x 128 x 64) into one of two TMEM score buffers and
 //              T_j = P_j V_j (128 x 64 x 128) into one of two TMEM output-tile buffers; S_{j+1} is
@@ -19,6 +19,7 @@
 // The exponentials are the bound at this head size (one MUFU.EX2 per score).
 // Every wait is bounded as in the GEMM kernel; on timeout an error word is set and the CTA leaves.
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -26,7 +27,6 @@
 
 namespace cgb {
 
-constexpr int kAttnThreads = 320;
 constexpr int kAttnBM = 128;          // query rows per CTA = TMEM lanes
 constexpr int kAttnBN = 128;          // key rows per step
 constexpr int kAttnD = 64;            // head dim: 128 bytes of bf16 = one swizzle span
@@ -50,8 +50,30 @@ struct AttnParams {
     uint32_t* err_word;
 };
 
-template <typename T>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+// columns of one TMEM lane per thread: 16, 32 or 64 consecutive fp32 values
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, float (&v)[N]) {
+    static_assert(N == 16 || N == 32 || N == 64, "supported widths");
+    if constexpr (N == 16) {
+        uint32_t* r = reinterpret_cast<uint32_t*>(v);
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+            : "r"(taddr)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    } else if constexpr (N == 32) {
+        tmem_ld32(taddr, v);
+    } else {
+        tmem_ld32(taddr, *reinterpret_cast<float(*)[32]>(&v[0]));
+        tmem_ld32(taddr + 32, *reinterpret_cast<float(*)[32]>(&v[32]));
+    }
+}
+
+template <typename T, int kParts>
+__global__ void __launch_bounds__(64 + 128 * kParts, 1)
 attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -61,8 +83,9 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     __shared__ __align__(8) uint64_t bar_t_full[2], bar_t_empty[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile uint32_t abort_flag;
-    __shared__ float xval[2][2][128];          // row exchange between the two halves: [parity][half][row]
-    __shared__ volatile int xtag[2][2][128];
+    constexpr int kAttnThreads = 64 + 128 * kParts;
+    __shared__ float xval[2][kParts][128];     // row exchange between the threads of a row: [parity][part][row]
+    __shared__ volatile int xtag[2][kParts][128];
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t s_q = smem_base;
@@ -87,17 +110,17 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&bar_s_full[i]), 1);
-            mbar_init(smem_u32(&bar_s_empty[i]), 8);
-            mbar_init(smem_u32(&bar_p_full[i]), 8);
+            mbar_init(smem_u32(&bar_s_empty[i]), 4 * kParts);
+            mbar_init(smem_u32(&bar_p_full[i]), 4 * kParts);
             mbar_init(smem_u32(&bar_p_empty[i]), 1);
             mbar_init(smem_u32(&bar_t_full[i]), 1);
-            mbar_init(smem_u32(&bar_t_empty[i]), 8);
+            mbar_init(smem_u32(&bar_t_empty[i]), 4 * kParts);
         }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    for (int i = threadIdx.x; i < 2 * 2 * 128; i += kAttnThreads) (&xtag[0][0][0])[i] = 0;
+    for (int i = threadIdx.x; i < 2 * kParts * 128; i += kAttnThreads) (&xtag[0][0][0])[i] = 0;
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_u32(&tmem_base_slot)), "r"(kAttnTmemCols) : "memory");
@@ -170,50 +193,64 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
     } else {
         // ---------------- softmax + output accumulation ----------------
-        // Eight warps: two per TMEM lane quarter. Thread = (query row, half): it owns 64 of the 128 keys
-        // of each score tile and 32 of the 64 output columns. The two threads of a row exchange their
-        // partial row maxima (and, at the end, row sums) through shared memory.
+        // kParts warps per TMEM lane quarter. Thread = (query row, part): it owns kKeys of the 128 keys of
+        // each score tile and kCols of the 64 output columns. The threads of a row exchange their partial
+        // row maxima (and, at the end, row sums) through shared memory. More threads per row mean more
+        // warps per scheduler to hide the latencies of the dependent steps of a tile.
+        constexpr int kKeys = kAttnBN / kParts, kCols = kAttnD / kParts;
         const int q = warp & 3;
-        const int half = (warp - 2) >> 2;
+        const int part = (warp - 2) >> 2;
         const int row = q * 32 + lane;
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
-        float o[32];
+        float o[kCols];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = 0.0f;
+        for (int i = 0; i < kCols; ++i) o[i] = 0.0f;
         float m = -INFINITY, l = 0.0f, alpha_prev = 0.0f;
         bool ok = true;
-        // partner exchange: value + tag (tile number + 1), double-buffered by tile parity. Bounded.
-        auto exchange = [&](float mine, int seq, bool& good) -> float {
+        // row exchange: value + tag (sequence number), double-buffered by sequence parity. Bounded.
+        auto exchange = [&](float mine, int seq, bool is_max, bool& good) -> float {
             const int par = seq & 1;
-            xval[par][half][row] = mine;
+            xval[par][part][row] = mine;
             __threadfence_block();
-            xtag[par][half][row] = seq;
-            const volatile int* tag = &xtag[par][half ^ 1][row];
-            for (uint32_t it = 0; *tag != seq; ++it) {
-                if ((it & 0xff) == 0xff) {
-                    if (abort_flag) { good = false; return mine; }
-                    if (it > (1u << 26)) {   // about a second of polling
-                        abort_flag = 1;
-                        if (p.err_word) atomicCAS(p.err_word, 0u, 0x690u);
-                        good = false;
-                        return mine;
+            xtag[par][part][row] = seq;
+            float acc = mine;
+#pragma unroll
+            for (int pp = 0; pp < kParts; ++pp) {
+                if (pp == part) continue;
+                const volatile int* tag = &xtag[par][pp][row];
+                for (uint32_t it = 0; *tag != seq; ++it) {
+                    if ((it & 0xff) == 0xff) {
+                        if (abort_flag) { good = false; return mine; }
+                        if (it > (1u << 26)) {   // about a second of polling
+                            abort_flag = 1;
+                            if (p.err_word) atomicCAS(p.err_word, 0u, 0x690u);
+                            good = false;
+                            return mine;
+                        }
                     }
                 }
+                __threadfence_block();
+                const float v = xval[par][pp][row];
+                acc = is_max ? fmaxf(acc, v) : acc + v;
             }
-            __threadfence_block();
-            return xval[par][half ^ 1][row];
+            return acc;
         };
-        auto add_tile = [&](int i, float alpha) -> bool {   // o = o * alpha + T_i (this thread's 32 columns)
+        auto add_tile = [&](int i, float alpha) -> bool {   // o = o * alpha + T_i (this thread's columns)
             const int buf = i & 1;
             const uint32_t use = (uint32_t)(i >> 1);
             bool w = mbar_wait(smem_u32(&bar_t_full[buf]), use & 1u, &abort_flag, p.err_word, 0x660u + buf);
             w = __all_sync(0xffffffffu, w);
             if (!w) return false;
             tc_fence_after();
-            float t[32];
-            tmem_ld32(tmem_base + lane_base + kAttnTCol + (uint32_t)(buf * kAttnD + half * 32), t);
+            float t[kCols];
+            tmem_ld_cols<kCols>(tmem_base + lane_base + kAttnTCol + (uint32_t)(buf * kAttnD + part * kCols), t);
+            const float2 a2 = make_float2(alpha, alpha);
 #pragma unroll
-            for (int i2 = 0; i2 < 32; ++i2) o[i2] = fmaf(o[i2], alpha, t[i2]);
+            for (int i2 = 0; i2 < kCols; i2 += 2) {
+                const float2 r = __ffma2_rn(make_float2(o[i2], o[i2 + 1]), a2, make_float2(t[i2], t[i2 + 1]));
+                o[i2] = r.x;
+                o[i2 + 1] = r.y;
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bar_t_empty[buf]));
@@ -226,53 +263,65 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             w = __all_sync(0xffffffffu, w);
             if (!w) { ok = false; break; }
             tc_fence_after();
-            const uint32_t s_addr = tmem_base + lane_base + kAttnSCol + (uint32_t)(buf * kAttnBN + half * 64);
-            const long long kv0 = (long long)j * kAttnBN + half * 64;
-            const bool ragged = kv0 + 64 > p.S_kv;   // keys past S_kv are zero-filled rows of K
-            float s[64];
-            tmem_ld32(s_addr, *reinterpret_cast<float(*)[32]>(&s[0]));
-            tmem_ld32(s_addr + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+            const uint32_t s_addr = tmem_base + lane_base + kAttnSCol + (uint32_t)(buf * kAttnBN + part * kKeys);
+            const long long kv0 = (long long)j * kAttnBN + part * kKeys;
+            const bool ragged = kv0 + kKeys > p.S_kv;   // keys past S_kv are zero-filled rows of K
+            float s[kKeys];
+            tmem_ld_cols<kKeys>(s_addr, s);
             // the scores are in registers: the TMEM buffer can take S_{j+2}
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bar_s_empty[buf]));
-            float mx = -INFINITY;
+            if (ragged) {   // only the last key tile: mask the zero-filled keys
+                const int valid = (int)(p.S_kv - kv0);   // < kKeys here, may be <= 0
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                if (ragged && kv0 + i >= p.S_kv) s[i] = -INFINITY;
-                mx = fmaxf(mx, s[i]);
+                for (int i = 0; i < kKeys; ++i)
+                    if (i >= valid) s[i] = -INFINITY;
+            }
+            float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];   // four chains, not one long dependency
+#pragma unroll
+            for (int i = 4; i < kKeys; i += 4) {
+                mx0 = fmaxf(mx0, s[i]);
+                mx1 = fmaxf(mx1, s[i + 1]);
+                mx2 = fmaxf(mx2, s[i + 2]);
+                mx3 = fmaxf(mx3, s[i + 3]);
             }
             bool good = true;
-            const float mx_other = exchange(mx, j + 1, good);
+            const float mx = exchange(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), j + 1, true, good);
             good = __all_sync(0xffffffffu, good);
             if (!good) { ok = false; break; }
-            const float m_new = fmaxf(m, fmaxf(mx, mx_other) * p.scale_log2e);
+            const float m_new = fmaxf(m, mx * p.scale_log2e);
             const float alpha = (m == -INFINITY) ? 0.0f : ex2_approx(m - m_new);
             // the P buffer is free once T_{j-2} has consumed it
             w = mbar_wait(smem_u32(&bar_p_empty[buf]), (use & 1u) ^ 1u, &abort_flag, p.err_word, 0x680u + buf);
             w = __all_sync(0xffffffffu, w);
             if (!w) { ok = false; break; }
-            // p = 2^(s * scale * log2e - m_new); this half's 64 keys are one 128-byte swizzle span of P
-            float l_tile = 0.0f;
-            uint8_t* prow = p_gen + buf * kAttnPBytes + half * kAttnTileBytes + row * 128;
+            // p = 2^(s * scale * log2e - m_new). Pairs of keys per instruction where the ISA allows it
+            // (fp32x2 fma / add, packed convert): this loop is bound by instruction issue and the MUFU pipe.
+            float2 l2 = make_float2(0.0f, 0.0f);
+            const float2 sc2 = make_float2(p.scale_log2e, p.scale_log2e), nm2 = make_float2(-m_new, -m_new);
+            uint8_t* prow = p_gen + buf * kAttnPBytes + row * 128;
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {   // eight 16-byte pieces of 8 keys
+            for (int g = 0; g < kKeys / 8; ++g) {   // 16-byte pieces of 8 keys
                 float e[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    e[i] = ex2_approx(fmaf(s[g * 8 + i], p.scale_log2e, -m_new));   // 2^-inf = 0 for masked keys
-                    l_tile += e[i];
+                for (int i = 0; i < 8; i += 2) {
+                    const float2 t = __ffma2_rn(make_float2(s[g * 8 + i], s[g * 8 + i + 1]), sc2, nm2);
+                    const float2 ex = make_float2(ex2_approx(t.x), ex2_approx(t.y));   // 2^-inf = 0 for masked keys
+                    l2 = __fadd2_rn(l2, ex);
+                    e[i] = ex.x;
+                    e[i + 1] = ex.y;
                 }
-                // packed two-at-a-time conversion: single-value cvt instructions share the MUFU pipe with
-                // the exponentials, which is the pipe that bounds this kernel
                 const Vec16<T> o8 = pack16<T>(e);
-                *reinterpret_cast<int4*>(prow + ((g ^ (row & 7)) << 4)) = *reinterpret_cast<const int4*>(&o8);
+                const int piece = part * (kKeys / 8) + g;   // 0..15 along the 128 keys: 64-key span, slot in span
+                *reinterpret_cast<int4*>(prow + (piece >> 3) * kAttnTileBytes + (((piece & 7) ^ (row & 7)) << 4)) =
+                    *reinterpret_cast<const int4*>(&o8);
             }
             // P written through the generic proxy must be visible to the tensor pipe
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bar_p_full[buf]));
-            l = fmaf(l, alpha, l_tile);
+            l = fmaf(l, alpha, l2.x + l2.y);
             if (j > 0) ok = add_tile(j - 1, alpha_prev);
             alpha_prev = alpha;
             m = m_new;
@@ -280,14 +329,13 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         if (ok && n_tiles > 0) ok = add_tile(n_tiles - 1, alpha_prev);
         if (ok) {
             bool good = true;
-            const float l_other = exchange(l, n_tiles + 1, good);
+            const float lt = exchange(l, n_tiles + 1, false, good);
             if (good && q0 + row < p.S_q) {
-                const float lt = l + l_other;
                 const float inv = lt > 0.0f ? 1.0f / lt : 0.0f;
                 T* orow = static_cast<T*>(p.O) + (long long)b * p.o_stride_b + (long long)h * p.o_stride_h +
-                          (long long)(q0 + row) * p.ldo + half * 32;
+                          (long long)(q0 + row) * p.ldo + part * kCols;
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
+                for (int g = 0; g < kCols / 8; ++g) {
                     float e[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) e[i] = o[g * 8 + i] * inv;
@@ -390,15 +438,22 @@ extern "C" int cg_b200_attention(const cg_b200_attention_desc* desc, const void*
     const long long items = (long long)p.q_tiles * p.H * p.B;
     if (items > 0x7fffffffLL) return CG_B200_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
+    static const int parts = [] {   // CG_B200_ATTN_PARTS=2|4: threads per query row (a tuning knob)
+        const char* e = getenv("CG_B200_ATTN_PARTS");
+        return (e && e[0] == '4') ? 4 : 2;
+    }();
+#define CGB_ATTN_LAUNCH(TYPE, PARTS)                                                                          \
+    do {                                                                                                      \
+        auto kern = attention_sm100_kernel<TYPE, PARTS>;                                                      \
+        CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));          \
+        kern<<<(unsigned)items, 64 + 128 * PARTS, kAttnSmem, s>>>(tq, tk, tv, p);                              \
+    } while (0)
     if (d.dtype == CG_B200_BF16) {
-        auto kern = attention_sm100_kernel<__nv_bfloat16>;
-        CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
-        kern<<<(unsigned)items, kAttnThreads, kAttnSmem, s>>>(tq, tk, tv, p);
+        if (parts == 2) CGB_ATTN_LAUNCH(__nv_bfloat16, 2); else CGB_ATTN_LAUNCH(__nv_bfloat16, 4);
     } else {
-        auto kern = attention_sm100_kernel<__half>;
-        CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
-        kern<<<(unsigned)items, kAttnThreads, kAttnSmem, s>>>(tq, tk, tv, p);
+        if (parts == 2) CGB_ATTN_LAUNCH(__half, 2); else CGB_ATTN_LAUNCH(__half, 4);
     }
+#undef CGB_ATTN_LAUNCH
     CGB_CUDA(cudaGetLastError());
     return CG_B200_OK;
 }
