@@ -5,15 +5,18 @@
 // the path - matmul, softmax, matmul (src/ir/ops.cpp) - whose [B, H, S, S] intermediate makes three
 // trips through HBM. Here the scores never leave the SM.
 //
-// One CTA per (batch, head, 128 query rows), 320 threads (576 with four threads per row):
-//   warp 0     TMA: the Q tile once, then K and V tiles of 128 key rows through a 3-stage ring
-//   warp 1     one thread issues S_j = Q K_j^T (128 x 128 x 64) into one of two TMEM score buffers and
-//              T_j = P_j V_j (128 x 64 x 128) into one of two TMEM output-tile buffers; S_{j+1} is
-//              issued before T_j so the tensor pipe works while the softmax warps do
-//   warps 2-9  two threads per query row (64 keys and 32 output columns each): scores from TMEM to
-//              registers, row max exchanged through shared memory, p = 2^(s - m) and row sum, P_j written
-//              as bf16/f16 into 128-byte-swizzled shared memory (the A operand of T_j), running output
-//              in registers: O = O * 2^(m_old - m_new) + T_{j-1}
+// One CTA per (batch, head, 128 query rows), 320 threads:
+//   warp 0     TMA: the Q tile once, then K and V tiles of 128 key rows through a 4-stage ring
+//   warp 1     one thread issues S_j = Q K_j^T (128 x 128 x 64) into TMEM score buffer j&1 and
+//              T_j = P_j V_j (128 x 64 x 128) into TMEM output-tile buffer j&1
+//   warps 2-5  softmax group 0: the even key tiles;  warps 6-9  softmax group 1: the odd key tiles.
+//              One thread per query row, so no exchange between threads inside a tile: pass 1 reads the
+//              128 scores of the row from TMEM for the row max, pass 2 reads them again, p = 2^(s - m),
+//              row sum, P_j written as bf16/f16 into 128-byte-swizzled shared memory (the A operand of
+//              T_j). Each group keeps its own running (max, sum, output row) over its tiles:
+//              O = O * 2^(m_old - m_new) + T_j; the two are merged once at the end. The two warps that
+//              share a scheduler belong to different groups, i.e. to different tiles in different
+//              phases: one runs its exponentials while the other loads, reduces or waits.
 // Q, K, V are read in place from strided buffers (head = 64 contiguous columns of a row), so the
 // packed [rows, 3*d_model] output of a QKV projection needs no reshuffle. head_dim is 64.
 // The exponentials are the bound at this head size (one MUFU.EX2 per score).
@@ -21,6 +24,8 @@
 #include <math.h>
 #include <stdlib.h>
 #include <string.h>
+
+#include <type_traits>
 
 #include "common.cuh"
 #include "tc_sm100.cuh"
@@ -30,7 +35,8 @@ namespace cgb {
 constexpr int kAttnBM = 128;          // query rows per CTA = TMEM lanes
 constexpr int kAttnBN = 128;          // key rows per step
 constexpr int kAttnD = 64;            // head dim: 128 bytes of bf16 = one swizzle span
-constexpr int kAttnKVStages = 3;
+constexpr int kAttnKVStages = 4;
+constexpr int kAttnThreads = 320;
 constexpr int kAttnTileBytes = 128 * 128;                 // a 128-row x 128-byte tile (Q, K or V)
 constexpr int kAttnPBytes = 2 * kAttnTileBytes;           // P: 128 rows x 128 keys, two 64-key swizzle spans
 constexpr int kAttnSmem = kAttnTileBytes + kAttnKVStages * 2 * kAttnTileBytes + 2 * kAttnPBytes + 1024;
@@ -50,47 +56,22 @@ struct AttnParams {
     uint32_t* err_word;
 };
 
-// columns of one TMEM lane per thread: 16, 32 or 64 consecutive fp32 values
-template <int N>
-__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, float (&v)[N]) {
-    static_assert(N == 16 || N == 32 || N == 64, "supported widths");
-    if constexpr (N == 16) {
-        uint32_t* r = reinterpret_cast<uint32_t*>(v);
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-            : "r"(taddr)
-            : "memory");
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-    } else if constexpr (N == 32) {
-        tmem_ld32(taddr, v);
-    } else {
-        tmem_ld32(taddr, *reinterpret_cast<float(*)[32]>(&v[0]));
-        tmem_ld32(taddr + 32, *reinterpret_cast<float(*)[32]>(&v[32]));
-    }
-}
-
-template <typename T, int kParts>
-__global__ void __launch_bounds__(64 + 128 * kParts, 1)
+template <typename T>
+__global__ void __launch_bounds__(kAttnThreads, 1)
 attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_q;
     __shared__ __align__(8) uint64_t bar_kv_full[kAttnKVStages], bar_kv_empty[kAttnKVStages];
-    __shared__ __align__(8) uint64_t bar_s_full[2], bar_s_empty[2], bar_p_full[2], bar_p_empty[2];
-    __shared__ __align__(8) uint64_t bar_t_full[2], bar_t_empty[2];
+    __shared__ __align__(8) uint64_t bar_s_full[2], bar_p_full[2], bar_t_full[2], bar_t_empty[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile uint32_t abort_flag;
-    constexpr int kAttnThreads = 64 + 128 * kParts;
-    __shared__ float xval[2][kParts][128];     // row exchange between the threads of a row: [parity][part][row]
-    __shared__ volatile int xtag[2][kParts][128];
+    __shared__ float xm[2][128], xl[2][128];   // running max and sum of each group, for the final merge
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t s_q = smem_base;
     const uint32_t s_kv = s_q + kAttnTileBytes;                         // stage s: K at +s*2T, V at +s*2T + T
-    const uint32_t s_p = s_kv + kAttnKVStages * 2 * kAttnTileBytes;     // two P buffers
+    const uint32_t s_p = s_kv + kAttnKVStages * 2 * kAttnTileBytes;     // two P buffers, one per group
     uint8_t* const p_gen = smem_raw + (s_p - smem_u32(smem_raw));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -110,17 +91,14 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&bar_s_full[i]), 1);
-            mbar_init(smem_u32(&bar_s_empty[i]), 4 * kParts);
-            mbar_init(smem_u32(&bar_p_full[i]), 4 * kParts);
-            mbar_init(smem_u32(&bar_p_empty[i]), 1);
+            mbar_init(smem_u32(&bar_p_full[i]), 4);    // one arrival per warp of the group
             mbar_init(smem_u32(&bar_t_full[i]), 1);
-            mbar_init(smem_u32(&bar_t_empty[i]), 4 * kParts);
+            mbar_init(smem_u32(&bar_t_empty[i]), 4);
         }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    for (int i = threadIdx.x; i < 2 * kParts * 128; i += kAttnThreads) (&xtag[0][0][0])[i] = 0;
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_u32(&tmem_base_slot)), "r"(kAttnTmemCols) : "memory");
@@ -150,14 +128,34 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             bool ok = mbar_wait(smem_u32(&bar_q), 0, &abort_flag, p.err_word, 0x610u);
-            // T_i = P_i V_i: A = P_i (K-major, two 64-key spans), B = V_i ([key, d] with d contiguous: MN-major)
-            auto issue_t = [&](int i) -> bool {
-                const int buf = i & 1;
-                const uint32_t use = (uint32_t)(i >> 1);
-                if (!mbar_wait(smem_u32(&bar_p_full[buf]), use & 1u, &abort_flag, p.err_word, 0x620u + buf)) return false;
-                if (!mbar_wait(smem_u32(&bar_t_empty[buf]), (use & 1u) ^ 1u, &abort_flag, p.err_word, 0x630u + buf)) return false;
+            // S_i = Q K_i^T into score buffer i&1. The buffer is free: the group arrived on p_full for tile
+            // i-2 only after its last read of S_{i-2}.
+            auto issue_s = [&](int i) -> bool {
+                const int st = i % kAttnKVStages, buf = i & 1;
+                const uint32_t kv_use = (uint32_t)(i / kAttnKVStages);
+                if (!mbar_wait(smem_u32(&bar_kv_full[st]), kv_use & 1u, &abort_flag, p.err_word, 0x640u + st)) return false;
                 tc_fence_after();
-                const int st = i % kAttnKVStages;
+                const uint32_t kb = s_kv + st * 2 * kAttnTileBytes;
+                const uint32_t tmem_s = tmem_base + kAttnSCol + (uint32_t)(buf * kAttnBN);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {   // 16 of the 64 head dims per MMA
+                    const uint64_t da = make_smem_desc(s_q + k * 32, 16, 1024);
+                    const uint64_t db = make_smem_desc(kb + k * 32, 16, 1024);
+                    umma<false, 1>(tmem_s, da, db, p.idesc_s, k > 0 ? 1u : 0u);
+                }
+                tc_commit<1>(smem_u32(&bar_s_full[buf]));
+                return true;
+            };
+            if (ok && n_tiles > 0) ok = issue_s(0);
+            if (ok && n_tiles > 1) ok = issue_s(1);
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                // T_j = P_j V_j: A = P_j (K-major, two 64-key spans), B = V_j ([key, d] with d contiguous: MN-major)
+                const int buf = j & 1;
+                const uint32_t use = (uint32_t)(j >> 1);
+                if (!mbar_wait(smem_u32(&bar_p_full[buf]), use & 1u, &abort_flag, p.err_word, 0x620u + buf)) break;
+                if (!mbar_wait(smem_u32(&bar_t_empty[buf]), (use & 1u) ^ 1u, &abort_flag, p.err_word, 0x630u + buf)) break;
+                tc_fence_after();
+                const int st = j % kAttnKVStages;
                 const uint32_t pa = s_p + buf * kAttnPBytes;
                 const uint32_t vb = s_kv + st * 2 * kAttnTileBytes + kAttnTileBytes;
                 const uint32_t tmem_t = tmem_base + kAttnTCol + (uint32_t)(buf * kAttnD);
@@ -169,180 +167,164 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 }
                 tc_commit<1>(smem_u32(&bar_t_full[buf]));
                 tc_commit<1>(smem_u32(&bar_kv_empty[st]));
-                tc_commit<1>(smem_u32(&bar_p_empty[buf]));
-                return true;
-            };
-            for (int j = 0; ok && j < n_tiles; ++j) {
-                const int st = j % kAttnKVStages, buf = j & 1;
-                const uint32_t kv_use = (uint32_t)(j / kAttnKVStages), s_use = (uint32_t)(j >> 1);
-                if (!mbar_wait(smem_u32(&bar_kv_full[st]), kv_use & 1u, &abort_flag, p.err_word, 0x640u + st)) { ok = false; break; }
-                if (!mbar_wait(smem_u32(&bar_s_empty[buf]), (s_use & 1u) ^ 1u, &abort_flag, p.err_word, 0x650u + buf)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t kb = s_kv + st * 2 * kAttnTileBytes;
-                const uint32_t tmem_s = tmem_base + kAttnSCol + (uint32_t)(buf * kAttnBN);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {   // 16 of the 64 head dims per MMA
-                    const uint64_t da = make_smem_desc(s_q + k * 32, 16, 1024);
-                    const uint64_t db = make_smem_desc(kb + k * 32, 16, 1024);
-                    umma<false, 1>(tmem_s, da, db, p.idesc_s, k > 0 ? 1u : 0u);
-                }
-                tc_commit<1>(smem_u32(&bar_s_full[buf]));
-                if (j > 0) ok = issue_t(j - 1);
+                if (j + 2 < n_tiles) ok = issue_s(j + 2);
             }
-            if (ok && n_tiles > 0) issue_t(n_tiles - 1);
         }
     } else {
         // ---------------- softmax + output accumulation ----------------
-        // kParts warps per TMEM lane quarter. Thread = (query row, part): it owns kKeys of the 128 keys of
-        // each score tile and kCols of the 64 output columns. The threads of a row exchange their partial
-        // row maxima (and, at the end, row sums) through shared memory. More threads per row mean more
-        // warps per scheduler to hide the latencies of the dependent steps of a tile.
-        constexpr int kKeys = kAttnBN / kParts, kCols = kAttnD / kParts;
-        const int q = warp & 3;
-        const int part = (warp - 2) >> 2;
+        const int q = warp & 3;               // TMEM lane quarter this warp may read
+        const int g = (warp - 2) >> 2;        // group: key tiles g, g+2, g+4, ...
         const int row = q * 32 + lane;
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
-        float o[kCols];
+        const uint32_t s_addr = tmem_base + lane_base + kAttnSCol + (uint32_t)(g * kAttnBN);
+        const uint32_t t_addr = tmem_base + lane_base + kAttnTCol + (uint32_t)(g * kAttnD);
+        uint8_t* const prow = p_gen + g * kAttnPBytes + row * 128;
+        float o[kAttnD];
 #pragma unroll
-        for (int i = 0; i < kCols; ++i) o[i] = 0.0f;
+        for (int i = 0; i < kAttnD; ++i) o[i] = 0.0f;
         float m = -INFINITY, l = 0.0f, alpha_prev = 0.0f;
         bool ok = true;
-        // row exchange: value + tag (sequence number), double-buffered by sequence parity. Bounded.
-        auto exchange = [&](float mine, int seq, bool is_max, bool& good) -> float {
-            const int par = seq & 1;
-            xval[par][part][row] = mine;
-            __threadfence_block();
-            xtag[par][part][row] = seq;
-            float acc = mine;
-#pragma unroll
-            for (int pp = 0; pp < kParts; ++pp) {
-                if (pp == part) continue;
-                const volatile int* tag = &xtag[par][pp][row];
-                for (uint32_t it = 0; *tag != seq; ++it) {
-                    if ((it & 0xff) == 0xff) {
-                        if (abort_flag) { good = false; return mine; }
-                        if (it > (1u << 26)) {   // about a second of polling
-                            abort_flag = 1;
-                            if (p.err_word) atomicCAS(p.err_word, 0u, 0x690u);
-                            good = false;
-                            return mine;
-                        }
-                    }
-                }
-                __threadfence_block();
-                const float v = xval[par][pp][row];
-                acc = is_max ? fmaxf(acc, v) : acc + v;
-            }
-            return acc;
-        };
-        auto add_tile = [&](int i, float alpha) -> bool {   // o = o * alpha + T_i (this thread's columns)
-            const int buf = i & 1;
-            const uint32_t use = (uint32_t)(i >> 1);
-            bool w = mbar_wait(smem_u32(&bar_t_full[buf]), use & 1u, &abort_flag, p.err_word, 0x660u + buf);
+        auto add_tile = [&](uint32_t use, bool release) -> bool {   // o = o * alpha_prev + T (the group's last tile)
+            bool w = mbar_wait(smem_u32(&bar_t_full[g]), use & 1u, &abort_flag, p.err_word, 0x660u + g);
             w = __all_sync(0xffffffffu, w);
             if (!w) return false;
             tc_fence_after();
-            float t[kCols];
-            tmem_ld_cols<kCols>(tmem_base + lane_base + kAttnTCol + (uint32_t)(buf * kAttnD + part * kCols), t);
-            const float2 a2 = make_float2(alpha, alpha);
+            const float2 a2 = make_float2(alpha_prev, alpha_prev);
 #pragma unroll
-            for (int i2 = 0; i2 < kCols; i2 += 2) {
-                const float2 r = __ffma2_rn(make_float2(o[i2], o[i2 + 1]), a2, make_float2(t[i2], t[i2 + 1]));
-                o[i2] = r.x;
-                o[i2 + 1] = r.y;
+            for (int c = 0; c < kAttnD / 32; ++c) {
+                float t[32];
+                tmem_ld32(t_addr + c * 32, t);
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float2 r = __ffma2_rn(make_float2(o[c * 32 + i], o[c * 32 + i + 1]), a2, make_float2(t[i], t[i + 1]));
+                    o[c * 32 + i] = r.x;
+                    o[c * 32 + i + 1] = r.y;
+                }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar_t_empty[buf]));
+            if (release) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bar_t_empty[g]));
+            }
             return true;
         };
-        for (int j = 0; ok && j < n_tiles; ++j) {
-            const int buf = j & 1;
+        int last = -1;
+        for (int j = g; ok && j < n_tiles; j += 2) {
             const uint32_t use = (uint32_t)(j >> 1);
-            bool w = mbar_wait(smem_u32(&bar_s_full[buf]), use & 1u, &abort_flag, p.err_word, 0x670u + buf);
+            if (j >= 2) {
+                ok = add_tile(use - 1, true);
+                if (!ok) break;
+            }
+            bool w = mbar_wait(smem_u32(&bar_s_full[g]), use & 1u, &abort_flag, p.err_word, 0x670u + g);
             w = __all_sync(0xffffffffu, w);
             if (!w) { ok = false; break; }
             tc_fence_after();
-            const uint32_t s_addr = tmem_base + lane_base + kAttnSCol + (uint32_t)(buf * kAttnBN + part * kKeys);
-            const long long kv0 = (long long)j * kAttnBN + part * kKeys;
-            const bool ragged = kv0 + kKeys > p.S_kv;   // keys past S_kv are zero-filled rows of K
-            float s[kKeys];
-            tmem_ld_cols<kKeys>(s_addr, s);
-            // the scores are in registers: the TMEM buffer can take S_{j+2}
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar_s_empty[buf]));
-            if (ragged) {   // only the last key tile: mask the zero-filled keys
-                const int valid = (int)(p.S_kv - kv0);   // < kKeys here, may be <= 0
+            const long long kv0 = (long long)j * kAttnBN;
+            const bool ragged = kv0 + kAttnBN > p.S_kv;   // keys past S_kv are zero-filled rows of K
+            // pass 1: row max over the 128 keys of the tile
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;   // four chains
 #pragma unroll
-                for (int i = 0; i < kKeys; ++i)
-                    if (i >= valid) s[i] = -INFINITY;
-            }
-            float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];   // four chains, not one long dependency
+            for (int c = 0; c < kAttnBN / 32; ++c) {
+                float s[32];
+                tmem_ld32(s_addr + c * 32, s);
+                if (ragged) {   // only the last key tile: mask the zero-filled keys
+                    const int valid = (int)(p.S_kv - kv0) - c * 32;
 #pragma unroll
-            for (int i = 4; i < kKeys; i += 4) {
-                mx0 = fmaxf(mx0, s[i]);
-                mx1 = fmaxf(mx1, s[i + 1]);
-                mx2 = fmaxf(mx2, s[i + 2]);
-                mx3 = fmaxf(mx3, s[i + 3]);
+                    for (int i = 0; i < 32; ++i)
+                        if (i >= valid) s[i] = -INFINITY;
+                }
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    mx0 = fmaxf(mx0, s[i]);
+                    mx1 = fmaxf(mx1, s[i + 1]);
+                    mx2 = fmaxf(mx2, s[i + 2]);
+                    mx3 = fmaxf(mx3, s[i + 3]);
+                }
             }
-            bool good = true;
-            const float mx = exchange(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), j + 1, true, good);
-            good = __all_sync(0xffffffffu, good);
-            if (!good) { ok = false; break; }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));   // finite: a tile holds at least one key
             const float m_new = fmaxf(m, mx * p.scale_log2e);
             const float alpha = (m == -INFINITY) ? 0.0f : ex2_approx(m - m_new);
-            // the P buffer is free once T_{j-2} has consumed it
-            w = mbar_wait(smem_u32(&bar_p_empty[buf]), (use & 1u) ^ 1u, &abort_flag, p.err_word, 0x680u + buf);
-            w = __all_sync(0xffffffffu, w);
-            if (!w) { ok = false; break; }
-            // p = 2^(s * scale * log2e - m_new). Pairs of keys per instruction where the ISA allows it
-            // (fp32x2 fma / add, packed convert): this loop is bound by instruction issue and the MUFU pipe.
+            // pass 2: p = 2^(s * scale * log2e - m_new). Pairs of keys per instruction where the ISA allows
+            // it (fp32x2 fma / add, packed convert). The P buffer is free: T of the group's previous tile,
+            // its last reader, was waited for above.
             float2 l2 = make_float2(0.0f, 0.0f);
             const float2 sc2 = make_float2(p.scale_log2e, p.scale_log2e), nm2 = make_float2(-m_new, -m_new);
-            uint8_t* prow = p_gen + buf * kAttnPBytes + row * 128;
 #pragma unroll
-            for (int g = 0; g < kKeys / 8; ++g) {   // 16-byte pieces of 8 keys
-                float e[8];
+            for (int c = 0; c < kAttnBN / 32; ++c) {
+                float s[32];
+                tmem_ld32(s_addr + c * 32, s);
+                if (ragged) {
+                    const int valid = (int)(p.S_kv - kv0) - c * 32;
 #pragma unroll
-                for (int i = 0; i < 8; i += 2) {
-                    const float2 t = __ffma2_rn(make_float2(s[g * 8 + i], s[g * 8 + i + 1]), sc2, nm2);
-                    const float2 ex = make_float2(ex2_approx(t.x), ex2_approx(t.y));   // 2^-inf = 0 for masked keys
-                    l2 = __fadd2_rn(l2, ex);
-                    e[i] = ex.x;
-                    e[i + 1] = ex.y;
+                    for (int i = 0; i < 32; ++i)
+                        if (i >= valid) s[i] = -INFINITY;
                 }
-                const Vec16<T> o8 = pack16<T>(e);
-                const int piece = part * (kKeys / 8) + g;   // 0..15 along the 128 keys: 64-key span, slot in span
-                *reinterpret_cast<int4*>(prow + (piece >> 3) * kAttnTileBytes + (((piece & 7) ^ (row & 7)) << 4)) =
-                    *reinterpret_cast<const int4*>(&o8);
-            }
-            // P written through the generic proxy must be visible to the tensor pipe
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar_p_full[buf]));
-            l = fmaf(l, alpha, l2.x + l2.y);
-            if (j > 0) ok = add_tile(j - 1, alpha_prev);
-            alpha_prev = alpha;
-            m = m_new;
-        }
-        if (ok && n_tiles > 0) ok = add_tile(n_tiles - 1, alpha_prev);
-        if (ok) {
-            bool good = true;
-            const float lt = exchange(l, n_tiles + 1, false, good);
-            if (good && q0 + row < p.S_q) {
-                const float inv = lt > 0.0f ? 1.0f / lt : 0.0f;
-                T* orow = static_cast<T*>(p.O) + (long long)b * p.o_stride_b + (long long)h * p.o_stride_h +
-                          (long long)(q0 + row) * p.ldo + part * kCols;
 #pragma unroll
-                for (int g = 0; g < kCols / 8; ++g) {
+                for (int gi = 0; gi < 4; ++gi) {   // 16-byte pieces of 8 keys
                     float e[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) e[i] = o[g * 8 + i] * inv;
+                    for (int i = 0; i < 8; i += 2) {
+                        const float2 t = __ffma2_rn(make_float2(s[gi * 8 + i], s[gi * 8 + i + 1]), sc2, nm2);
+                        const float2 ex = make_float2(ex2_approx(t.x), ex2_approx(t.y));   // 2^-inf = 0 for masked keys
+                        l2 = __fadd2_rn(l2, ex);
+                        e[i] = ex.x;
+                        e[i + 1] = ex.y;
+                    }
                     const Vec16<T> o8 = pack16<T>(e);
-                    *reinterpret_cast<int4*>(orow + g * 8) = *reinterpret_cast<const int4*>(&o8);
+                    const int piece = c * 4 + gi;   // 0..15 along the 128 keys: 64-key span, slot in span
+                    *reinterpret_cast<int4*>(prow + (piece >> 3) * kAttnTileBytes + (((piece & 7) ^ (row & 7)) << 4)) =
+                        *reinterpret_cast<const int4*>(&o8);
                 }
             }
+            // P written through the generic proxy must be visible to the tensor pipe; the score buffer has
+            // been read for the last time
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_p_full[g]));
+            l = fmaf(l, alpha, l2.x + l2.y);
+            alpha_prev = alpha;
+            m = m_new;
+            last = j;
+        }
+        if (ok && last >= 0) ok = add_tile((uint32_t)(last >> 1), false);
+        // merge of the two groups: each hands the other the 32 output columns the other stores, through
+        // its own P buffer (free: the last T that read it was waited for), as [column][row] floats
+        float* const mine = reinterpret_cast<float*>(p_gen + g * kAttnPBytes);
+        const float* const theirs = reinterpret_cast<const float*>(p_gen + (g ^ 1) * kAttnPBytes);
+        auto hand_over = [&](auto other_cols) {
+            constexpr int kC0 = decltype(other_cols)::value;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) mine[c * 128 + row] = o[kC0 + c];
+        };
+        if (ok) {
+            xm[g][row] = m;
+            xl[g][row] = l;
+            if (g == 0) hand_over(std::integral_constant<int, 32>{}); else hand_over(std::integral_constant<int, 0>{});
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");   // every softmax thread gets here, after a timeout too
+        auto finish = [&](auto own_cols) {
+            constexpr int kC0 = decltype(own_cols)::value;
+            const float mo = xm[g ^ 1][row], lo = xl[g ^ 1][row];
+            const float mm = fmaxf(m, mo);
+            const float w_own = (m == -INFINITY) ? 0.0f : ex2_approx(m - mm);
+            const float w_oth = (mo == -INFINITY) ? 0.0f : ex2_approx(mo - mm);
+            const float lt = l * w_own + lo * w_oth;
+            const float inv = lt > 0.0f ? 1.0f / lt : 0.0f;
+            const float a = w_own * inv, bo = w_oth * inv;
+            T* orow = static_cast<T*>(p.O) + (long long)b * p.o_stride_b + (long long)h * p.o_stride_h +
+                      (long long)(q0 + row) * p.ldo + kC0;
+#pragma unroll
+            for (int gi = 0; gi < 4; ++gi) {
+                float e[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) e[i] = o[kC0 + gi * 8 + i] * a + theirs[(gi * 8 + i) * 128 + row] * bo;
+                const Vec16<T> o8 = pack16<T>(e);
+                *reinterpret_cast<int4*>(orow + gi * 8) = *reinterpret_cast<const int4*>(&o8);
+            }
+        };
+        if (ok && !abort_flag && q0 + row < p.S_q) {
+            if (g == 0) finish(std::integral_constant<int, 0>{}); else finish(std::integral_constant<int, 32>{});
         }
     }
 
@@ -438,22 +420,15 @@ extern "C" int cg_b200_attention(const cg_b200_attention_desc* desc, const void*
     const long long items = (long long)p.q_tiles * p.H * p.B;
     if (items > 0x7fffffffLL) return CG_B200_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    static const int parts = [] {   // CG_B200_ATTN_PARTS=2|4: threads per query row (a tuning knob)
-        const char* e = getenv("CG_B200_ATTN_PARTS");
-        return (e && e[0] == '4') ? 4 : 2;
-    }();
-#define CGB_ATTN_LAUNCH(TYPE, PARTS)                                                                          \
-    do {                                                                                                      \
-        auto kern = attention_sm100_kernel<TYPE, PARTS>;                                                      \
-        CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));          \
-        kern<<<(unsigned)items, 64 + 128 * PARTS, kAttnSmem, s>>>(tq, tk, tv, p);                              \
-    } while (0)
     if (d.dtype == CG_B200_BF16) {
-        if (parts == 2) CGB_ATTN_LAUNCH(__nv_bfloat16, 2); else CGB_ATTN_LAUNCH(__nv_bfloat16, 4);
+        auto kern = attention_sm100_kernel<__nv_bfloat16>;
+        CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
+        kern<<<(unsigned)items, kAttnThreads, kAttnSmem, s>>>(tq, tk, tv, p);
     } else {
-        if (parts == 2) CGB_ATTN_LAUNCH(__half, 2); else CGB_ATTN_LAUNCH(__half, 4);
+        auto kern = attention_sm100_kernel<__half>;
+        CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
+        kern<<<(unsigned)items, kAttnThreads, kAttnSmem, s>>>(tq, tk, tv, p);
     }
-#undef CGB_ATTN_LAUNCH
     CGB_CUDA(cudaGetLastError());
     return CG_B200_OK;
 }
