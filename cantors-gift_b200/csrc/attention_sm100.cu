@@ -6,17 +6,21 @@
 // trips through HBM. Here the scores never leave the SM.
 //
 // One CTA per (batch, head, 128 query rows), 320 threads:
-//   warp 0     TMA: the Q tile once, then K and V tiles of 128 key rows through a 4-stage ring
-//   warp 1     one thread issues S_j = Q K_j^T (128 x 128 x 64) into TMEM score buffer j&1 and
-//              T_j = P_j V_j (128 x 64 x 128) into TMEM output-tile buffer j&1
+//   warp 0     TMA: the Q tile once, then K and V tiles of 128 key rows through a 6-stage ring
+//   warp 1     issues S_j = Q K_j^T (128 x 128 x 64) into TMEM score buffer j%3 and
+//              T_j = P_j V_j (128 x 64 x 128, P_j read from TMEM) into TMEM output-tile buffer j&1.
+//              The warp runs its loop converged and one elected lane issues, which keeps descriptors
+//              and addresses in uniform registers. S_{j+3} is issued right behind T_j, so the scores
+//              of a group's next tile are complete long before the group asks for them.
 //   warps 2-5  softmax group 0: the even key tiles;  warps 6-9  softmax group 1: the odd key tiles.
 //              One thread per query row, so no exchange between threads inside a tile: pass 1 reads the
 //              128 scores of the row from TMEM for the row max, pass 2 reads them again, p = 2^(s - m),
-//              row sum, P_j written as bf16/f16 into 128-byte-swizzled shared memory (the A operand of
-//              T_j). Each group keeps its own running (max, sum, output row) over its tiles:
-//              O = O * 2^(m_old - m_new) + T_j; the two are merged once at the end. The two warps that
-//              share a scheduler belong to different groups, i.e. to different tiles in different
-//              phases: one runs its exponentials while the other loads, reduces or waits.
+//              row sum, and writes P_j as bf16/f16 pairs over the first 64 columns of the same score
+//              buffer (the writes trail the reads). Each group keeps its own running (max, sum, output
+//              row) over its tiles: O = O * 2^(m_old - m_new) + T_j; the two are merged once at the end
+//              through tensor memory. The two warps that share a scheduler belong to different groups,
+//              i.e. to different tiles in different phases: one runs its exponentials while the other
+//              loads, reduces or waits.
 // Q, K, V are read in place from strided buffers (head = 64 contiguous columns of a row), so the
 // packed [rows, 3*d_model] output of a QKV projection needs no reshuffle. head_dim is 64.
 // The exponentials are the bound at this head size (one MUFU.EX2 per score).
@@ -35,14 +39,14 @@ namespace cgb {
 constexpr int kAttnBM = 128;          // query rows per CTA = TMEM lanes
 constexpr int kAttnBN = 128;          // key rows per step
 constexpr int kAttnD = 64;            // head dim: 128 bytes of bf16 = one swizzle span
-constexpr int kAttnKVStages = 4;
+constexpr int kAttnKVStages = 6;
+constexpr int kAttnSBufs = 3;
 constexpr int kAttnThreads = 320;
 constexpr int kAttnTileBytes = 128 * 128;                 // a 128-row x 128-byte tile (Q, K or V)
-constexpr int kAttnPBytes = 2 * kAttnTileBytes;           // P: 128 rows x 128 keys, two 64-key swizzle spans
-constexpr int kAttnSmem = kAttnTileBytes + kAttnKVStages * 2 * kAttnTileBytes + 2 * kAttnPBytes + 1024;
+constexpr int kAttnSmem = kAttnTileBytes + kAttnKVStages * 2 * kAttnTileBytes + 1024;
 constexpr uint32_t kAttnTmemCols = 512;
-constexpr uint32_t kAttnSCol = 0;     // two score buffers of 128 columns
-constexpr uint32_t kAttnTCol = 256;   // two output-tile buffers of 64 columns
+constexpr uint32_t kAttnSCol = 0;     // three score buffers of 128 columns; P over the first 64 of each
+constexpr uint32_t kAttnTCol = 384;   // two output-tile buffers of 64 columns
 
 struct AttnParams {
     long long S_q, S_kv;
@@ -63,16 +67,14 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_q;
     __shared__ __align__(8) uint64_t bar_kv_full[kAttnKVStages], bar_kv_empty[kAttnKVStages];
-    __shared__ __align__(8) uint64_t bar_s_full[2], bar_p_full[2], bar_t_full[2], bar_t_empty[2];
+    __shared__ __align__(8) uint64_t bar_s_full[kAttnSBufs], bar_p_full[2], bar_t_full[2], bar_t_empty[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile uint32_t abort_flag;
     __shared__ float xm[2][128], xl[2][128];   // running max and sum of each group, for the final merge
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t s_q = smem_base;
-    const uint32_t s_kv = s_q + kAttnTileBytes;                         // stage s: K at +s*2T, V at +s*2T + T
-    const uint32_t s_p = s_kv + kAttnKVStages * 2 * kAttnTileBytes;     // two P buffers, one per group
-    uint8_t* const p_gen = smem_raw + (s_p - smem_u32(smem_raw));
+    const uint32_t s_kv = s_q + kAttnTileBytes;   // stage s: K at +s*2T, V at +s*2T + T
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     // work item: query tile fastest so that the CTAs of one head run together and share K, V in L2
@@ -89,8 +91,8 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             mbar_init(smem_u32(&bar_kv_full[s]), 1);
             mbar_init(smem_u32(&bar_kv_empty[s]), 1);
         }
+        for (int i = 0; i < kAttnSBufs; ++i) mbar_init(smem_u32(&bar_s_full[i]), 1);
         for (int i = 0; i < 2; ++i) {
-            mbar_init(smem_u32(&bar_s_full[i]), 1);
             mbar_init(smem_u32(&bar_p_full[i]), 4);    // one arrival per warp of the group
             mbar_init(smem_u32(&bar_t_full[i]), 1);
             mbar_init(smem_u32(&bar_t_empty[i]), 4);
@@ -126,77 +128,86 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            bool ok = mbar_wait(smem_u32(&bar_q), 0, &abort_flag, p.err_word, 0x610u);
-            // S_i = Q K_i^T into score buffer i&1. The buffer is free: the group arrived on p_full for tile
-            // i-2 only after its last read of S_{i-2}.
-            auto issue_s = [&](int i) -> bool {
-                const int st = i % kAttnKVStages, buf = i & 1;
-                const uint32_t kv_use = (uint32_t)(i / kAttnKVStages);
-                if (!mbar_wait(smem_u32(&bar_kv_full[st]), kv_use & 1u, &abort_flag, p.err_word, 0x640u + st)) return false;
-                tc_fence_after();
-                const uint32_t kb = s_kv + st * 2 * kAttnTileBytes;
-                const uint32_t tmem_s = tmem_base + kAttnSCol + (uint32_t)(buf * kAttnBN);
+        // The whole warp runs the loop and waits; one elected lane issues (see elect_one()).
+        bool ok = mbar_wait_poll(smem_u32(&bar_q), 0, &abort_flag, p.err_word, 0x610u);
+        ok = __all_sync(0xffffffffu, ok);
+        // S_i = Q K_i^T into score buffer i%3. The tensor pipe runs its instructions in issue order, and
+        // this is issued behind T_{i-3}, the last reader of that buffer (P_{i-3} lives in it).
+        auto issue_s = [&](int i) -> bool {
+            const int st = i % kAttnKVStages, sb = i % kAttnSBufs;
+            const uint32_t kv_use = (uint32_t)(i / kAttnKVStages);
+            bool w = mbar_wait_poll(smem_u32(&bar_kv_full[st]), kv_use & 1u, &abort_flag, p.err_word, 0x640u + st);
+            w = __all_sync(0xffffffffu, w);
+            if (!w) return false;
+            tc_fence_after();
+            const uint32_t kb = s_kv + st * 2 * kAttnTileBytes;
+            const uint32_t tmem_s = tmem_base + kAttnSCol + (uint32_t)(sb * kAttnBN);
+            if (elect_one()) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {   // 16 of the 64 head dims per MMA
                     const uint64_t da = make_smem_desc(s_q + k * 32, 16, 1024);
                     const uint64_t db = make_smem_desc(kb + k * 32, 16, 1024);
                     umma<false, 1>(tmem_s, da, db, p.idesc_s, k > 0 ? 1u : 0u);
                 }
-                tc_commit<1>(smem_u32(&bar_s_full[buf]));
-                return true;
-            };
-            if (ok && n_tiles > 0) ok = issue_s(0);
-            if (ok && n_tiles > 1) ok = issue_s(1);
-            for (int j = 0; ok && j < n_tiles; ++j) {
-                // T_j = P_j V_j: A = P_j (K-major, two 64-key spans), B = V_j ([key, d] with d contiguous: MN-major)
-                const int buf = j & 1;
-                const uint32_t use = (uint32_t)(j >> 1);
-                if (!mbar_wait(smem_u32(&bar_p_full[buf]), use & 1u, &abort_flag, p.err_word, 0x620u + buf)) break;
-                if (!mbar_wait(smem_u32(&bar_t_empty[buf]), (use & 1u) ^ 1u, &abort_flag, p.err_word, 0x630u + buf)) break;
-                tc_fence_after();
-                const int st = j % kAttnKVStages;
-                const uint32_t pa = s_p + buf * kAttnPBytes;
-                const uint32_t vb = s_kv + st * 2 * kAttnTileBytes + kAttnTileBytes;
-                const uint32_t tmem_t = tmem_base + kAttnTCol + (uint32_t)(buf * kAttnD);
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {   // 16 keys per MMA
-                    const uint64_t da = make_smem_desc(pa + (k >> 2) * kAttnTileBytes + (k & 3) * 32, 16, 1024);
-                    const uint64_t db = make_smem_desc(vb + k * 2048, kAttnTileBytes, 1024);
-                    umma<false, 1>(tmem_t, da, db, p.idesc_t, k > 0 ? 1u : 0u);
-                }
-                tc_commit<1>(smem_u32(&bar_t_full[buf]));
-                tc_commit<1>(smem_u32(&bar_kv_empty[st]));
-                if (j + 2 < n_tiles) ok = issue_s(j + 2);
+                tc_commit<1>(smem_u32(&bar_s_full[sb]));
             }
+            __syncwarp();
+            return true;
+        };
+        for (int i = 0; ok && i < kAttnSBufs && i < n_tiles; ++i) ok = issue_s(i);
+        for (int j = 0; ok && j < n_tiles; ++j) {
+            const int g = j & 1;
+            const uint32_t use = (uint32_t)(j >> 1);
+            // P_j is written (and S_j read for the last time); the group has taken T_{j-2} out of the buffer
+            bool w = mbar_wait_poll(smem_u32(&bar_p_full[g]), use & 1u, &abort_flag, p.err_word, 0x620u + g);
+            w = w && mbar_wait_poll(smem_u32(&bar_t_empty[g]), (use & 1u) ^ 1u, &abort_flag, p.err_word, 0x630u + g);
+            w = __all_sync(0xffffffffu, w);
+            if (!w) break;
+            tc_fence_after();
+            // T_j = P_j V_j: A = P_j in tensor memory, B = V_j ([key, d] with d contiguous: MN-major)
+            const int st = j % kAttnKVStages;
+            const uint32_t tmem_p = tmem_base + kAttnSCol + (uint32_t)((j % kAttnSBufs) * kAttnBN);
+            const uint32_t vb = s_kv + st * 2 * kAttnTileBytes + kAttnTileBytes;
+            const uint32_t tmem_t = tmem_base + kAttnTCol + (uint32_t)(g * kAttnD);
+            if (elect_one()) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {   // 16 keys per MMA: 8 columns of P
+                    const uint64_t db = make_smem_desc(vb + k * 2048, kAttnTileBytes, 1024);
+                    umma_ts(tmem_t, tmem_p + k * 8, db, p.idesc_t, k > 0 ? 1u : 0u);
+                }
+                tc_commit<1>(smem_u32(&bar_t_full[g]));
+                tc_commit<1>(smem_u32(&bar_kv_empty[st]));
+            }
+            __syncwarp();
+            if (j + kAttnSBufs < n_tiles) ok = issue_s(j + kAttnSBufs);
         }
     } else {
         // ---------------- softmax + output accumulation ----------------
-        const int q = warp & 3;               // TMEM lane quarter this warp may read
+        const int q = warp & 3;               // TMEM lane quarter this warp may access
         const int g = (warp - 2) >> 2;        // group: key tiles g, g+2, g+4, ...
         const int row = q * 32 + lane;
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
-        const uint32_t s_addr = tmem_base + lane_base + kAttnSCol + (uint32_t)(g * kAttnBN);
         const uint32_t t_addr = tmem_base + lane_base + kAttnTCol + (uint32_t)(g * kAttnD);
-        uint8_t* const prow = p_gen + g * kAttnPBytes + row * 128;
         float o[kAttnD];
 #pragma unroll
         for (int i = 0; i < kAttnD; ++i) o[i] = 0.0f;
         float m = -INFINITY, l = 0.0f, alpha_prev = 0.0f;
         bool ok = true;
         auto add_tile = [&](uint32_t use, bool release) -> bool {   // o = o * alpha_prev + T (the group's last tile)
-            bool w = mbar_wait(smem_u32(&bar_t_full[g]), use & 1u, &abort_flag, p.err_word, 0x660u + g);
+            bool w = mbar_wait_poll(smem_u32(&bar_t_full[g]), use & 1u, &abort_flag, p.err_word, 0x660u + g);
             w = __all_sync(0xffffffffu, w);
             if (!w) return false;
             tc_fence_after();
             const float2 a2 = make_float2(alpha_prev, alpha_prev);
+            float t[2][32];
+            tmem_ld32_issue(t_addr, t[0]);
+            tmem_ld32_issue(t_addr + 32, t[1]);
 #pragma unroll
-            for (int c = 0; c < kAttnD / 32; ++c) {
-                float t[32];
-                tmem_ld32(t_addr + c * 32, t);
+            for (int c = 0; c < 2; ++c) {
+                tmem_ld_wait(t[c]);
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    const float2 r = __ffma2_rn(make_float2(o[c * 32 + i], o[c * 32 + i + 1]), a2, make_float2(t[i], t[i + 1]));
+                    const float2 r = __ffma2_rn(make_float2(o[c * 32 + i], o[c * 32 + i + 1]), a2, make_float2(t[c][i], t[c][i + 1]));
                     o[c * 32 + i] = r.x;
                     o[c * 32 + i + 1] = r.y;
                 }
@@ -211,11 +222,9 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         int last = -1;
         for (int j = g; ok && j < n_tiles; j += 2) {
             const uint32_t use = (uint32_t)(j >> 1);
-            if (j >= 2) {
-                ok = add_tile(use - 1, true);
-                if (!ok) break;
-            }
-            bool w = mbar_wait(smem_u32(&bar_s_full[g]), use & 1u, &abort_flag, p.err_word, 0x670u + g);
+            const int sb = j % kAttnSBufs;
+            const uint32_t s_addr = tmem_base + lane_base + kAttnSCol + (uint32_t)(sb * kAttnBN);
+            bool w = mbar_wait_poll(smem_u32(&bar_s_full[sb]), (uint32_t)(j / kAttnSBufs) & 1u, &abort_flag, p.err_word, 0x670u + sb);
             w = __all_sync(0xffffffffu, w);
             if (!w) { ok = false; break; }
             tc_fence_after();
@@ -223,62 +232,80 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             const bool ragged = kv0 + kAttnBN > p.S_kv;   // keys past S_kv are zero-filled rows of K
             // pass 1: row max over the 128 keys of the tile
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;   // four chains
+            {
+                float s[2][32];
+                tmem_ld32_issue(s_addr, s[0]);
+                tmem_ld32_issue(s_addr + 32, s[1]);
 #pragma unroll
-            for (int c = 0; c < kAttnBN / 32; ++c) {
-                float s[32];
-                tmem_ld32(s_addr + c * 32, s);
-                if (ragged) {   // only the last key tile: mask the zero-filled keys
-                    const int valid = (int)(p.S_kv - kv0) - c * 32;
+                for (int c = 0; c < 4; ++c) {
+                    float (&cur)[32] = s[c & 1];
+                    tmem_ld_wait(cur);
+                    if (ragged) {   // only the last key tile: mask the zero-filled keys
+                        const int valid = (int)(p.S_kv - kv0) - c * 32;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (i >= valid) s[i] = -INFINITY;
-                }
+                        for (int i = 0; i < 32; ++i)
+                            if (i >= valid) cur[i] = -INFINITY;
+                    }
 #pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    mx0 = fmaxf(mx0, s[i]);
-                    mx1 = fmaxf(mx1, s[i + 1]);
-                    mx2 = fmaxf(mx2, s[i + 2]);
-                    mx3 = fmaxf(mx3, s[i + 3]);
+                    for (int i = 0; i < 32; i += 4) {
+                        mx0 = fmaxf(mx0, cur[i]);
+                        mx1 = fmaxf(mx1, cur[i + 1]);
+                        mx2 = fmaxf(mx2, cur[i + 2]);
+                        mx3 = fmaxf(mx3, cur[i + 3]);
+                    }
+                    if (c + 2 < 4) tmem_ld32_issue(s_addr + (c + 2) * 32, cur);
                 }
             }
             const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));   // finite: a tile holds at least one key
             const float m_new = fmaxf(m, mx * p.scale_log2e);
             const float alpha = (m == -INFINITY) ? 0.0f : ex2_approx(m - m_new);
+            // the group's previous tile, out of its T buffer before T_j is issued into it
+            if (j >= 2) {
+                ok = add_tile(use - 1, true);
+                if (!ok) break;
+            }
             // pass 2: p = 2^(s * scale * log2e - m_new). Pairs of keys per instruction where the ISA allows
-            // it (fp32x2 fma / add, packed convert). The P buffer is free: T of the group's previous tile,
-            // its last reader, was waited for above.
+            // it (fp32x2 fma / add, packed convert). P goes over the first 64 columns of the score buffer:
+            // chunk c is written to columns 16c.. after columns up to 32c+31 have been read, and the chunk
+            // loaded ahead lies further right still.
             float2 l2 = make_float2(0.0f, 0.0f);
             const float2 sc2 = make_float2(p.scale_log2e, p.scale_log2e), nm2 = make_float2(-m_new, -m_new);
+            float s[2][32];
+            tmem_ld32_issue(s_addr, s[0]);
 #pragma unroll
-            for (int c = 0; c < kAttnBN / 32; ++c) {
-                float s[32];
-                tmem_ld32(s_addr + c * 32, s);
+            for (int c = 0; c < 4; ++c) {
+                float (&cur)[32] = s[c & 1];
+                tmem_ld_wait(cur);
+                if (c + 1 < 4) tmem_ld32_issue(s_addr + (c + 1) * 32, s[(c + 1) & 1]);
                 if (ragged) {
                     const int valid = (int)(p.S_kv - kv0) - c * 32;
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
-                        if (i >= valid) s[i] = -INFINITY;
+                        if (i >= valid) cur[i] = -INFINITY;
                 }
+                uint32_t pk[16];
 #pragma unroll
-                for (int gi = 0; gi < 4; ++gi) {   // 16-byte pieces of 8 keys
+                for (int gi = 0; gi < 4; ++gi) {   // 8 keys at a time
                     float e[8];
 #pragma unroll
                     for (int i = 0; i < 8; i += 2) {
-                        const float2 t = __ffma2_rn(make_float2(s[gi * 8 + i], s[gi * 8 + i + 1]), sc2, nm2);
+                        const float2 t = __ffma2_rn(make_float2(cur[gi * 8 + i], cur[gi * 8 + i + 1]), sc2, nm2);
                         const float2 ex = make_float2(ex2_approx(t.x), ex2_approx(t.y));   // 2^-inf = 0 for masked keys
                         l2 = __fadd2_rn(l2, ex);
                         e[i] = ex.x;
                         e[i + 1] = ex.y;
                     }
                     const Vec16<T> o8 = pack16<T>(e);
-                    const int piece = c * 4 + gi;   // 0..15 along the 128 keys: 64-key span, slot in span
-                    *reinterpret_cast<int4*>(prow + (piece >> 3) * kAttnTileBytes + (((piece & 7) ^ (row & 7)) << 4)) =
-                        *reinterpret_cast<const int4*>(&o8);
+                    const uint4 u = *reinterpret_cast<const uint4*>(&o8);
+                    pk[gi * 4 + 0] = u.x;
+                    pk[gi * 4 + 1] = u.y;
+                    pk[gi * 4 + 2] = u.z;
+                    pk[gi * 4 + 3] = u.w;
                 }
+                tmem_st16(s_addr + c * 16, pk);   // keys 32c .. 32c+31 of this row, two per column
             }
-            // P written through the generic proxy must be visible to the tensor pipe; the score buffer has
-            // been read for the last time
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            // P is complete in tensor memory and the scores have been read for the last time
+            tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bar_p_full[g]));
@@ -289,20 +316,23 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
         if (ok && last >= 0) ok = add_tile((uint32_t)(last >> 1), false);
         // merge of the two groups: each hands the other the 32 output columns the other stores, through
-        // its own P buffer (free: the last T that read it was waited for), as [column][row] floats
-        float* const mine = reinterpret_cast<float*>(p_gen + g * kAttnPBytes);
-        const float* const theirs = reinterpret_cast<const float*>(p_gen + (g ^ 1) * kAttnPBytes);
+        // its own T buffer in tensor memory (both groups' warps of a lane quarter reach the same lanes)
         auto hand_over = [&](auto other_cols) {
             constexpr int kC0 = decltype(other_cols)::value;
+            uint32_t r[32];
 #pragma unroll
-            for (int c = 0; c < 32; ++c) mine[c * 128 + row] = o[kC0 + c];
+            for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(o[kC0 + c]);
+            tmem_st32(t_addr, r);
+            tmem_wait_st();
         };
         if (ok) {
             xm[g][row] = m;
             xl[g][row] = l;
             if (g == 0) hand_over(std::integral_constant<int, 32>{}); else hand_over(std::integral_constant<int, 0>{});
         }
+        tc_fence_before();
         asm volatile("bar.sync 1, 256;" ::: "memory");   // every softmax thread gets here, after a timeout too
+        tc_fence_after();
         auto finish = [&](auto own_cols) {
             constexpr int kC0 = decltype(own_cols)::value;
             const float mo = xm[g ^ 1][row], lo = xl[g ^ 1][row];
@@ -312,18 +342,22 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             const float lt = l * w_own + lo * w_oth;
             const float inv = lt > 0.0f ? 1.0f / lt : 0.0f;
             const float a = w_own * inv, bo = w_oth * inv;
-            T* orow = static_cast<T*>(p.O) + (long long)b * p.o_stride_b + (long long)h * p.o_stride_h +
-                      (long long)(q0 + row) * p.ldo + kC0;
+            float theirs[32];
+            tmem_ld32(tmem_base + lane_base + kAttnTCol + (uint32_t)((g ^ 1) * kAttnD), theirs);
+            if (q0 + row < p.S_q) {
+                T* orow = static_cast<T*>(p.O) + (long long)b * p.o_stride_b + (long long)h * p.o_stride_h +
+                          (long long)(q0 + row) * p.ldo + kC0;
 #pragma unroll
-            for (int gi = 0; gi < 4; ++gi) {
-                float e[8];
+                for (int gi = 0; gi < 4; ++gi) {
+                    float e[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) e[i] = o[kC0 + gi * 8 + i] * a + theirs[(gi * 8 + i) * 128 + row] * bo;
-                const Vec16<T> o8 = pack16<T>(e);
-                *reinterpret_cast<int4*>(orow + gi * 8) = *reinterpret_cast<const int4*>(&o8);
+                    for (int i = 0; i < 8; ++i) e[i] = o[kC0 + gi * 8 + i] * a + theirs[gi * 8 + i] * bo;
+                    const Vec16<T> o8 = pack16<T>(e);
+                    *reinterpret_cast<int4*>(orow + gi * 8) = *reinterpret_cast<const int4*>(&o8);
+                }
             }
         };
-        if (ok && !abort_flag && q0 + row < p.S_q) {
+        if (__all_sync(0xffffffffu, ok && !abort_flag)) {   // warp-uniform: the TMEM load inside is warp-collective
             if (g == 0) finish(std::integral_constant<int, 0>{}); else finish(std::integral_constant<int, 32>{});
         }
     }
