@@ -60,6 +60,12 @@ struct AttnParams {
     uint32_t* err_word;
 };
 
+__device__ __forceinline__ float fmax3(float a, float b, float c) {   // one instruction on sm_100
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -67,7 +73,7 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_q;
     __shared__ __align__(8) uint64_t bar_kv_full[kAttnKVStages], bar_kv_empty[kAttnKVStages];
-    __shared__ __align__(8) uint64_t bar_s_full[kAttnSBufs], bar_p_full[2], bar_t_full[2], bar_t_empty[2];
+    __shared__ __align__(8) uint64_t bar_s_full[kAttnSBufs], bar_p_full[2], bar_t_full[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile uint32_t abort_flag;
     __shared__ float xm[2][128], xl[2][128];   // running max and sum of each group, for the final merge
@@ -95,7 +101,6 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&bar_p_full[i]), 4);    // one arrival per warp of the group
             mbar_init(smem_u32(&bar_t_full[i]), 1);
-            mbar_init(smem_u32(&bar_t_empty[i]), 4);
         }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -133,13 +138,14 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         ok = __all_sync(0xffffffffu, ok);
         // S_i = Q K_i^T into score buffer i%3. The tensor pipe runs its instructions in issue order, and
         // this is issued behind T_{i-3}, the last reader of that buffer (P_{i-3} lives in it).
-        auto issue_s = [&](int i) -> bool {
-            const int st = i % kAttnKVStages, sb = i % kAttnSBufs;
+        auto wait_kv = [&](int i) -> bool {
+            const int st = i % kAttnKVStages;
             const uint32_t kv_use = (uint32_t)(i / kAttnKVStages);
             bool w = mbar_wait_poll(smem_u32(&bar_kv_full[st]), kv_use & 1u, &abort_flag, p.err_word, 0x640u + st);
-            w = __all_sync(0xffffffffu, w);
-            if (!w) return false;
-            tc_fence_after();
+            return __all_sync(0xffffffffu, w);
+        };
+        auto issue_s = [&](int i) {   // after wait_kv(i)
+            const int st = i % kAttnKVStages, sb = i % kAttnSBufs;
             const uint32_t kb = s_kv + st * 2 * kAttnTileBytes;
             const uint32_t tmem_s = tmem_base + kAttnSCol + (uint32_t)(sb * kAttnBN);
             if (elect_one()) {
@@ -152,15 +158,20 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 tc_commit<1>(smem_u32(&bar_s_full[sb]));
             }
             __syncwarp();
-            return true;
         };
-        for (int i = 0; ok && i < kAttnSBufs && i < n_tiles; ++i) ok = issue_s(i);
+        for (int i = 0; ok && i < kAttnSBufs && i < n_tiles; ++i) {
+            ok = wait_kv(i);
+            tc_fence_after();
+            if (ok) issue_s(i);
+        }
         for (int j = 0; ok && j < n_tiles; ++j) {
             const int g = j & 1;
             const uint32_t use = (uint32_t)(j >> 1);
-            // P_j is written (and S_j read for the last time); the group has taken T_{j-2} out of the buffer
+            // K of the scores issued behind T_j (its V is in the same stage as K_j, here since S_j)
+            if (j + kAttnSBufs < n_tiles && !wait_kv(j + kAttnSBufs)) break;
+            // P_j is written and S_j read for the last time; before that the group took T_{j-2} out of
+            // the output-tile buffer
             bool w = mbar_wait_poll(smem_u32(&bar_p_full[g]), use & 1u, &abort_flag, p.err_word, 0x620u + g);
-            w = w && mbar_wait_poll(smem_u32(&bar_t_empty[g]), (use & 1u) ^ 1u, &abort_flag, p.err_word, 0x630u + g);
             w = __all_sync(0xffffffffu, w);
             if (!w) break;
             tc_fence_after();
@@ -179,7 +190,7 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 tc_commit<1>(smem_u32(&bar_kv_empty[st]));
             }
             __syncwarp();
-            if (j + kAttnSBufs < n_tiles) ok = issue_s(j + kAttnSBufs);
+            if (j + kAttnSBufs < n_tiles) issue_s(j + kAttnSBufs);
         }
     } else {
         // ---------------- softmax + output accumulation ----------------
@@ -193,7 +204,7 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         for (int i = 0; i < kAttnD; ++i) o[i] = 0.0f;
         float m = -INFINITY, l = 0.0f, alpha_prev = 0.0f;
         bool ok = true;
-        auto add_tile = [&](uint32_t use, bool release) -> bool {   // o = o * alpha_prev + T (the group's last tile)
+        auto add_tile = [&](uint32_t use) -> bool {   // o = o * alpha_prev + T (the group's last tile)
             bool w = mbar_wait_poll(smem_u32(&bar_t_full[g]), use & 1u, &abort_flag, p.err_word, 0x660u + g);
             w = __all_sync(0xffffffffu, w);
             if (!w) return false;
@@ -211,11 +222,6 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     o[c * 32 + i] = r.x;
                     o[c * 32 + i + 1] = r.y;
                 }
-            }
-            if (release) {
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bar_t_empty[g]));
             }
             return true;
         };
@@ -247,11 +253,11 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                             if (i >= valid) cur[i] = -INFINITY;
                     }
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        mx0 = fmaxf(mx0, cur[i]);
-                        mx1 = fmaxf(mx1, cur[i + 1]);
-                        mx2 = fmaxf(mx2, cur[i + 2]);
-                        mx3 = fmaxf(mx3, cur[i + 3]);
+                    for (int i = 0; i < 32; i += 8) {
+                        mx0 = fmax3(mx0, cur[i], cur[i + 1]);
+                        mx1 = fmax3(mx1, cur[i + 2], cur[i + 3]);
+                        mx2 = fmax3(mx2, cur[i + 4], cur[i + 5]);
+                        mx3 = fmax3(mx3, cur[i + 6], cur[i + 7]);
                     }
                     if (c + 2 < 4) tmem_ld32_issue(s_addr + (c + 2) * 32, cur);
                 }
@@ -261,7 +267,7 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             const float alpha = (m == -INFINITY) ? 0.0f : ex2_approx(m - m_new);
             // the group's previous tile, out of its T buffer before T_j is issued into it
             if (j >= 2) {
-                ok = add_tile(use - 1, true);
+                ok = add_tile(use - 1);
                 if (!ok) break;
             }
             // pass 2: p = 2^(s * scale * log2e - m_new). Pairs of keys per instruction where the ISA allows
@@ -314,7 +320,7 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             m = m_new;
             last = j;
         }
-        if (ok && last >= 0) ok = add_tile((uint32_t)(last >> 1), false);
+        if (ok && last >= 0) ok = add_tile((uint32_t)(last >> 1));
         // merge of the two groups: each hands the other the 32 output columns the other stores, through
         // its own T buffer in tensor memory (both groups' warps of a lane quarter reach the same lanes)
         auto hand_over = [&](auto other_cols) {
