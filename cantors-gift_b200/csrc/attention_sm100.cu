@@ -5,22 +5,23 @@
 // the path - matmul, softmax, matmul (src/ir/ops.cpp) - whose [B, H, S, S] intermediate makes three
 // trips through HBM. Here the scores never leave the SM.
 //
-// One CTA per (batch, head, 128 query rows), 320 threads:
-//   warp 0     TMA: the Q tile once, then K and V tiles of 128 key rows through a 6-stage ring
-//   warp 1     issues S_j = Q K_j^T (128 x 128 x 64) into TMEM score buffer j%3 and
-//              T_j = P_j V_j (128 x 64 x 128, P_j read from TMEM) into TMEM output-tile buffer j&1.
+// One CTA per (batch, head, 256 query rows = two query tiles), 320 threads. Both query tiles meet each
+// K/V tile while it is in shared memory, which halves the K/V traffic from L2 - the first limit of a
+// one-tile CTA at head_dim 64. Work item w = 2 j + g is (key tile j, query tile g):
+//   warp 0     TMA: the two Q tiles once, then K and V tiles of 128 key rows through a 6-stage ring
+//   warp 1     issues S_w = Q_g K_j^T (128 x 128 x 64) into TMEM score buffer w%3 and
+//              T_w = P_w V_j (128 x 64 x 128, P_w read from TMEM) into TMEM output-tile buffer g.
 //              The warp runs its loop converged and one elected lane issues, which keeps descriptors
-//              and addresses in uniform registers. S_{j+3} is issued right behind T_j, so the scores
-//              of a group's next tile are complete long before the group asks for them.
-//   warps 2-5  softmax group 0: the even key tiles;  warps 6-9  softmax group 1: the odd key tiles.
-//              One thread per query row, so no exchange between threads inside a tile: pass 1 reads the
-//              128 scores of the row from TMEM for the row max, pass 2 reads them again, p = 2^(s - m),
-//              row sum, and writes P_j as bf16/f16 pairs over the first 64 columns of the same score
-//              buffer (the writes trail the reads). Each group keeps its own running (max, sum, output
-//              row) over its tiles: O = O * 2^(m_old - m_new) + T_j; the two are merged once at the end
-//              through tensor memory. The two warps that share a scheduler belong to different groups,
-//              i.e. to different tiles in different phases: one runs its exponentials while the other
-//              loads, reduces or waits.
+//              and addresses in uniform registers. S_{w+3} is issued right behind T_w, so the scores
+//              of a group's next item are complete before the group asks for them.
+//   warps 2-5  softmax group 0: query tile 0;  warps 6-9  softmax group 1: query tile 1.
+//              One thread per query row, so no exchange between threads: pass 1 reads the 128 scores
+//              of the row from TMEM for the row max, pass 2 reads them again, p = 2^(s - m), row sum,
+//              and writes P_w as bf16/f16 pairs over the first 64 columns of the same score buffer
+//              (the writes trail the reads). Running output row in registers:
+//              O = O * 2^(m_old - m_new) + T_w. The two warps that share a scheduler belong to
+//              different groups, i.e. to different items in different phases: one runs its
+//              exponentials while the other loads, reduces or waits.
 // Q, K, V are read in place from strided buffers (head = 64 contiguous columns of a row), so the
 // packed [rows, 3*d_model] output of a QKV projection needs no reshuffle. head_dim is 64.
 // The exponentials are the bound at this head size (one MUFU.EX2 per score).
@@ -29,21 +30,20 @@
 #include <stdlib.h>
 #include <string.h>
 
-#include <type_traits>
-
 #include "common.cuh"
 #include "tc_sm100.cuh"
 
 namespace cgb {
 
-constexpr int kAttnBM = 128;          // query rows per CTA = TMEM lanes
+constexpr int kAttnBM = 128;          // query rows per tile = TMEM lanes
+constexpr int kAttnQRows = 2 * kAttnBM;   // query rows per CTA
 constexpr int kAttnBN = 128;          // key rows per step
 constexpr int kAttnD = 64;            // head dim: 128 bytes of bf16 = one swizzle span
 constexpr int kAttnKVStages = 6;
 constexpr int kAttnSBufs = 3;
 constexpr int kAttnThreads = 320;
 constexpr int kAttnTileBytes = 128 * 128;                 // a 128-row x 128-byte tile (Q, K or V)
-constexpr int kAttnSmem = kAttnTileBytes + kAttnKVStages * 2 * kAttnTileBytes + 1024;
+constexpr int kAttnSmem = 2 * kAttnTileBytes + kAttnKVStages * 2 * kAttnTileBytes + 1024;
 constexpr uint32_t kAttnTmemCols = 512;
 constexpr uint32_t kAttnSCol = 0;     // three score buffers of 128 columns; P over the first 64 of each
 constexpr uint32_t kAttnTCol = 384;   // two output-tile buffers of 64 columns
@@ -76,11 +76,10 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     __shared__ __align__(8) uint64_t bar_s_full[kAttnSBufs], bar_p_full[2], bar_t_full[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile uint32_t abort_flag;
-    __shared__ float xm[2][128], xl[2][128];   // running max and sum of each group, for the final merge
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t s_q = smem_base;
-    const uint32_t s_kv = s_q + kAttnTileBytes;   // stage s: K at +s*2T, V at +s*2T + T
+    const uint32_t s_kv = s_q + 2 * kAttnTileBytes;   // stage s: K at +s*2T, V at +s*2T + T
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     // work item: query tile fastest so that the CTAs of one head run together and share K, V in L2
@@ -88,7 +87,7 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const int qt = (int)(item % p.q_tiles);
     const int h = (int)((item / p.q_tiles) % p.H);
     const int b = (int)(item / ((long long)p.q_tiles * p.H));
-    const int q0 = qt * kAttnBM;
+    const int q0 = qt * kAttnQRows;
     const int n_tiles = p.kv_tiles;
 
     if (threadIdx.x == 0) {
@@ -119,8 +118,9 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            mbar_expect_tx(smem_u32(&bar_q), kAttnTileBytes);
+            mbar_expect_tx(smem_u32(&bar_q), 2 * kAttnTileBytes);   // rows past S_q arrive as zeros
             tma_load_4d<1>(s_q, &tm_q, smem_u32(&bar_q), 0, q0, h, b);
+            tma_load_4d<1>(s_q + kAttnTileBytes, &tm_q, smem_u32(&bar_q), 0, q0 + kAttnBM, h, b);
             for (int j = 0; j < n_tiles; ++j) {
                 const int st = j % kAttnKVStages;
                 const uint32_t use = (uint32_t)(j / kAttnKVStages);
@@ -136,22 +136,25 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         // The whole warp runs the loop and waits; one elected lane issues (see elect_one()).
         bool ok = mbar_wait_poll(smem_u32(&bar_q), 0, &abort_flag, p.err_word, 0x610u);
         ok = __all_sync(0xffffffffu, ok);
-        // S_i = Q K_i^T into score buffer i%3. The tensor pipe runs its instructions in issue order, and
-        // this is issued behind T_{i-3}, the last reader of that buffer (P_{i-3} lives in it).
-        auto wait_kv = [&](int i) -> bool {
-            const int st = i % kAttnKVStages;
-            const uint32_t kv_use = (uint32_t)(i / kAttnKVStages);
+        // S_w = Q_g K_j^T into score buffer w%3. The tensor pipe runs its instructions in issue order, and
+        // this is issued behind T_{w-3}, the last reader of that buffer (P_{w-3} lives in it).
+        const int n_items = 2 * n_tiles;
+        auto wait_kv = [&](int j) -> bool {
+            const int st = j % kAttnKVStages;
+            const uint32_t kv_use = (uint32_t)(j / kAttnKVStages);
             bool w = mbar_wait_poll(smem_u32(&bar_kv_full[st]), kv_use & 1u, &abort_flag, p.err_word, 0x640u + st);
             return __all_sync(0xffffffffu, w);
         };
-        auto issue_s = [&](int i) {   // after wait_kv(i)
-            const int st = i % kAttnKVStages, sb = i % kAttnSBufs;
+        auto issue_s = [&](int w) {   // after wait_kv(w >> 1)
+            const int j = w >> 1, g = w & 1;
+            const int st = j % kAttnKVStages, sb = w % kAttnSBufs;
+            const uint32_t qa = s_q + g * kAttnTileBytes;
             const uint32_t kb = s_kv + st * 2 * kAttnTileBytes;
             const uint32_t tmem_s = tmem_base + kAttnSCol + (uint32_t)(sb * kAttnBN);
             if (elect_one()) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {   // 16 of the 64 head dims per MMA
-                    const uint64_t da = make_smem_desc(s_q + k * 32, 16, 1024);
+                    const uint64_t da = make_smem_desc(qa + k * 32, 16, 1024);
                     const uint64_t db = make_smem_desc(kb + k * 32, 16, 1024);
                     umma<false, 1>(tmem_s, da, db, p.idesc_s, k > 0 ? 1u : 0u);
                 }
@@ -159,25 +162,24 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             }
             __syncwarp();
         };
-        for (int i = 0; ok && i < kAttnSBufs && i < n_tiles; ++i) {
-            ok = wait_kv(i);
+        for (int w = 0; ok && w < kAttnSBufs && w < n_items; ++w) {
+            ok = wait_kv(w >> 1);
             tc_fence_after();
-            if (ok) issue_s(i);
+            if (ok) issue_s(w);
         }
-        for (int j = 0; ok && j < n_tiles; ++j) {
-            const int g = j & 1;
-            const uint32_t use = (uint32_t)(j >> 1);
-            // K of the scores issued behind T_j (its V is in the same stage as K_j, here since S_j)
-            if (j + kAttnSBufs < n_tiles && !wait_kv(j + kAttnSBufs)) break;
-            // P_j is written and S_j read for the last time; before that the group took T_{j-2} out of
-            // the output-tile buffer
-            bool w = mbar_wait_poll(smem_u32(&bar_p_full[g]), use & 1u, &abort_flag, p.err_word, 0x620u + g);
-            w = __all_sync(0xffffffffu, w);
-            if (!w) break;
+        for (int w = 0; ok && w < n_items; ++w) {
+            const int j = w >> 1, g = w & 1;
+            // K of the scores issued behind T_w
+            if (w + kAttnSBufs < n_items && !wait_kv((w + kAttnSBufs) >> 1)) break;
+            // P_w is written and S_w read for the last time; before that the group took its previous
+            // T out of the output-tile buffer
+            bool ready = mbar_wait_poll(smem_u32(&bar_p_full[g]), (uint32_t)j & 1u, &abort_flag, p.err_word, 0x620u + g);
+            ready = __all_sync(0xffffffffu, ready);
+            if (!ready) break;
             tc_fence_after();
-            // T_j = P_j V_j: A = P_j in tensor memory, B = V_j ([key, d] with d contiguous: MN-major)
+            // T_w = P_w V_j: A = P_w in tensor memory, B = V_j ([key, d] with d contiguous: MN-major)
             const int st = j % kAttnKVStages;
-            const uint32_t tmem_p = tmem_base + kAttnSCol + (uint32_t)((j % kAttnSBufs) * kAttnBN);
+            const uint32_t tmem_p = tmem_base + kAttnSCol + (uint32_t)((w % kAttnSBufs) * kAttnBN);
             const uint32_t vb = s_kv + st * 2 * kAttnTileBytes + kAttnTileBytes;
             const uint32_t tmem_t = tmem_base + kAttnTCol + (uint32_t)(g * kAttnD);
             if (elect_one()) {
@@ -187,15 +189,15 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     umma_ts(tmem_t, tmem_p + k * 8, db, p.idesc_t, k > 0 ? 1u : 0u);
                 }
                 tc_commit<1>(smem_u32(&bar_t_full[g]));
-                tc_commit<1>(smem_u32(&bar_kv_empty[st]));
+                if (g == 1) tc_commit<1>(smem_u32(&bar_kv_empty[st]));   // both query tiles are through with the stage
             }
             __syncwarp();
-            if (j + kAttnSBufs < n_tiles) issue_s(j + kAttnSBufs);
+            if (w + kAttnSBufs < n_items) issue_s(w + kAttnSBufs);
         }
     } else {
         // ---------------- softmax + output accumulation ----------------
         const int q = warp & 3;               // TMEM lane quarter this warp may access
-        const int g = (warp - 2) >> 2;        // group: key tiles g, g+2, g+4, ...
+        const int g = (warp - 2) >> 2;        // group = query tile
         const int row = q * 32 + lane;
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
         const uint32_t t_addr = tmem_base + lane_base + kAttnTCol + (uint32_t)(g * kAttnD);
@@ -225,14 +227,13 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             }
             return true;
         };
-        int last = -1;
-        for (int j = g; ok && j < n_tiles; j += 2) {
-            const uint32_t use = (uint32_t)(j >> 1);
-            const int sb = j % kAttnSBufs;
+        for (int j = 0; ok && j < n_tiles; ++j) {
+            const int w = 2 * j + g;
+            const int sb = w % kAttnSBufs;
             const uint32_t s_addr = tmem_base + lane_base + kAttnSCol + (uint32_t)(sb * kAttnBN);
-            bool w = mbar_wait_poll(smem_u32(&bar_s_full[sb]), (uint32_t)(j / kAttnSBufs) & 1u, &abort_flag, p.err_word, 0x670u + sb);
-            w = __all_sync(0xffffffffu, w);
-            if (!w) { ok = false; break; }
+            bool ready = mbar_wait_poll(smem_u32(&bar_s_full[sb]), (uint32_t)(w / kAttnSBufs) & 1u, &abort_flag, p.err_word, 0x670u + sb);
+            ready = __all_sync(0xffffffffu, ready);
+            if (!ready) { ok = false; break; }
             tc_fence_after();
             const long long kv0 = (long long)j * kAttnBN;
             const bool ragged = kv0 + kAttnBN > p.S_kv;   // keys past S_kv are zero-filled rows of K
@@ -265,9 +266,9 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));   // finite: a tile holds at least one key
             const float m_new = fmaxf(m, mx * p.scale_log2e);
             const float alpha = (m == -INFINITY) ? 0.0f : ex2_approx(m - m_new);
-            // the group's previous tile, out of its T buffer before T_j is issued into it
-            if (j >= 2) {
-                ok = add_tile(use - 1);
+            // the previous tile, out of the T buffer before T_w is issued into it
+            if (j >= 1) {
+                ok = add_tile((uint32_t)(j - 1));
                 if (!ok) break;
             }
             // pass 2: p = 2^(s * scale * log2e - m_new). Pairs of keys per instruction where the ISA allows
@@ -318,53 +319,20 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             l = fmaf(l, alpha, l2.x + l2.y);
             alpha_prev = alpha;
             m = m_new;
-            last = j;
         }
-        if (ok && last >= 0) ok = add_tile((uint32_t)(last >> 1));
-        // merge of the two groups: each hands the other the 32 output columns the other stores, through
-        // its own T buffer in tensor memory (both groups' warps of a lane quarter reach the same lanes)
-        auto hand_over = [&](auto other_cols) {
-            constexpr int kC0 = decltype(other_cols)::value;
-            uint32_t r[32];
+        if (ok && n_tiles > 0) ok = add_tile((uint32_t)(n_tiles - 1));
+        const long long qrow = (long long)q0 + g * kAttnBM + row;
+        if (ok && qrow < p.S_q) {
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            T* orow = static_cast<T*>(p.O) + (long long)b * p.o_stride_b + (long long)h * p.o_stride_h + qrow * p.ldo;
 #pragma unroll
-            for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(o[kC0 + c]);
-            tmem_st32(t_addr, r);
-            tmem_wait_st();
-        };
-        if (ok) {
-            xm[g][row] = m;
-            xl[g][row] = l;
-            if (g == 0) hand_over(std::integral_constant<int, 32>{}); else hand_over(std::integral_constant<int, 0>{});
-        }
-        tc_fence_before();
-        asm volatile("bar.sync 1, 256;" ::: "memory");   // every softmax thread gets here, after a timeout too
-        tc_fence_after();
-        auto finish = [&](auto own_cols) {
-            constexpr int kC0 = decltype(own_cols)::value;
-            const float mo = xm[g ^ 1][row], lo = xl[g ^ 1][row];
-            const float mm = fmaxf(m, mo);
-            const float w_own = (m == -INFINITY) ? 0.0f : ex2_approx(m - mm);
-            const float w_oth = (mo == -INFINITY) ? 0.0f : ex2_approx(mo - mm);
-            const float lt = l * w_own + lo * w_oth;
-            const float inv = lt > 0.0f ? 1.0f / lt : 0.0f;
-            const float a = w_own * inv, bo = w_oth * inv;
-            float theirs[32];
-            tmem_ld32(tmem_base + lane_base + kAttnTCol + (uint32_t)((g ^ 1) * kAttnD), theirs);
-            if (q0 + row < p.S_q) {
-                T* orow = static_cast<T*>(p.O) + (long long)b * p.o_stride_b + (long long)h * p.o_stride_h +
-                          (long long)(q0 + row) * p.ldo + kC0;
+            for (int gi = 0; gi < kAttnD / 8; ++gi) {   // the thread's row: 128 contiguous bytes
+                float e[8];
 #pragma unroll
-                for (int gi = 0; gi < 4; ++gi) {
-                    float e[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) e[i] = o[kC0 + gi * 8 + i] * a + theirs[gi * 8 + i] * bo;
-                    const Vec16<T> o8 = pack16<T>(e);
-                    *reinterpret_cast<int4*>(orow + gi * 8) = *reinterpret_cast<const int4*>(&o8);
-                }
+                for (int i = 0; i < 8; ++i) e[i] = o[gi * 8 + i] * inv;
+                const Vec16<T> o8 = pack16<T>(e);
+                *reinterpret_cast<int4*>(orow + gi * 8) = *reinterpret_cast<const int4*>(&o8);
             }
-        };
-        if (__all_sync(0xffffffffu, ok && !abort_flag)) {   // warp-uniform: the TMEM load inside is warp-collective
-            if (g == 0) finish(std::integral_constant<int, 0>{}); else finish(std::integral_constant<int, 32>{});
         }
     }
 
@@ -452,7 +420,7 @@ extern "C" int cg_b200_attention(const cg_b200_attention_desc* desc, const void*
     p.ldo = d.ldo; p.o_stride_h = d.head_stride_o; p.o_stride_b = d.batch_stride_o;
     p.O = O;
     p.scale_log2e = d.scale * 1.4426950408889634f;
-    p.q_tiles = (int)((d.seq_q + kAttnBM - 1) / kAttnBM);
+    p.q_tiles = (int)((d.seq_q + kAttnQRows - 1) / kAttnQRows);
     p.kv_tiles = (int)((d.seq_kv + kAttnBN - 1) / kAttnBN);
     p.idesc_s = attn_idesc(d.dtype, false, kAttnBN);
     p.idesc_t = attn_idesc(d.dtype, true, kAttnD);
