@@ -222,8 +222,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 const int zb = p.b_in ? b_in : 0, wb = p.b_out ? b_out : 0;
                 const uint32_t stage_tx = (uint32_t)(kCta * kCopies * (L::kABytes + bnl * kRowBytes));
                 for (int kb = 0; kb < p.num_kb; ++kb) {
-                    if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag, p.err_word, 0x100u + stage,
-                                   2000000000ull, 40)) {
+                    if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag, p.err_word, 0x100u + stage)) {
                         ok = false;
                         break;
                     }
@@ -283,7 +282,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0 && cta_rank == 0) {
+        // The whole warp runs the loop converged and waits; one elected lane issues. Under a divergent
+        // "if (lane == 0)" the compiler keeps descriptors and addresses in per-thread registers and moves
+        // them to the uniform file before every tcgen05.mma, which costs more than the instruction itself.
+        if (cta_rank == 0) {
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
@@ -295,7 +297,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             // span when K is contiguous, kUmmaK rows of 128 bytes when N is contiguous
             const uint32_t b_kstep = p.b_mn_major ? (uint32_t)(kUmmaKBytes / kElem) * kRowBytes : (uint32_t)kUmmaKBytes;
             for (long long tile = tile_first; ok && tile < p.num_tiles; tile += tile_step) {
-                if (!mbar_wait(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, &abort_flag, p.err_word, 0x200u + acc)) {
+                bool w = mbar_wait(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, &abort_flag, p.err_word, 0x200u + acc);
+                if (!__all_sync(0xffffffffu, w)) {
                     ok = false;
                     break;
                 }
@@ -304,35 +307,40 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 const uint32_t idesc = tile >= p.full_units ? p.idesc_half : p.idesc;
                 uint32_t first = 0;
                 for (int kb = 0; kb < p.num_kb; ++kb) {
-                    if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag, p.err_word, 0x300u + stage)) {
+                    w = mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag, p.err_word, 0x300u + stage);
+                    if (!__all_sync(0xffffffffu, w)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
                     const uint32_t sa = smem_base + stage * L::kStageBytes;
                     const uint32_t sb = sa + kCopies * L::kABytes;
-                    // passes: (lo, hi), (hi, lo), (hi, hi) for the split; (hi, hi) alone otherwise
+                    if (elect_one()) {
+                        // passes: (lo, hi), (hi, lo), (hi, hi) for the split; (hi, hi) alone otherwise
 #pragma unroll
-                    for (int ps = 0; ps < kPasses; ++ps) {
-                        const int ia = (kPasses == 3 && ps == 0) ? 1 : 0;
-                        const int ib = (kPasses == 3 && ps == 1) ? 1 : 0;
-                        const uint64_t da = make_smem_desc(sa + ia * L::kABytes, a_lbo, a_sbo);
-                        const uint64_t db = make_smem_desc(sb + ib * L::kBBytes, b_lbo, b_sbo);
+                        for (int ps = 0; ps < kPasses; ++ps) {
+                            const int ia = (kPasses == 3 && ps == 0) ? 1 : 0;
+                            const int ib = (kPasses == 3 && ps == 1) ? 1 : 0;
+                            const uint64_t da = make_smem_desc(sa + ia * L::kABytes, a_lbo, a_sbo);
+                            const uint64_t db = make_smem_desc(sb + ib * L::kBBytes, b_lbo, b_sbo);
 #pragma unroll
-                        for (int k = 0; k < kKSteps; ++k) {
-                            umma<kTF32, kCta>(tmem_d, da + (uint64_t)((k * kUmmaKBytes) >> 4), db + (uint64_t)((k * b_kstep) >> 4),
-                                        idesc, first);
-                            first = 1;
+                            for (int k = 0; k < kKSteps; ++k) {
+                                umma<kTF32, kCta>(tmem_d, da + (uint64_t)((k * kUmmaKBytes) >> 4),
+                                                  db + (uint64_t)((k * b_kstep) >> 4), idesc, (ps | k | (int)first) ? 1u : 0u);
+                            }
                         }
+                        tc_commit<kCta>(smem_u32(&bar_empty[stage]));
                     }
-                    tc_commit<kCta>(smem_u32(&bar_empty[stage]));
+                    __syncwarp();
+                    first = 1;
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
                 if (!ok) break;
-                tc_commit<kCta>(smem_u32(&bar_acc_full[acc]));
+                if (elect_one()) tc_commit<kCta>(smem_u32(&bar_acc_full[acc]));
+                __syncwarp();
                 acc ^= 1;
                 if (acc == 0) acc_phase ^= 1u;
             }
