@@ -5,10 +5,14 @@
 // the path - matmul, softmax, matmul (src/ir/ops.cpp) - whose [B, H, S, S] intermediate makes three
 // trips through HBM. Here the scores never leave the SM.
 //
-// One CTA per (batch, head, 256 query rows = two query tiles), 320 threads. Both query tiles meet each
+// A work unit is (batch, head, 256 query rows = two query tiles); persistent CTAs of 320 threads, one per
+// SM, take units blockIdx.x, blockIdx.x + gridDim.x, ... and carry the whole pipeline - K/V ring, score
+// buffers, barrier phases - across units, so the loads and the first scores of the next unit are under
+// way while the softmax groups finish the current one (no fill and drain per unit; the Q tiles are
+// double-buffered for that). Both query tiles meet each
 // K/V tile while it is in shared memory, which halves the K/V traffic from L2 - the first limit of a
 // one-tile CTA at head_dim 64. Work item w = 2 j + g is (key tile j, query tile g):
-//   warp 0     TMA: the two Q tiles once, then K and V tiles of 128 key rows through a 6-stage ring
+//   warp 0     TMA: the two Q tiles of a unit, then K and V tiles of 128 key rows through a 5-stage ring
 //   warp 1     issues S_w = Q_g K_j^T (128 x 128 x 64) into TMEM score buffer w%3 and
 //              T_w = P_w V_j (128 x 64 x 128, P_w read from TMEM) into TMEM output-tile buffer g.
 //              The warp runs its loop converged and one elected lane issues, which keeps descriptors
@@ -39,11 +43,11 @@ constexpr int kAttnBM = 128;          // query rows per tile = TMEM lanes
 constexpr int kAttnQRows = 2 * kAttnBM;   // query rows per CTA
 constexpr int kAttnBN = 128;          // key rows per step
 constexpr int kAttnD = 64;            // head dim: 128 bytes of bf16 = one swizzle span
-constexpr int kAttnKVStages = 6;
+constexpr int kAttnKVStages = 5;
 constexpr int kAttnSBufs = 3;
 constexpr int kAttnThreads = 320;
 constexpr int kAttnTileBytes = 128 * 128;                 // a 128-row x 128-byte tile (Q, K or V)
-constexpr int kAttnSmem = 2 * kAttnTileBytes + kAttnKVStages * 2 * kAttnTileBytes + 1024;
+constexpr int kAttnSmem = 2 * 2 * kAttnTileBytes + kAttnKVStages * 2 * kAttnTileBytes + 1024;
 constexpr uint32_t kAttnTmemCols = 512;
 constexpr uint32_t kAttnSCol = 0;     // three score buffers of 128 columns; P over the first 64 of each
 constexpr uint32_t kAttnTCol = 384;   // two output-tile buffers of 64 columns
@@ -56,6 +60,7 @@ struct AttnParams {
     void* O;
     float scale_log2e;
     int q_tiles, kv_tiles;
+    long long units;   // B * H * q_tiles
     uint32_t idesc_s, idesc_t;
     uint32_t* err_word;
 };
@@ -71,7 +76,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_q;
+    __shared__ __align__(8) uint64_t bar_q_full[2], bar_q_empty[2];
     __shared__ __align__(8) uint64_t bar_kv_full[kAttnKVStages], bar_kv_empty[kAttnKVStages];
     __shared__ __align__(8) uint64_t bar_s_full[kAttnSBufs], bar_p_full[2], bar_t_full[2];
     __shared__ uint32_t tmem_base_slot;
@@ -79,19 +84,27 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t s_q = smem_base;
-    const uint32_t s_kv = s_q + 2 * kAttnTileBytes;   // stage s: K at +s*2T, V at +s*2T + T
+    const uint32_t s_kv = s_q + 2 * 2 * kAttnTileBytes;   // after two Q buffers; stage s: K at +s*2T, V at +s*2T + T
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    // work item: query tile fastest so that the CTAs of one head run together and share K, V in L2
-    const long long item = blockIdx.x;
-    const int qt = (int)(item % p.q_tiles);
-    const int h = (int)((item / p.q_tiles) % p.H);
-    const int b = (int)(item / ((long long)p.q_tiles * p.H));
-    const int q0 = qt * kAttnQRows;
+    // unit -> (batch, head, query rows): query tile fastest, so that the CTAs running at one time work on
+    // few heads and share their K, V in L2
+    struct Unit { int q0, h, b; };
+    auto decode = [&](long long unit) {
+        Unit u;
+        u.q0 = (int)(unit % p.q_tiles) * kAttnQRows;
+        u.h = (int)((unit / p.q_tiles) % p.H);
+        u.b = (int)(unit / ((long long)p.q_tiles * p.H));
+        return u;
+    };
     const int n_tiles = p.kv_tiles;
+    const int n_items = 2 * n_tiles;   // per unit
 
     if (threadIdx.x == 0) {
-        mbar_init(smem_u32(&bar_q), 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&bar_q_full[i]), 1);
+            mbar_init(smem_u32(&bar_q_empty[i]), 1);
+        }
         for (int s = 0; s < kAttnKVStages; ++s) {
             mbar_init(smem_u32(&bar_kv_full[s]), 1);
             mbar_init(smem_u32(&bar_kv_empty[s]), 1);
@@ -118,39 +131,70 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            mbar_expect_tx(smem_u32(&bar_q), 2 * kAttnTileBytes);   // rows past S_q arrive as zeros
-            tma_load_4d<1>(s_q, &tm_q, smem_u32(&bar_q), 0, q0, h, b);
-            tma_load_4d<1>(s_q + kAttnTileBytes, &tm_q, smem_u32(&bar_q), 0, q0 + kAttnBM, h, b);
-            for (int j = 0; j < n_tiles; ++j) {
-                const int st = j % kAttnKVStages;
-                const uint32_t use = (uint32_t)(j / kAttnKVStages);
-                if (!mbar_wait(smem_u32(&bar_kv_empty[st]), (use & 1u) ^ 1u, &abort_flag, p.err_word, 0x600u + st)) break;
-                const uint32_t full = smem_u32(&bar_kv_full[st]);
-                mbar_expect_tx(full, 2 * kAttnTileBytes);
-                tma_load_4d<1>(s_kv + st * 2 * kAttnTileBytes, &tm_k, full, 0, j * kAttnBN, h, b);
-                tma_load_4d<1>(s_kv + st * 2 * kAttnTileBytes + kAttnTileBytes, &tm_v, full, 0, j * kAttnBN, h, b);
+            uint32_t k = 0;          // units this CTA has started
+            int st = 0;              // K/V ring position and the parity of its current round
+            uint32_t st_phase = 0;
+            bool ok = true;
+            for (long long unit = blockIdx.x; ok && unit < p.units; unit += gridDim.x, ++k) {
+                const Unit u = decode(unit);
+                const int qb = (int)(k & 1u);
+                if (!mbar_wait(smem_u32(&bar_q_empty[qb]), ((k >> 1) & 1u) ^ 1u, &abort_flag, p.err_word, 0x608u + qb)) break;
+                const uint32_t qfull = smem_u32(&bar_q_full[qb]);
+                mbar_expect_tx(qfull, 2 * kAttnTileBytes);   // rows past S_q arrive as zeros
+                tma_load_4d<1>(s_q + qb * 2 * kAttnTileBytes, &tm_q, qfull, 0, u.q0, u.h, u.b);
+                tma_load_4d<1>(s_q + qb * 2 * kAttnTileBytes + kAttnTileBytes, &tm_q, qfull, 0, u.q0 + kAttnBM, u.h, u.b);
+                for (int j = 0; j < n_tiles; ++j) {
+                    if (!mbar_wait(smem_u32(&bar_kv_empty[st]), st_phase ^ 1u, &abort_flag, p.err_word, 0x600u + st)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t full = smem_u32(&bar_kv_full[st]);
+                    mbar_expect_tx(full, 2 * kAttnTileBytes);
+                    tma_load_4d<1>(s_kv + st * 2 * kAttnTileBytes, &tm_k, full, 0, j * kAttnBN, u.h, u.b);
+                    tma_load_4d<1>(s_kv + st * 2 * kAttnTileBytes + kAttnTileBytes, &tm_v, full, 0, j * kAttnBN, u.h, u.b);
+                    if (++st == kAttnKVStages) {
+                        st = 0;
+                        st_phase ^= 1u;
+                    }
+                }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         // The whole warp runs the loop and waits; one elected lane issues (see elect_one()).
-        bool ok = mbar_wait_poll(smem_u32(&bar_q), 0, &abort_flag, p.err_word, 0x610u);
-        ok = __all_sync(0xffffffffu, ok);
-        // S_w = Q_g K_j^T into score buffer w%3. The tensor pipe runs its instructions in issue order, and
-        // this is issued behind T_{w-3}, the last reader of that buffer (P_{w-3} lives in it).
-        const int n_items = 2 * n_tiles;
-        auto wait_kv = [&](int j) -> bool {
-            const int st = j % kAttnKVStages;
-            const uint32_t kv_use = (uint32_t)(j / kAttnKVStages);
-            bool w = mbar_wait_poll(smem_u32(&bar_kv_full[st]), kv_use & 1u, &abort_flag, p.err_word, 0x640u + st);
+        // Items are numbered through all units of this CTA: W = k * n_items + 2 j + g. S_W goes into score
+        // buffer W%3. The tensor pipe runs its instructions in issue order, and S_W is issued behind
+        // T_{W-3}, the last reader of that buffer (P_{W-3} lives in it). Positions are kept as small
+        // rotating counters: "s" for the scores being issued (three items ahead), "t" for the T behind.
+        long long my_units = p.units > (long long)blockIdx.x ? (p.units - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+        const long long total = my_units * n_items;
+        struct Pos {
+            int w;          // item within the unit
+            uint32_t k;     // unit count
+            int st;         // K/V ring stage of the item's key tile, and the parity of that round
+            uint32_t st_phase;
+            int sb;         // score buffer, and the parity of its current use
+            uint32_t sb_phase;
+        };
+        auto advance = [&](Pos& x) {
+            if (++x.sb == kAttnSBufs) { x.sb = 0; x.sb_phase ^= 1u; }
+            if (x.w & 1) {   // second query tile of the key tile: next key tile
+                if (++x.st == kAttnKVStages) { x.st = 0; x.st_phase ^= 1u; }
+            }
+            if (++x.w == n_items) { x.w = 0; ++x.k; }
+        };
+        bool ok = true;
+        auto prep_s = [&](const Pos& x) -> bool {   // operands of S for item x: Q of a new unit, K of a new key tile
+            bool w = true;
+            if (x.w == 0) w = mbar_wait_poll(smem_u32(&bar_q_full[x.k & 1u]), (x.k >> 1) & 1u, &abort_flag, p.err_word, 0x610u);
+            if (w && !(x.w & 1)) w = mbar_wait_poll(smem_u32(&bar_kv_full[x.st]), x.st_phase, &abort_flag, p.err_word, 0x640u + x.st);
             return __all_sync(0xffffffffu, w);
         };
-        auto issue_s = [&](int w) {   // after wait_kv(w >> 1)
-            const int j = w >> 1, g = w & 1;
-            const int st = j % kAttnKVStages, sb = w % kAttnSBufs;
-            const uint32_t qa = s_q + g * kAttnTileBytes;
-            const uint32_t kb = s_kv + st * 2 * kAttnTileBytes;
-            const uint32_t tmem_s = tmem_base + kAttnSCol + (uint32_t)(sb * kAttnBN);
+        auto issue_s = [&](const Pos& x) {   // after prep_s(x)
+            const int g = x.w & 1;
+            const uint32_t qa = s_q + (uint32_t)(x.k & 1u) * 2 * kAttnTileBytes + g * kAttnTileBytes;
+            const uint32_t kb = s_kv + x.st * 2 * kAttnTileBytes;
+            const uint32_t tmem_s = tmem_base + kAttnSCol + (uint32_t)(x.sb * kAttnBN);
             if (elect_one()) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {   // 16 of the 64 head dims per MMA
@@ -158,29 +202,33 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     const uint64_t db = make_smem_desc(kb + k * 32, 16, 1024);
                     umma<false, 1>(tmem_s, da, db, p.idesc_s, k > 0 ? 1u : 0u);
                 }
-                tc_commit<1>(smem_u32(&bar_s_full[sb]));
+                tc_commit<1>(smem_u32(&bar_s_full[x.sb]));
+                if (x.w == n_items - 1) tc_commit<1>(smem_u32(&bar_q_empty[x.k & 1u]));   // last reader of this Q buffer
             }
             __syncwarp();
         };
-        for (int w = 0; ok && w < kAttnSBufs && w < n_items; ++w) {
-            ok = wait_kv(w >> 1);
+        Pos ps = {0, 0u, 0, 0u, 0, 0u}, pt = ps;
+        long long issued_s = 0;
+        for (; ok && issued_s < kAttnSBufs && issued_s < total; ++issued_s) {
+            ok = prep_s(ps);
             tc_fence_after();
-            if (ok) issue_s(w);
+            if (ok) issue_s(ps);
+            advance(ps);
         }
-        for (int w = 0; ok && w < n_items; ++w) {
-            const int j = w >> 1, g = w & 1;
-            // K of the scores issued behind T_w
-            if (w + kAttnSBufs < n_items && !wait_kv((w + kAttnSBufs) >> 1)) break;
-            // P_w is written and S_w read for the last time; before that the group took its previous
+        uint32_t tiles_done[2] = {0u, 0u};   // per query tile: T issued so far = parity source of p_full / t_full
+        for (long long W = 0; ok && W < total; ++W) {
+            const int g = pt.w & 1;
+            // operands of the scores issued behind T_W
+            if (issued_s < total && !prep_s(ps)) break;
+            // P_W is written and S_W read for the last time; before that the group took its previous
             // T out of the output-tile buffer
-            bool ready = mbar_wait_poll(smem_u32(&bar_p_full[g]), (uint32_t)j & 1u, &abort_flag, p.err_word, 0x620u + g);
+            bool ready = mbar_wait_poll(smem_u32(&bar_p_full[g]), tiles_done[g] & 1u, &abort_flag, p.err_word, 0x620u + g);
             ready = __all_sync(0xffffffffu, ready);
             if (!ready) break;
             tc_fence_after();
-            // T_w = P_w V_j: A = P_w in tensor memory, B = V_j ([key, d] with d contiguous: MN-major)
-            const int st = j % kAttnKVStages;
-            const uint32_t tmem_p = tmem_base + kAttnSCol + (uint32_t)((w % kAttnSBufs) * kAttnBN);
-            const uint32_t vb = s_kv + st * 2 * kAttnTileBytes + kAttnTileBytes;
+            // T_W = P_W V_j: A = P_W in tensor memory, B = V_j ([key, d] with d contiguous: MN-major)
+            const uint32_t tmem_p = tmem_base + kAttnSCol + (uint32_t)(pt.sb * kAttnBN);
+            const uint32_t vb = s_kv + pt.st * 2 * kAttnTileBytes + kAttnTileBytes;
             const uint32_t tmem_t = tmem_base + kAttnTCol + (uint32_t)(g * kAttnD);
             if (elect_one()) {
 #pragma unroll
@@ -189,10 +237,16 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     umma_ts(tmem_t, tmem_p + k * 8, db, p.idesc_t, k > 0 ? 1u : 0u);
                 }
                 tc_commit<1>(smem_u32(&bar_t_full[g]));
-                if (g == 1) tc_commit<1>(smem_u32(&bar_kv_empty[st]));   // both query tiles are through with the stage
+                if (g == 1) tc_commit<1>(smem_u32(&bar_kv_empty[pt.st]));   // both query tiles are through with the stage
             }
             __syncwarp();
-            if (w + kAttnSBufs < n_items) issue_s(w + kAttnSBufs);
+            ++tiles_done[g];
+            advance(pt);
+            if (issued_s < total) {
+                issue_s(ps);
+                advance(ps);
+                ++issued_s;
+            }
         }
     } else {
         // ---------------- softmax + output accumulation ----------------
@@ -202,10 +256,11 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
         const uint32_t t_addr = tmem_base + lane_base + kAttnTCol + (uint32_t)(g * kAttnD);
         float o[kAttnD];
-#pragma unroll
-        for (int i = 0; i < kAttnD; ++i) o[i] = 0.0f;
-        float m = -INFINITY, l = 0.0f, alpha_prev = 0.0f;
+        float m, l, alpha_prev;
         bool ok = true;
+        int sb = g;               // score buffer of the group's next item (items g, g+2, g+4, ... mod 3) and
+        uint32_t sb_phase = 0;    // the parity of that buffer's current use
+        uint32_t tcount = 0;      // key tiles this group has finished, over all units
         auto add_tile = [&](uint32_t use) -> bool {   // o = o * alpha_prev + T (the group's last tile)
             bool w = mbar_wait_poll(smem_u32(&bar_t_full[g]), use & 1u, &abort_flag, p.err_word, 0x660u + g);
             w = __all_sync(0xffffffffu, w);
@@ -227,11 +282,16 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             }
             return true;
         };
+        for (long long unit = blockIdx.x; ok && unit < p.units; unit += gridDim.x) {
+        const Unit u = decode(unit);
+#pragma unroll
+        for (int i = 0; i < kAttnD; ++i) o[i] = 0.0f;
+        m = -INFINITY;
+        l = 0.0f;
+        alpha_prev = 0.0f;
         for (int j = 0; ok && j < n_tiles; ++j) {
-            const int w = 2 * j + g;
-            const int sb = w % kAttnSBufs;
             const uint32_t s_addr = tmem_base + lane_base + kAttnSCol + (uint32_t)(sb * kAttnBN);
-            bool ready = mbar_wait_poll(smem_u32(&bar_s_full[sb]), (uint32_t)(w / kAttnSBufs) & 1u, &abort_flag, p.err_word, 0x670u + sb);
+            bool ready = mbar_wait_poll(smem_u32(&bar_s_full[sb]), sb_phase, &abort_flag, p.err_word, 0x670u + sb);
             ready = __all_sync(0xffffffffu, ready);
             if (!ready) { ok = false; break; }
             tc_fence_after();
@@ -268,7 +328,7 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             const float alpha = (m == -INFINITY) ? 0.0f : ex2_approx(m - m_new);
             // the previous tile, out of the T buffer before T_w is issued into it
             if (j >= 1) {
-                ok = add_tile((uint32_t)(j - 1));
+                ok = add_tile(tcount - 1u);
                 if (!ok) break;
             }
             // pass 2: p = 2^(s * scale * log2e - m_new). Pairs of keys per instruction where the ISA allows
@@ -319,12 +379,18 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             l = fmaf(l, alpha, l2.x + l2.y);
             alpha_prev = alpha;
             m = m_new;
+            ++tcount;
+            sb += 2;
+            if (sb >= kAttnSBufs) {
+                sb -= kAttnSBufs;
+                sb_phase ^= 1u;
+            }
         }
-        if (ok && n_tiles > 0) ok = add_tile((uint32_t)(n_tiles - 1));
-        const long long qrow = (long long)q0 + g * kAttnBM + row;
+        if (ok && n_tiles > 0) ok = add_tile(tcount - 1u);
+        const long long qrow = (long long)u.q0 + g * kAttnBM + row;
         if (ok && qrow < p.S_q) {
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            T* orow = static_cast<T*>(p.O) + (long long)b * p.o_stride_b + (long long)h * p.o_stride_h + qrow * p.ldo;
+            T* orow = static_cast<T*>(p.O) + (long long)u.b * p.o_stride_b + (long long)u.h * p.o_stride_h + qrow * p.ldo;
 #pragma unroll
             for (int gi = 0; gi < kAttnD / 8; ++gi) {   // the thread's row: 128 contiguous bytes
                 float e[8];
@@ -334,6 +400,7 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 *reinterpret_cast<int4*>(orow + gi * 8) = *reinterpret_cast<const int4*>(&o8);
             }
         }
+        }   // units
     }
 
     if (abort_flag) {
@@ -425,17 +492,17 @@ extern "C" int cg_b200_attention(const cg_b200_attention_desc* desc, const void*
     p.idesc_s = attn_idesc(d.dtype, false, kAttnBN);
     p.idesc_t = attn_idesc(d.dtype, true, kAttnD);
     p.err_word = device_error_word();
-    const long long items = (long long)p.q_tiles * p.H * p.B;
-    if (items > 0x7fffffffLL) return CG_B200_ERR_UNSUPPORTED;
+    p.units = (long long)p.q_tiles * p.H * p.B;
+    const long long grid = p.units < sm_count() ? p.units : sm_count();   // one persistent CTA per SM
     cudaStream_t s = (cudaStream_t)stream;
     if (d.dtype == CG_B200_BF16) {
         auto kern = attention_sm100_kernel<__nv_bfloat16>;
         CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
-        kern<<<(unsigned)items, kAttnThreads, kAttnSmem, s>>>(tq, tk, tv, p);
+        kern<<<(unsigned)grid, kAttnThreads, kAttnSmem, s>>>(tq, tk, tv, p);
     } else {
         auto kern = attention_sm100_kernel<__half>;
         CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
-        kern<<<(unsigned)items, kAttnThreads, kAttnSmem, s>>>(tq, tk, tv, p);
+        kern<<<(unsigned)grid, kAttnThreads, kAttnSmem, s>>>(tq, tk, tv, p);
     }
     CGB_CUDA(cudaGetLastError());
     return CG_B200_OK;
