@@ -250,12 +250,15 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
     } else {
         // ---------------- softmax + output accumulation ----------------
+        // One thread per query row. (Two threads per row, sixteen softmax warps, was tried: the exchange of
+        // the row maximum and the tighter register budget cost more than the extra warps hid.)
+        constexpr int kKeys = kAttnBN, kCols = kAttnD, kChunks = kKeys / 32;
         const int q = warp & 3;               // TMEM lane quarter this warp may access
         const int g = (warp - 2) >> 2;        // group = query tile
         const int row = q * 32 + lane;
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
         const uint32_t t_addr = tmem_base + lane_base + kAttnTCol + (uint32_t)(g * kAttnD);
-        float o[kAttnD];
+        float o[kCols];
         float m, l, alpha_prev;
         bool ok = true;
         int sb = g;               // score buffer of the group's next item (items g, g+2, g+4, ... mod 3) and
@@ -267,11 +270,11 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             if (!w) return false;
             tc_fence_after();
             const float2 a2 = make_float2(alpha_prev, alpha_prev);
-            float t[2][32];
-            tmem_ld32_issue(t_addr, t[0]);
-            tmem_ld32_issue(t_addr + 32, t[1]);
+            float t[kCols / 32][32];
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
+            for (int c = 0; c < kCols / 32; ++c) tmem_ld32_issue(t_addr + c * 32, t[c]);
+#pragma unroll
+            for (int c = 0; c < kCols / 32; ++c) {
                 tmem_ld_wait(t[c]);
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
@@ -283,123 +286,123 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             return true;
         };
         for (long long unit = blockIdx.x; ok && unit < p.units; unit += gridDim.x) {
-        const Unit u = decode(unit);
+            const Unit u = decode(unit);
 #pragma unroll
-        for (int i = 0; i < kAttnD; ++i) o[i] = 0.0f;
-        m = -INFINITY;
-        l = 0.0f;
-        alpha_prev = 0.0f;
-        for (int j = 0; ok && j < n_tiles; ++j) {
-            const uint32_t s_addr = tmem_base + lane_base + kAttnSCol + (uint32_t)(sb * kAttnBN);
-            bool ready = mbar_wait_poll(smem_u32(&bar_s_full[sb]), sb_phase, &abort_flag, p.err_word, 0x670u + sb);
-            ready = __all_sync(0xffffffffu, ready);
-            if (!ready) { ok = false; break; }
-            tc_fence_after();
-            const long long kv0 = (long long)j * kAttnBN;
-            const bool ragged = kv0 + kAttnBN > p.S_kv;   // keys past S_kv are zero-filled rows of K
-            // pass 1: row max over the 128 keys of the tile
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;   // four chains
-            {
+            for (int i = 0; i < kCols; ++i) o[i] = 0.0f;
+            m = -INFINITY;
+            l = 0.0f;
+            alpha_prev = 0.0f;
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                const uint32_t s_addr = tmem_base + lane_base + kAttnSCol + (uint32_t)(sb * kAttnBN);
+                bool ready = mbar_wait_poll(smem_u32(&bar_s_full[sb]), sb_phase, &abort_flag, p.err_word, 0x670u + sb);
+                ready = __all_sync(0xffffffffu, ready);
+                if (!ready) { ok = false; break; }
+                tc_fence_after();
+                const long long kv0 = (long long)j * kAttnBN;
+                const bool ragged = kv0 + kKeys > p.S_kv;   // keys past S_kv are zero-filled rows of K
+                // pass 1: row maximum over the 128 keys of the tile
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;   // four chains
+                {
+                    float s[2][32];
+                    tmem_ld32_issue(s_addr, s[0]);
+                    tmem_ld32_issue(s_addr + 32, s[1]);
+#pragma unroll
+                    for (int c = 0; c < kChunks; ++c) {
+                        float (&cur)[32] = s[c & 1];
+                        tmem_ld_wait(cur);
+                        if (ragged) {   // only the last key tile: mask the zero-filled keys
+                            const int valid = (int)(p.S_kv - kv0) - c * 32;
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (i >= valid) cur[i] = -INFINITY;
+                        }
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            mx0 = fmax3(mx0, cur[i], cur[i + 1]);
+                            mx1 = fmax3(mx1, cur[i + 2], cur[i + 3]);
+                            mx2 = fmax3(mx2, cur[i + 4], cur[i + 5]);
+                            mx3 = fmax3(mx3, cur[i + 6], cur[i + 7]);
+                        }
+                        if (c + 2 < kChunks) tmem_ld32_issue(s_addr + (c + 2) * 32, cur);
+                    }
+                }
+                const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));   // finite: a tile holds at least one key
+                const float m_new = fmaxf(m, mx * p.scale_log2e);
+                const float alpha = (m == -INFINITY) ? 0.0f : ex2_approx(m - m_new);
+                // the previous tile, out of the T buffer before T_w is issued into it
+                if (j >= 1) {
+                    ok = add_tile(tcount - 1u);
+                    if (!ok) break;
+                }
+                // pass 2: p = 2^(s * scale * log2e - m_new). Pairs of keys per instruction where the ISA allows
+                // it (fp32x2 fma / add, packed convert). P goes over the first 64 columns of the score buffer:
+                // chunk c is written to columns 16c.. after columns up to 32c+31 have been read, and the chunk
+                // loaded ahead lies further right still.
+                float2 l2 = make_float2(0.0f, 0.0f);
+                const float2 sc2 = make_float2(p.scale_log2e, p.scale_log2e), nm2 = make_float2(-m_new, -m_new);
                 float s[2][32];
                 tmem_ld32_issue(s_addr, s[0]);
-                tmem_ld32_issue(s_addr + 32, s[1]);
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < kChunks; ++c) {
                     float (&cur)[32] = s[c & 1];
                     tmem_ld_wait(cur);
-                    if (ragged) {   // only the last key tile: mask the zero-filled keys
+                    if (c + 1 < kChunks) tmem_ld32_issue(s_addr + (c + 1) * 32, s[(c + 1) & 1]);
+                    if (ragged) {
                         const int valid = (int)(p.S_kv - kv0) - c * 32;
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
                             if (i >= valid) cur[i] = -INFINITY;
                     }
+                    uint32_t pk[16];
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        mx0 = fmax3(mx0, cur[i], cur[i + 1]);
-                        mx1 = fmax3(mx1, cur[i + 2], cur[i + 3]);
-                        mx2 = fmax3(mx2, cur[i + 4], cur[i + 5]);
-                        mx3 = fmax3(mx3, cur[i + 6], cur[i + 7]);
+                    for (int gi = 0; gi < 4; ++gi) {   // 8 keys at a time
+                        float e[8];
+#pragma unroll
+                        for (int i = 0; i < 8; i += 2) {
+                            const float2 t = __ffma2_rn(make_float2(cur[gi * 8 + i], cur[gi * 8 + i + 1]), sc2, nm2);
+                            const float2 ex = make_float2(ex2_approx(t.x), ex2_approx(t.y));   // 2^-inf = 0 for masked keys
+                            l2 = __fadd2_rn(l2, ex);
+                            e[i] = ex.x;
+                            e[i + 1] = ex.y;
+                        }
+                        const Vec16<T> o8 = pack16<T>(e);
+                        const uint4 u4 = *reinterpret_cast<const uint4*>(&o8);
+                        pk[gi * 4 + 0] = u4.x;
+                        pk[gi * 4 + 1] = u4.y;
+                        pk[gi * 4 + 2] = u4.z;
+                        pk[gi * 4 + 3] = u4.w;
                     }
-                    if (c + 2 < 4) tmem_ld32_issue(s_addr + (c + 2) * 32, cur);
+                    tmem_st16(s_addr + c * 16, pk);   // keys 32c .. 32c+31 of this row, two per column
+                }
+                // P is complete in tensor memory and the scores have been read for the last time
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bar_p_full[g]));
+                l = fmaf(l, alpha, l2.x + l2.y);
+                alpha_prev = alpha;
+                m = m_new;
+                ++tcount;
+                sb += 2;
+                if (sb >= kAttnSBufs) {
+                    sb -= kAttnSBufs;
+                    sb_phase ^= 1u;
                 }
             }
-            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));   // finite: a tile holds at least one key
-            const float m_new = fmaxf(m, mx * p.scale_log2e);
-            const float alpha = (m == -INFINITY) ? 0.0f : ex2_approx(m - m_new);
-            // the previous tile, out of the T buffer before T_w is issued into it
-            if (j >= 1) {
-                ok = add_tile(tcount - 1u);
-                if (!ok) break;
-            }
-            // pass 2: p = 2^(s * scale * log2e - m_new). Pairs of keys per instruction where the ISA allows
-            // it (fp32x2 fma / add, packed convert). P goes over the first 64 columns of the score buffer:
-            // chunk c is written to columns 16c.. after columns up to 32c+31 have been read, and the chunk
-            // loaded ahead lies further right still.
-            float2 l2 = make_float2(0.0f, 0.0f);
-            const float2 sc2 = make_float2(p.scale_log2e, p.scale_log2e), nm2 = make_float2(-m_new, -m_new);
-            float s[2][32];
-            tmem_ld32_issue(s_addr, s[0]);
+            if (ok && n_tiles > 0) ok = add_tile(tcount - 1u);
+            const long long qrow = (long long)u.q0 + g * kAttnBM + row;
+            if (ok && qrow < p.S_q) {
+                const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+                T* orow = static_cast<T*>(p.O) + (long long)u.b * p.o_stride_b + (long long)u.h * p.o_stride_h + qrow * p.ldo;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                float (&cur)[32] = s[c & 1];
-                tmem_ld_wait(cur);
-                if (c + 1 < 4) tmem_ld32_issue(s_addr + (c + 1) * 32, s[(c + 1) & 1]);
-                if (ragged) {
-                    const int valid = (int)(p.S_kv - kv0) - c * 32;
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (i >= valid) cur[i] = -INFINITY;
-                }
-                uint32_t pk[16];
-#pragma unroll
-                for (int gi = 0; gi < 4; ++gi) {   // 8 keys at a time
+                for (int gi = 0; gi < kCols / 8; ++gi) {
                     float e[8];
 #pragma unroll
-                    for (int i = 0; i < 8; i += 2) {
-                        const float2 t = __ffma2_rn(make_float2(cur[gi * 8 + i], cur[gi * 8 + i + 1]), sc2, nm2);
-                        const float2 ex = make_float2(ex2_approx(t.x), ex2_approx(t.y));   // 2^-inf = 0 for masked keys
-                        l2 = __fadd2_rn(l2, ex);
-                        e[i] = ex.x;
-                        e[i + 1] = ex.y;
-                    }
+                    for (int i = 0; i < 8; ++i) e[i] = o[gi * 8 + i] * inv;
                     const Vec16<T> o8 = pack16<T>(e);
-                    const uint4 u = *reinterpret_cast<const uint4*>(&o8);
-                    pk[gi * 4 + 0] = u.x;
-                    pk[gi * 4 + 1] = u.y;
-                    pk[gi * 4 + 2] = u.z;
-                    pk[gi * 4 + 3] = u.w;
+                    *reinterpret_cast<int4*>(orow + gi * 8) = *reinterpret_cast<const int4*>(&o8);
                 }
-                tmem_st16(s_addr + c * 16, pk);   // keys 32c .. 32c+31 of this row, two per column
             }
-            // P is complete in tensor memory and the scores have been read for the last time
-            tmem_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar_p_full[g]));
-            l = fmaf(l, alpha, l2.x + l2.y);
-            alpha_prev = alpha;
-            m = m_new;
-            ++tcount;
-            sb += 2;
-            if (sb >= kAttnSBufs) {
-                sb -= kAttnSBufs;
-                sb_phase ^= 1u;
-            }
-        }
-        if (ok && n_tiles > 0) ok = add_tile(tcount - 1u);
-        const long long qrow = (long long)u.q0 + g * kAttnBM + row;
-        if (ok && qrow < p.S_q) {
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            T* orow = static_cast<T*>(p.O) + (long long)u.b * p.o_stride_b + (long long)u.h * p.o_stride_h + qrow * p.ldo;
-#pragma unroll
-            for (int gi = 0; gi < kAttnD / 8; ++gi) {   // the thread's row: 128 contiguous bytes
-                float e[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) e[i] = o[gi * 8 + i] * inv;
-                const Vec16<T> o8 = pack16<T>(e);
-                *reinterpret_cast<int4*>(orow + gi * 8) = *reinterpret_cast<const int4*>(&o8);
-            }
-        }
         }   // units
     }
 
