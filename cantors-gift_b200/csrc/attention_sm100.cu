@@ -65,6 +65,17 @@ struct AttnParams {
     uint32_t* err_word;
 };
 
+template <typename T>
+__device__ __forceinline__ uint32_t pack_pair(float a, float b) {   // two values rounded to T in one word, a in the low half
+    if constexpr (Elem<T>::dtype == CG_B200_BF16) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    } else {
+        const __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
+}
+
 __device__ __forceinline__ float fmax3(float a, float b, float c) {   // one instruction on sm_100
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -275,7 +286,7 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             for (int c = 0; c < kCols / 32; ++c) tmem_ld32_issue(t_addr + c * 32, t[c]);
 #pragma unroll
             for (int c = 0; c < kCols / 32; ++c) {
-                tmem_ld_wait(t[c]);
+                tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     const float2 r = __ffma2_rn(make_float2(o[c * 32 + i], o[c * 32 + i + 1]), a2, make_float2(t[c][i], t[c][i + 1]));
@@ -309,7 +320,7 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #pragma unroll
                     for (int c = 0; c < kChunks; ++c) {
                         float (&cur)[32] = s[c & 1];
-                        tmem_ld_wait(cur);
+                        tmem_ld_wait();
                         if (ragged) {   // only the last key tile: mask the zero-filled keys
                             const int valid = (int)(p.S_kv - kv0) - c * 32;
 #pragma unroll
@@ -345,7 +356,7 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #pragma unroll
                 for (int c = 0; c < kChunks; ++c) {
                     float (&cur)[32] = s[c & 1];
-                    tmem_ld_wait(cur);
+                    tmem_ld_wait();
                     if (c + 1 < kChunks) tmem_ld32_issue(s_addr + (c + 1) * 32, s[(c + 1) & 1]);
                     if (ragged) {
                         const int valid = (int)(p.S_kv - kv0) - c * 32;
@@ -355,22 +366,11 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     }
                     uint32_t pk[16];
 #pragma unroll
-                    for (int gi = 0; gi < 4; ++gi) {   // 8 keys at a time
-                        float e[8];
-#pragma unroll
-                        for (int i = 0; i < 8; i += 2) {
-                            const float2 t = __ffma2_rn(make_float2(cur[gi * 8 + i], cur[gi * 8 + i + 1]), sc2, nm2);
-                            const float2 ex = make_float2(ex2_approx(t.x), ex2_approx(t.y));   // 2^-inf = 0 for masked keys
-                            l2 = __fadd2_rn(l2, ex);
-                            e[i] = ex.x;
-                            e[i + 1] = ex.y;
-                        }
-                        const Vec16<T> o8 = pack16<T>(e);
-                        const uint4 u4 = *reinterpret_cast<const uint4*>(&o8);
-                        pk[gi * 4 + 0] = u4.x;
-                        pk[gi * 4 + 1] = u4.y;
-                        pk[gi * 4 + 2] = u4.z;
-                        pk[gi * 4 + 3] = u4.w;
+                    for (int i = 0; i < 32; i += 2) {   // two keys at a time
+                        const float2 t = __ffma2_rn(make_float2(cur[i], cur[i + 1]), sc2, nm2);
+                        const float2 ex = make_float2(ex2_approx(t.x), ex2_approx(t.y));   // 2^-inf = 0 for masked keys
+                        l2 = __fadd2_rn(l2, ex);
+                        pk[i >> 1] = pack_pair<T>(ex.x, ex.y);
                     }
                     tmem_st16(s_addr + c * 16, pk);   // keys 32c .. 32c+31 of this row, two per column
                 }

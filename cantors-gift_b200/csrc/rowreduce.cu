@@ -295,7 +295,10 @@ __device__ __forceinline__ float packet_max(const Vec16<T>& v) {
     }
 }
 
-template <typename T, int THREADS, int CHUNKS, int MIN_CTAS>
+// FULL: the row is exactly THREADS * CHUNKS packets, so no packet needs a bounds predicate (the
+// predicates and the re-convergence points around them were a seventh of the instructions issued,
+// and this kernel is bound by instruction issue, not by DRAM).
+template <typename T, int THREADS, int CHUNKS, int MIN_CTAS, bool FULL>
 __global__ void __launch_bounds__(THREADS, MIN_CTAS) softmax_layernorm_reg_kernel(const __grid_constant__ RowParams p) {
     constexpr int L = 16 / sizeof(T);
     constexpr int P = L / 2;   // pairs per packet
@@ -315,7 +318,7 @@ __global__ void __launch_bounds__(THREADS, MIN_CTAS) softmax_layernorm_reg_kerne
     // issuing the prefetch later, into the registers the unpack frees, measured far slower).
     bool live[CHUNKS];
 #pragma unroll
-    for (int j = 0; j < CHUNKS; ++j) live[j] = (long long)j * THREADS + threadIdx.x < n_pkt;
+    for (int j = 0; j < CHUNKS; ++j) live[j] = FULL || (long long)j * THREADS + threadIdx.x < n_pkt;
     Vec16<T> raw[CHUNKS], nxt[CHUNKS];
     long long row = blockIdx.x;
     if (row < p.rows) {
@@ -324,7 +327,9 @@ __global__ void __launch_bounds__(THREADS, MIN_CTAS) softmax_layernorm_reg_kerne
         for (int j = 0; j < CHUNKS; ++j)
             if (live[j]) raw[j] = ld_stream(in0 + ((long long)j * THREADS + threadIdx.x) * L);
     }
-    for (; row < p.rows; row += gridDim.x) {
+    // one row: `cur` holds it, `nx` receives the row after it (the two buffers swap roles from row to
+    // row, so no packet is copied between registers)
+    auto one_row = [&](Vec16<T> (&raw)[CHUNKS], Vec16<T> (&nxt)[CHUNKS], long long row) {
         T* out = static_cast<T*>(p.out) + row * p.cols;
         const long long row_next = row + gridDim.x;
         if (row_next < p.rows) {
@@ -399,8 +404,10 @@ __global__ void __launch_bounds__(THREADS, MIN_CTAS) softmax_layernorm_reg_kerne
                 }
                 st_stream(out + pk * L, pack_pairs<T>(x[j]));
             }
-#pragma unroll
-        for (int j = 0; j < CHUNKS; ++j) raw[j] = nxt[j];
+    };
+    for (; row < p.rows; row += 2LL * gridDim.x) {
+        one_row(raw, nxt, row);
+        if (row + gridDim.x < p.rows) one_row(nxt, raw, row + gridDim.x);
     }
 }
 
@@ -468,7 +475,11 @@ static void launch_reg(const RowParams& p, int blocks, cudaStream_t s) {
         const long long cap = (long long)sm_count() * 8;
         const int g = (int)(p.rows < cap ? p.rows : cap);
         (void)blocks;
-        softmax_layernorm_reg_kernel<T, THREADS, CHUNKS, kMinCtas><<<g, THREADS, 0, s>>>(p);
+        constexpr int L = 16 / sizeof(T);
+        if (p.cols / L == (long long)THREADS * CHUNKS)
+            softmax_layernorm_reg_kernel<T, THREADS, CHUNKS, kMinCtas, true><<<g, THREADS, 0, s>>>(p);
+        else
+            softmax_layernorm_reg_kernel<T, THREADS, CHUNKS, kMinCtas, false><<<g, THREADS, 0, s>>>(p);
     }
     else
         row_reg_kernel<T, THREADS, CHUNKS, MODE><<<blocks, THREADS, 0, s>>>(p);

@@ -236,8 +236,8 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
-// A load whose registers may not be read before tmem_ld_wait() on the same array: lets a second load
-// or arithmetic on other registers run while the data is on its way.
+// A load whose registers may not be read before tmem_ld_wait(): lets a second load or arithmetic on
+// other registers run while the data is on its way.
 __device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, float (&v)[32]) {
     uint32_t* r = reinterpret_cast<uint32_t*>(v);
     asm volatile(
@@ -251,18 +251,10 @@ __device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, float (&v)[32]) 
         : "r"(taddr)
         : "memory");
 }
-// The wait names the registers as read-write operands, so no use of them can be scheduled before it.
-__device__ __forceinline__ void tmem_ld_wait(float (&v)[32]) {
-    uint32_t* r = reinterpret_cast<uint32_t*>(v);
-    asm volatile(
-        "tcgen05.wait::ld.sync.aligned;"
-        : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-          "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
-          "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
-          "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-        :
-        : "memory");
-}
+// Waits for every tensor-memory load issued so far. (Naming the loaded registers as read-write operands
+// of this statement, to pin their uses behind it, made the compiler copy all of them - a sixth of the
+// attention kernel's instructions; the volatile statement with a memory clobber is what stays.)
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // 64 consecutive columns of one TMEM lane per thread: two loads in flight, one wait.
