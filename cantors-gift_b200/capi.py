@@ -65,6 +65,10 @@ class GemmDesc(C.Structure):
                 ("inner_stride_c", C.c_int64)]
 
 
+class GemmTuning(C.Structure):
+    _fields_ = [("tile_n", C.c_int32), ("cta_pair", C.c_int32), ("tail_split", C.c_int32), ("reserved", C.c_int32)]
+
+
 class AttentionDesc(C.Structure):
     _fields_ = [("dtype", C.c_int32), ("head_dim", C.c_int32), ("batch", C.c_int64), ("heads", C.c_int64),
                 ("seq_q", C.c_int64), ("seq_kv", C.c_int64),
@@ -108,6 +112,7 @@ SIGNATURES = {
     "cg_b200_attention": (_i, [C.POINTER(AttentionDesc), _vp, _vp, _vp, _vp, _vp]),
     "cg_b200_gemm_workspace_bytes": (_i, [C.POINTER(GemmDesc), C.POINTER(_sz)]),
     "cg_b200_gemm": (_i, [C.POINTER(GemmDesc), _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "cg_b200_gemm_tuned": (_i, [C.POINTER(GemmDesc), C.POINTER(GemmTuning), _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "cg_b200_last_device_error": (_i, [_vp, C.POINTER(C.c_uint32)]),
     "cg_b200_gemm_f32_static": (_i, [C.POINTER(GemmDesc), _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cg_b200_comm_unique_id": (_i, [_vp]),

@@ -79,6 +79,7 @@ struct GemmParams {
     long long full_units;
     uint32_t idesc_half;   // instruction descriptor with N = BN / 2
     int debug;             // tuning experiments only (CG_B200_GEMM_DEBUG): 1 = no operand loads, 2 = no epilogue work
+    int tail_split;        // host side only: 0 = library default, 1 = off, 2 = on (cg_b200_gemm_tuning)
     uint32_t* err_word;
 };
 
@@ -693,7 +694,8 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& ta_lo, const
     // persistent: one CTA (or CTA pair) per SM (or SM pair), never more CTAs than tiles
     const long long slots = sm_count() / kCta;
     p.full_units = p.num_tiles;
-    if (kCta == 2 && BN == 256 && !kSplit && tail_split_enabled()) {
+    const bool tail = p.tail_split == 0 ? tail_split_enabled() : p.tail_split == 2;
+    if (kCta == 2 && BN == 256 && !kSplit && tail) {
         // a last partial wave of r <= slots / 2 tiles runs as 2r half-width units instead
         const long long r = p.num_tiles % slots;
         if (r > 0 && 2 * r <= slots) {
@@ -776,9 +778,16 @@ struct PeerSet {
 
 static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B, const void* bias,
                     const void* residual, void* C, void* workspace, size_t workspace_bytes, void* stream,
-                    bool shared_err_word, uint32_t* err_word, const PeerSet* peers = nullptr) {
+                    bool shared_err_word, uint32_t* err_word, const PeerSet* peers = nullptr,
+                    const cg_b200_gemm_tuning* tuning = nullptr) {
     int st = validate_desc(desc);
     if (st) return st;
+    if (tuning) {
+        const cg_b200_gemm_tuning& t = *tuning;
+        if ((t.tile_n != 0 && t.tile_n != 64 && t.tile_n != 128 && t.tile_n != 256) || t.cta_pair < 0 || t.cta_pair > 2 ||
+            t.tail_split < 0 || t.tail_split > 2 || t.reserved != 0)
+            return CG_B200_ERR_INVALID_ARG;
+    }
     const cg_b200_gemm_desc& d = *desc;
     if (d.M == 0 || d.N == 0) return CG_B200_OK;
     if (!C || (d.K > 0 && (!A || !B))) return CG_B200_ERR_NULL_POINTER;   // K == 0: A and B are empty
@@ -845,14 +854,33 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
     }
 
     const bool tf32 = d.in_dtype == CG_B200_F32;
-    int bn = choose_bn(desc, sp.active && sp.copies == 2);
+    const bool split = sp.active && sp.copies == 2;
+    int bn = choose_bn(desc, split);
     // CTA pairs (256 x 256 tiles) for 16-bit inputs once the problem spans more than one such tile row
-    const int cta = (!tf32 && bn == 256 && d.M > kBM && pair_enabled()) ? 2 : 1;
+    int cta = (!tf32 && bn == 256 && d.M > kBM && pair_enabled()) ? 2 : 1;
     if (cta == 2) {
         // too few 256 x 256 tiles to occupy half of the SM pairs (a small shard of a sharded GEMM):
         // halve the tile width so that twice as many pairs have work
         const long long tiles = ((d.M + 2 * kBM - 1) / (2 * kBM)) * ((d.N + 255) / 256) * d.batch;
         if (2 * tiles <= sm_count() / 2) bn = 128;
+    }
+    p.tail_split = 0;
+    if (tuning) {
+        // an autotuner's choice replaces the heuristic above; combinations the kernels do not have are refused
+        const cg_b200_gemm_tuning& t = *tuning;
+        if (t.cta_pair == 2 && tf32) return CG_B200_ERR_UNSUPPORTED;          // pairs: 16-bit inputs only
+        if (t.cta_pair != 0) cta = t.cta_pair;
+        else if (t.tile_n == 64) cta = 1;                                     // a 64-wide tile exists for one CTA only
+        if (t.tile_n != 0) {
+            if (split && t.tile_n != 128) return CG_B200_ERR_UNSUPPORTED;     // the 3xTF32 kernel has one tile
+            bn = t.tile_n;
+        } else if (cta == 2 && bn < 128) {
+            bn = 128;
+        } else if (cta == 1 && t.cta_pair == 1) {
+            bn = choose_bn(desc, split);
+        }
+        if (cta == 2 && bn == 64) return CG_B200_ERR_UNSUPPORTED;             // a pair's tile is 128 or 256 wide
+        p.tail_split = t.tail_split;
     }
     p.idesc = make_idesc(d.in_dtype, tf32, p.b_mn_major != 0, kBM * cta, bn);
     p.idesc_half = make_idesc(d.in_dtype, tf32, p.b_mn_major != 0, kBM * cta, bn / 2);
@@ -938,6 +966,12 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
 extern "C" int cg_b200_gemm(const cg_b200_gemm_desc* desc, const void* A, const void* B, const void* bias,
                             const void* residual, void* C, void* workspace, size_t workspace_bytes, void* stream) {
     return gemm_run(desc, A, B, bias, residual, C, workspace, workspace_bytes, stream, true, nullptr);
+}
+
+extern "C" int cg_b200_gemm_tuned(const cg_b200_gemm_desc* desc, const cg_b200_gemm_tuning* tuning, const void* A,
+                                  const void* B, const void* bias, const void* residual, void* C, void* workspace,
+                                  size_t workspace_bytes, void* stream) {
+    return gemm_run(desc, A, B, bias, residual, C, workspace, workspace_bytes, stream, true, nullptr, nullptr, tuning);
 }
 
 // ---- fp32 GEMM for callers that cannot allocate -----------------------------------------------------

@@ -80,14 +80,19 @@ def gemm_workspace(desc, device):
     return ws, ws.numel()
 
 
-def gemm(desc, A, B, C_out, bias=None, residual=None, workspace=None, stream=None):
+def gemm(desc, A, B, C_out, bias=None, residual=None, workspace=None, stream=None, tuning=None):
+    """`tuning`: a capi.GemmTuning (an autotuner's tile choice) or None for the library's heuristic."""
     _require_cuda(A, B, C_out, bias, residual)
     if workspace is None:
         workspace, ws_bytes = gemm_workspace(desc, A.device)
     else:
         ws_bytes = workspace.numel() * workspace.element_size()
-    check(lib().cg_b200_gemm(C.byref(desc), _ptr(A), _ptr(B), _ptr(bias), _ptr(residual), _ptr(C_out),
-                             _ptr(workspace), ws_bytes, _stream(stream)), "gemm")
+    if tuning is None:
+        check(lib().cg_b200_gemm(C.byref(desc), _ptr(A), _ptr(B), _ptr(bias), _ptr(residual), _ptr(C_out),
+                                 _ptr(workspace), ws_bytes, _stream(stream)), "gemm")
+    else:
+        check(lib().cg_b200_gemm_tuned(C.byref(desc), C.byref(tuning), _ptr(A), _ptr(B), _ptr(bias), _ptr(residual),
+                                       _ptr(C_out), _ptr(workspace), ws_bytes, _stream(stream)), "gemm_tuned")
     return C_out
 
 

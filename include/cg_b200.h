@@ -243,6 +243,23 @@ int cg_b200_gemm_workspace_bytes(const cg_b200_gemm_desc* desc, size_t* bytes);
 int cg_b200_gemm(const cg_b200_gemm_desc* desc, const void* A, const void* B,
                  const void* bias, const void* residual, void* C, void* workspace,
                  size_t workspace_bytes, void* stream);
+/* The same GEMM with the tile choice made by the caller instead of the library's heuristic: what a
+ * BenchmarkFn handed to the reference's autotuner times, one call per candidate schedule
+ * (include/cg/autotuner/bayesian_optimizer.hpp:79-96; Runtime::autotune_and_cache,
+ * src/runtime/runtime.cpp:287-312, and MatmulPipeline::run, src/pipeline/matmul_pipeline.cpp:261-323,
+ * take such a function and today receive a stub). Every field 0 = library default. Results do not
+ * depend on the choice (the K order of the accumulation is the same in every variant).
+ * CG_B200_ERR_UNSUPPORTED for a combination no kernel has: CTA pairs with fp32 inputs or with a
+ * 64-wide tile, any tile but 128 for the 3xTF32 path. */
+typedef struct cg_b200_gemm_tuning {
+    int32_t tile_n;      /* 0, 64, 128 or 256 output columns per tile                          */
+    int32_t cta_pair;    /* 0 = default, 1 = one CTA per 128-row tile, 2 = CTA pair, 256 rows   */
+    int32_t tail_split;  /* 0 = default, 1 = off, 2 = on: last partial wave as half-width units */
+    int32_t reserved;    /* 0 */
+} cg_b200_gemm_tuning;
+int cg_b200_gemm_tuned(const cg_b200_gemm_desc* desc, const cg_b200_gemm_tuning* tuning, const void* A,
+                       const void* B, const void* bias, const void* residual, void* C, void* workspace,
+                       size_t workspace_bytes, void* stream);
 /* Reads and clears the error word written by a bounded device-side wait that ran out
  * (0 = none). Synchronises `stream`. */
 int cg_b200_last_device_error(void* stream, uint32_t* word);

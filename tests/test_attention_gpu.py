@@ -20,20 +20,19 @@ def _host(O, t, dtype):
     return O.to_f32(t.cpu().view(torch.int16).numpy().view(np.uint16 if dtype == O.BF16 else np.float16), dtype)
 
 
-@pytest.mark.parametrize("dtype_name", ["BF16", "F16"])
-@pytest.mark.parametrize("B,H,Sq,Skv", [(1, 1, 128, 128), (2, 3, 256, 384), (1, 2, 100, 200), (2, 2, 130, 77), (1, 1, 1, 1)])
-def test_attention_contiguous_heads(ops, cgb, oracle, dtype_name, B, H, Sq, Skv):
+def _run_contiguous(ops, cgb, oracle, dtype_name, B, H, Sq, Skv, scale=0.125, spread=1.0):
     import torch
     capi, O = cgb.capi, oracle
     dtype = getattr(capi, dtype_name)
     d = 64
     rng = np.random.default_rng(B * 100 + Sq + Skv)
-    q, k, v = (O.to_storage(rng.standard_normal(s, dtype=np.float32), dtype) for s in ((B, H, Sq, d), (B, H, Skv, d), (B, H, Skv, d)))
-    want = O.to_f32(O.attention(q, k, v, dtype, 0.125), dtype)
+    q, k, v = (O.to_storage(rng.standard_normal(s, dtype=np.float32) * f, dtype)
+               for s, f in (((B, H, Sq, d), spread), ((B, H, Skv, d), spread), ((B, H, Skv, d), 1.0)))
+    want = O.to_f32(O.attention(q, k, v, dtype, scale), dtype)
     desc = capi.AttentionDesc(dtype=dtype, head_dim=d, batch=B, heads=H, seq_q=Sq, seq_kv=Skv, ldq=d, ldk=d, ldv=d, ldo=d,
                               head_stride_q=Sq * d, head_stride_k=Skv * d, head_stride_v=Skv * d, head_stride_o=Sq * d,
                               batch_stride_q=H * Sq * d, batch_stride_k=H * Skv * d, batch_stride_v=H * Skv * d,
-                              batch_stride_o=H * Sq * d, scale=0.125)
+                              batch_stride_o=H * Sq * d, scale=scale)
     qd, kd, vd = (_dev(ops, np.ascontiguousarray(t), dtype) for t in (q, k, v))
     od = torch.zeros(B, H, Sq, d, dtype=ops.TORCH_DTYPE[dtype], device="cuda")
     p = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
@@ -41,6 +40,26 @@ def test_attention_contiguous_heads(ops, cgb, oracle, dtype_name, B, H, Sq, Skv)
                                            C.c_void_p(torch.cuda.current_stream().cuda_stream)), "attention")
     assert ops.last_device_error() == 0
     assert_close(_host(O, od, dtype), want, 1e-2, f"attention {dtype_name} B{B} H{H} Sq{Sq} Skv{Skv}")
+
+
+@pytest.mark.parametrize("dtype_name", ["BF16", "F16"])
+@pytest.mark.parametrize("B,H,Sq,Skv", [(1, 1, 128, 128), (2, 3, 256, 384), (1, 2, 100, 200), (2, 2, 130, 77), (1, 1, 1, 1)])
+def test_attention_contiguous_heads(ops, cgb, oracle, dtype_name, B, H, Sq, Skv):
+    _run_contiguous(ops, cgb, oracle, dtype_name, B, H, Sq, Skv)
+
+
+# The kernel's CTAs are persistent (one per SM) over units of 256 query rows, with rings of 5 K/V
+# stages and 3 score buffers: more units than SMs, key-tile counts that wrap the rings, a second
+# query tile that lies wholly past the end, and both ragged edges at once.
+@pytest.mark.parametrize("B,H,Sq,Skv", [(40, 4, 256, 256), (1, 2, 300, 1000), (3, 50, 64, 640), (1, 1, 257, 129)])
+def test_attention_persistent_units_and_ring_wraps(ops, cgb, oracle, B, H, Sq, Skv):
+    _run_contiguous(ops, cgb, oracle, "BF16", B, H, Sq, Skv)
+
+
+def test_attention_wide_score_range(ops, cgb, oracle):
+    """Scores with a standard deviation of 32: the running row maximum moves by tens from tile to
+    tile, so the rescale of the running sum and output by 2^(m_old - m_new) does real work."""
+    _run_contiguous(ops, cgb, oracle, "BF16", 1, 2, 256, 768, scale=0.5, spread=2.0)
 
 
 def test_attention_on_packed_qkv_rows(ops, cgb, oracle):

@@ -2,6 +2,7 @@
 
 Tolerances are the path's stated bounds: rel-err <= 1e-4 for fp32 (3xTF32 split), <= 1e-2 for
 bf16/f16, on both metrics of conftest.assert_close."""
+import ctypes as C
 import os
 
 import numpy as np
@@ -249,3 +250,50 @@ def test_full_size_bf16_gemm_bias_gelu(ops, cgb, oracle):
     ops.gemm(gd0, Ad * 2, Bd, C2)
     torch.cuda.synchronize()
     assert torch.equal(C1 * 2, C2)
+
+
+def test_tuned_variants_agree_bit_for_bit(ops, cgb, oracle):
+    """cg_b200_gemm_tuned: every tile choice an autotuner may ask for gives the heuristic's result
+    bit for bit (same K order of accumulation), and combinations no kernel has are refused."""
+    import torch
+    capi, O = cgb.capi, oracle
+    M, N, K = 600, 840, 320   # several tile rows and columns with ragged edges for every tile shape
+    rng = np.random.default_rng(77)
+    A = O.to_storage(rng.standard_normal((M, K), dtype=np.float32) * 0.05, capi.BF16)
+    B = O.to_storage(rng.standard_normal((K, N), dtype=np.float32) * 0.05, capi.BF16)
+    bias = O.to_storage(rng.standard_normal(N, dtype=np.float32), capi.BF16)
+    desc = capi.make_gemm_desc(M, N, K, capi.BF16, capi.BF16, epilogue="bias_gelu_tanh")
+    Ad, Bd, bd = (_dev(ops, t, capi.BF16) for t in (A, B, bias))
+
+    def run(tuning):
+        Cd = torch.zeros(M * N, dtype=torch.bfloat16, device="cuda")
+        ops.gemm(desc, Ad, Bd, Cd, bias=bd, tuning=tuning)
+        assert ops.last_device_error() == 0
+        return Cd.view(torch.int16).cpu().numpy()
+
+    base = run(None)
+    want = O.gemm(O.make_gemm_desc(M, N, K, capi.BF16, capi.BF16, epilogue="bias_gelu_tanh"), A, B, bias=bias,
+                  out=np.zeros(M * N, dtype=O.NP_OF[capi.BF16]))
+    assert_close(O.to_f32(base.view(np.uint16), capi.BF16), O.to_f32(want, capi.BF16), 1e-2, "tuned gemm baseline")
+    ran = 0
+    for tile_n in (0, 64, 128, 256):
+        for pair in (0, 1, 2):
+            for tail in (0, 1, 2):
+                t = capi.GemmTuning(tile_n=tile_n, cta_pair=pair, tail_split=tail, reserved=0)
+                if pair == 2 and tile_n == 64:
+                    with pytest.raises(capi.CgB200Error) as e:
+                        run(t)
+                    assert e.value.status == capi.ERR_UNSUPPORTED
+                    continue
+                got = run(t)
+                assert np.array_equal(got, base), f"tile_n={tile_n} pair={pair} tail={tail} differs from the default"
+                ran += 1
+    assert ran == 33
+    bad = capi.GemmTuning(tile_n=96, cta_pair=0, tail_split=0, reserved=0)
+    assert cgb.lib().cg_b200_gemm_tuned(C.byref(desc), C.byref(bad), None, None, None, None, None, None, 0, None) == capi.ERR_INVALID_ARG
+    f32 = capi.make_gemm_desc(128, 128, 64, capi.F32, capi.F32)
+    pair = capi.GemmTuning(tile_n=0, cta_pair=2, tail_split=0, reserved=0)
+    x = torch.zeros(128 * 128, dtype=torch.float32, device="cuda")
+    with pytest.raises(capi.CgB200Error) as e:
+        ops.gemm(f32, x, x, x.clone(), tuning=pair)
+    assert e.value.status == capi.ERR_UNSUPPORTED
