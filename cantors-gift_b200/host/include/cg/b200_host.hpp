@@ -21,6 +21,7 @@
 
 #include <cstdint>
 #include <functional>
+#include <limits>
 #include <map>
 #include <memory>
 #include <optional>
@@ -202,6 +203,7 @@ struct PlanRecord {
     u32 kind = 0;
     cg_b200_eltwise_desc eltwise{};     // Eltwise
     cg_b200_gemm_desc gemm{};           // Gemm
+    cg_b200_gemm_tuning tuning{};       // Gemm: all zero = the library's heuristic
     i32 row_dtype = 0;                  // row reductions
     i64 rows = 0, cols = 0;
     float eps = 1e-5f;
@@ -212,7 +214,7 @@ struct PlanRecord {
 };
 
 struct LaunchPlan {
-    static constexpr u32 kMagic = 0x30304243;   // "CB00"
+    static constexpr u32 kMagic = 0x31304243;   // "CB01"
     u32 n_inputs = 0, n_outputs = 0;
     std::vector<PlanBuffer> buffers;
     std::vector<PlanRecord> records;
@@ -240,11 +242,77 @@ struct LoweringOptions {
     float layernorm_eps = 1e-5f;                    // the op carries no attribute (src/ir/ops.cpp:536-556)
 };
 
-class Schedule {};   // accepted and ignored, as in the reference (tensor_to_codegen.cpp:361-366)
+// ---- schedules and the autotuner's interface ------------------------------------------------------
+// Stand-ins for include/cg/schedule/schedule.hpp:24-84 (the schedule subsystem itself is outside this
+// path): a Schedule is a list of transforms, a ScheduleSpace a list of schedules, and grid_matmul
+// builds the same Tile m / Tile n / Tile k (+ Vectorize) schedules as src/schedule/schedule.cpp:66-87.
+// The reference's lowering accepts a schedule and ignores it (tensor_to_codegen.cpp:361-366); this
+// one reads the Tile transforms on "m" and "n" as the GEMM kernel's tile choice.
+enum class TransformKind : u8 { Split, Tile, Interchange, Fuse, Vectorize, Parallelize, Unroll, Cache, Pipeline, Prefetch, Bind };
+
+struct Transform {
+    TransformKind kind = TransformKind::Tile;
+    std::string dim;
+    i64 factor = 0;
+    i64 factor2 = 0;
+    std::string target;
+};
+
+class Schedule {
+public:
+    void add(Transform t) { transforms_.push_back(std::move(t)); }
+    const std::vector<Transform>& transforms() const { return transforms_; }
+    u64 hash() const;
+    bool operator==(const Schedule& o) const;
+
+private:
+    std::vector<Transform> transforms_;
+};
+
+class ScheduleSpace {
+public:
+    void add(Schedule s) { schedules_.push_back(std::move(s)); }
+    const std::vector<Schedule>& schedules() const { return schedules_; }
+    usize size() const { return schedules_.size(); }
+    static ScheduleSpace grid_matmul(std::vector<i64> m_tiles, std::vector<i64> n_tiles, std::vector<i64> k_tiles,
+                                     std::vector<i64> vector_widths);
+
+private:
+    std::vector<Schedule> schedules_;
+};
+
+// include/cg/autotuner/bayesian_optimizer.hpp:79-96. A benchmark function returns the measured runtime
+// of a schedule in seconds (infinity: cannot run).
+using BenchmarkFn = std::function<double(const Schedule&)>;
+
+struct AutotuneResult {
+    Schedule best_schedule;
+    double best_runtime = std::numeric_limits<double>::infinity();
+    std::vector<double> runtime_history;
+    usize total_benchmarks = 0;
+};
+
+// Same signature as the reference's search. The GEMM kernel's tile space has a dozen points, so this
+// one simply measures candidates in order until `max_benchmarks` (a surrogate model has nothing to
+// add at that size); `initial_random` is accepted for source compatibility.
+AutotuneResult bayesian_autotune(const ScheduleSpace& space, BenchmarkFn benchmark, usize max_benchmarks = 20,
+                                 usize initial_random = 3);
+
+// Tile m = 128 -> one CTA per tile, 256 -> CTA pair; Tile n = 64 / 128 / 256 -> tile width. Transforms
+// the kernel has no knob for are ignored. Empty optional: a tile the kernels do not have.
+std::optional<cg_b200_gemm_tuning> gemm_tuning_from_schedule(const Schedule& s);
+
+class Device;
+// The function an autotuner calls per candidate: runs `desc` with the schedule's tiles through
+// cg_b200_gemm_tuned on zero-filled operands of `device` and returns the mean seconds of `iters`
+// launches after `warmup`, timed with events on the device's stream. Infinity for a schedule that
+// maps to no kernel. The operand buffers live as long as the returned function.
+BenchmarkFn make_gemm_benchmark(const cg_b200_gemm_desc& desc, Device& device, int iters = 20, int warmup = 3);
 
 class TensorToCodegenLowering {
 public:
     explicit TensorToCodegenLowering(LoweringOptions opts = {}) : opts_(opts) {}
+    // Tile transforms on "m" / "n" in `schedule` choose the tiles of every GEMM kernel of the module.
     CGModule lower(const Module& m, const Schedule& schedule = {});
     const LoweringOptions& options() const { return opts_; }
     int status() const { return status_; }              // cg_b200_status of the last lower()
@@ -416,6 +484,18 @@ public:
         bool cache_hit = false;
     };
     CompileResult compile_and_cache(u64 cache_key, const CGModule& cgm, MachineBackend& backend);
+    // src/runtime/runtime.cpp:287-312 runs the search and then leaves compiling to the caller ("the
+    // caller would lower the Tensor IR using the best schedule"). Here the caller passes that lowering
+    // as `lower_best`, and the executable compiled from the winning schedule is what gets cached.
+    struct AutotuneResult {
+        std::shared_ptr<Executable> executable;
+        bool cache_hit = false;
+        double best_runtime = std::numeric_limits<double>::infinity();
+        usize total_benchmarks = 0;
+        Schedule best_schedule;
+    };
+    AutotuneResult autotune_and_cache(u64 cache_key, const ScheduleSpace& space, const BenchmarkFn& benchmark,
+                                      MachineBackend& backend, const std::function<CGModule(const Schedule&)>& lower_best);
 
 private:
     std::vector<std::unique_ptr<Device>> devices_;

@@ -451,14 +451,22 @@ std::string record_blob(const PlanRecord& r) {
 
 }  // namespace
 
-CGModule TensorToCodegenLowering::lower(const Module& m, const Schedule&) {
+CGModule TensorToCodegenLowering::lower(const Module& m, const Schedule& schedule) {
     status_ = CG_B200_OK;
     message_.clear();
     CGModule out;
+    const std::optional<cg_b200_gemm_tuning> tuning = gemm_tuning_from_schedule(schedule);
+    if (!tuning) {
+        status_ = CG_B200_ERR_UNSUPPORTED;
+        message_ = "schedule: the GEMM kernels have no such tile";
+        return out;
+    }
     try {
         for (const Function& fn : m.functions) {
             Planner p(fn, opts_);
             const LaunchPlan plan = p.run();
+            for (auto& ker : p.kernels)
+                if (ker.rec.kind == PlanRecord::Gemm) ker.rec.tuning = *tuning;
             CGFunction& cf = out.create_function(fn.name);
             for (u32 i = 0; i < plan.n_inputs + plan.n_outputs; ++i) {
                 CGValue v = cf.allocate(plan.buffers[i].dtype, 1);

@@ -128,8 +128,8 @@ public:
                     break;
                 }
                 case PlanRecord::Gemm:
-                    s = cg_b200_gemm(&r.gemm, at(r.input[0]), at(r.input[1]), at(r.input[2]), at(r.input[3]), at(r.output),
-                                     workspace_, plan_.workspace_bytes, st);
+                    s = cg_b200_gemm_tuned(&r.gemm, &r.tuning, at(r.input[0]), at(r.input[1]), at(r.input[2]), at(r.input[3]),
+                                           at(r.output), workspace_, plan_.workspace_bytes, st);
                     break;
                 case PlanRecord::Softmax:
                     s = cg_b200_softmax(r.row_dtype, at(r.input[0]), at(r.output), r.rows, r.cols, st);
@@ -302,6 +302,183 @@ Runtime::CompileResult Runtime::compile_and_cache(u64 cache_key, const CGModule&
         res.cache_hit = true;
         return res;
     }
+    res.executable = std::shared_ptr<Executable>(backend.compile(cgm).release());
+    if (res.executable) cache_.insert(cache_key, res.executable);
+    return res;
+}
+
+}  // namespace cg
+
+// ---- schedules and autotuning ---------------------------------------------------------------------------
+namespace cg {
+
+static u64 mix(u64 h, u64 v) {   // FNV-1a over 64-bit words
+    h ^= v;
+    return h * 1099511628211ull;
+}
+
+u64 Schedule::hash() const {
+    u64 h = 1469598103934665603ull;
+    for (const Transform& t : transforms_) {
+        h = mix(h, static_cast<u64>(t.kind));
+        for (char c : t.dim) h = mix(h, static_cast<u8>(c));
+        h = mix(h, static_cast<u64>(t.factor));
+        h = mix(h, static_cast<u64>(t.factor2));
+        for (char c : t.target) h = mix(h, static_cast<u8>(c));
+    }
+    return h;
+}
+
+bool Schedule::operator==(const Schedule& o) const {
+    if (transforms_.size() != o.transforms_.size()) return false;
+    for (usize i = 0; i < transforms_.size(); ++i) {
+        const Transform &a = transforms_[i], &b = o.transforms_[i];
+        if (a.kind != b.kind || a.dim != b.dim || a.factor != b.factor || a.factor2 != b.factor2 || a.target != b.target)
+            return false;
+    }
+    return true;
+}
+
+ScheduleSpace ScheduleSpace::grid_matmul(std::vector<i64> m_tiles, std::vector<i64> n_tiles, std::vector<i64> k_tiles,
+                                         std::vector<i64> vector_widths) {
+    ScheduleSpace space;
+    for (i64 m : m_tiles)
+        for (i64 n : n_tiles)
+            for (i64 k : k_tiles)
+                for (i64 v : vector_widths) {
+                    Schedule s;
+                    s.add({TransformKind::Tile, "m", m, n, ""});
+                    s.add({TransformKind::Tile, "n", n, 0, ""});
+                    s.add({TransformKind::Tile, "k", k, 0, ""});
+                    s.add({TransformKind::Parallelize, "m", 0, 0, ""});
+                    s.add({TransformKind::Parallelize, "n", 0, 0, ""});
+                    s.add({TransformKind::Vectorize, "n_inner", v, 0, ""});
+                    s.add({TransformKind::Cache, "a", 0, 0, "A"});
+                    s.add({TransformKind::Cache, "b", 0, 0, "B"});
+                    space.add(std::move(s));
+                }
+    return space;
+}
+
+AutotuneResult bayesian_autotune(const ScheduleSpace& space, BenchmarkFn benchmark, usize max_benchmarks, usize initial_random) {
+    (void)initial_random;
+    AutotuneResult res;
+    if (!benchmark) return res;
+    for (const Schedule& s : space.schedules()) {
+        if (res.total_benchmarks >= max_benchmarks) break;
+        const double t = benchmark(s);
+        res.runtime_history.push_back(t);
+        ++res.total_benchmarks;
+        if (t < res.best_runtime) {
+            res.best_runtime = t;
+            res.best_schedule = s;
+        }
+    }
+    return res;
+}
+
+std::optional<cg_b200_gemm_tuning> gemm_tuning_from_schedule(const Schedule& s) {
+    cg_b200_gemm_tuning t{};
+    for (const Transform& x : s.transforms()) {
+        if (x.kind != TransformKind::Tile) continue;
+        if (x.dim == "m") {
+            if (x.factor == 128) t.cta_pair = 1;
+            else if (x.factor == 256) t.cta_pair = 2;
+            else if (x.factor != 0) return std::nullopt;
+        } else if (x.dim == "n") {
+            if (x.factor == 64 || x.factor == 128 || x.factor == 256) t.tile_n = static_cast<int32_t>(x.factor);
+            else if (x.factor != 0) return std::nullopt;
+        }
+    }
+    if (t.cta_pair == 2 && t.tile_n == 64) return std::nullopt;   // a CTA pair's tile is 128 or 256 wide
+    return t;
+}
+
+namespace {
+struct GemmBenchState {
+    cg_b200_gemm_desc desc{};
+    Device* device = nullptr;
+    std::unique_ptr<Stream> stream;
+    std::unique_ptr<Event> begin, end;
+    void *a = nullptr, *b = nullptr, *c = nullptr, *bias = nullptr, *res = nullptr, *ws = nullptr;
+    size_t ws_bytes = 0;
+    int iters = 20, warmup = 3;
+    bool ok = false;
+    ~GemmBenchState() {
+        if (!device) return;
+        for (void* p : {a, b, c, bias, res, ws})
+            if (p) device->allocator().deallocate(p);
+    }
+};
+u64 elem_bytes(int dtype) { return dtype == CG_B200_F32 ? 4 : 2; }
+void* stream_handle(Stream& s) { return static_cast<CudaStream&>(s).handle(); }
+}  // namespace
+
+BenchmarkFn make_gemm_benchmark(const cg_b200_gemm_desc& desc, Device& device, int iters, int warmup) {
+    auto st = std::make_shared<GemmBenchState>();
+    st->desc = desc;
+    st->device = &device;
+    st->iters = iters > 0 ? iters : 1;
+    st->warmup = warmup >= 0 ? warmup : 0;
+    st->stream = device.create_stream();
+    st->begin = device.create_event();
+    st->end = device.create_event();
+    const cg_b200_gemm_desc& d = st->desc;
+    const u64 in = elem_bytes(d.in_dtype), out = elem_bytes(d.out_dtype);
+    const i64 b_rows = d.b_transposed ? d.N : d.K;
+    const u64 a_bytes = static_cast<u64>((d.batch_stride_a ? d.batch_stride_a * d.batch : d.M * d.lda)) * in;
+    const u64 b_bytes = static_cast<u64>((d.batch_stride_b ? d.batch_stride_b * d.batch : b_rows * d.ldb)) * in;
+    const u64 c_bytes = static_cast<u64>((d.batch_stride_c ? d.batch_stride_c * d.batch : d.M * d.ldc)) * out;
+    auto zeroed = [&](u64 bytes) -> void* {
+        void* p = device.allocator().allocate(bytes ? bytes : 16);
+        if (p) cg_b200_memset(p, 0, bytes ? bytes : 16, nullptr);
+        return p;
+    };
+    st->a = zeroed(a_bytes);
+    st->b = zeroed(b_bytes);
+    st->c = zeroed(c_bytes);
+    st->bias = zeroed(static_cast<u64>(d.N) * out);
+    st->res = zeroed(c_bytes);
+    if (cg_b200_gemm_workspace_bytes(&st->desc, &st->ws_bytes) == CG_B200_OK && st->ws_bytes) st->ws = zeroed(st->ws_bytes);
+    st->ok = st->stream && st->begin && st->end && st->a && st->b && st->c && st->bias && st->res && (st->ws || !st->ws_bytes);
+    cg_b200_stream_sync(nullptr);
+    return [st](const Schedule& s) -> double {
+        const double never = std::numeric_limits<double>::infinity();
+        if (!st->ok) return never;
+        const auto tuning = gemm_tuning_from_schedule(s);
+        if (!tuning) return never;
+        void* h = stream_handle(*st->stream);
+        auto once = [&]() {
+            return cg_b200_gemm_tuned(&st->desc, &*tuning, st->a, st->b, st->bias, st->res, st->c, st->ws, st->ws_bytes, h);
+        };
+        for (int i = 0; i < st->warmup + 1; ++i)
+            if (once() != CG_B200_OK) return never;   // refused combinations end here
+        st->begin->record(*st->stream);
+        for (int i = 0; i < st->iters; ++i)
+            if (once() != CG_B200_OK) return never;
+        st->end->record(*st->stream);
+        st->end->wait();
+        uint32_t word = 0;
+        if (cg_b200_last_device_error(h, &word) != CG_B200_OK || word != 0) return never;
+        return st->end->elapsed_sec_since(*st->begin) / st->iters;
+    };
+}
+
+Runtime::AutotuneResult Runtime::autotune_and_cache(u64 cache_key, const ScheduleSpace& space, const BenchmarkFn& benchmark,
+                                                    MachineBackend& backend,
+                                                    const std::function<CGModule(const Schedule&)>& lower_best) {
+    AutotuneResult res;
+    if (auto hit = cache_.lookup(cache_key)) {
+        res.executable = *hit;
+        res.cache_hit = true;
+        return res;
+    }
+    const cg::AutotuneResult tuned = bayesian_autotune(space, benchmark);
+    res.best_runtime = tuned.best_runtime;
+    res.total_benchmarks = tuned.total_benchmarks;
+    res.best_schedule = tuned.best_schedule;
+    if (!(tuned.best_runtime < std::numeric_limits<double>::infinity()) || !lower_best) return res;   // nothing ran
+    const CGModule cgm = lower_best(tuned.best_schedule);
     res.executable = std::shared_ptr<Executable>(backend.compile(cgm).release());
     if (res.executable) cache_.insert(cache_key, res.executable);
     return res;

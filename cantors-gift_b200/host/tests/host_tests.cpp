@@ -16,6 +16,8 @@ extern "C" {   // the CPU oracle (test infrastructure)
 int cgo_eltwise(const cg_b200_eltwise_desc* d, const void* const* inputs, int n_inputs, void* out, size_t n);
 int cgo_gemm(const cg_b200_gemm_desc* d, const void* A, const void* B, const void* bias, const void* residual, void* C,
              const int64_t* rows, int64_t n_rows, int acc64);
+void cgo_f32_to_bf16(const float* in, uint16_t* out, size_t n);
+void cgo_bf16_to_f32(const uint16_t* in, float* out, size_t n);
 int cgo_softmax_layernorm(int dt, const void* in, const void* gamma, const void* beta, float eps, void* out,
                           int64_t rows, int64_t cols);
 }
@@ -239,9 +241,74 @@ static void test_backend_and_cache() {
     CHECK(k && k->name() == "cg_b200_layernorm");
 }
 
+// ---- schedules and the autotuner's interface (no GPU: the benchmark function is a table) ------------------
+static void test_autotune_host_logic() {
+    const ScheduleSpace space = ScheduleSpace::grid_matmul({128, 256}, {64, 128, 256}, {64}, {8});
+    CHECK(space.size() == 6);
+    CHECK(space.schedules()[0].transforms().size() == 8);   // as src/schedule/schedule.cpp:74-82 builds them
+    CHECK(space.schedules()[0] == space.schedules()[0] && !(space.schedules()[0] == space.schedules()[1]));
+    CHECK(space.schedules()[0].hash() != space.schedules()[1].hash());
+    // tiles -> kernel variant
+    auto t0 = gemm_tuning_from_schedule(space.schedules()[0]);   // m 128, n 64
+    CHECK(t0 && t0->cta_pair == 1 && t0->tile_n == 64 && t0->tail_split == 0);
+    auto t5 = gemm_tuning_from_schedule(space.schedules()[5]);   // m 256, n 256
+    CHECK(t5 && t5->cta_pair == 2 && t5->tile_n == 256);
+    CHECK(!gemm_tuning_from_schedule(space.schedules()[3]));     // m 256, n 64: no such kernel
+    auto none = gemm_tuning_from_schedule(Schedule{});
+    CHECK(none && none->cta_pair == 0 && none->tile_n == 0);     // empty schedule = the library's heuristic
+    Schedule odd;
+    odd.add({TransformKind::Tile, "n", 96, 0, ""});
+    CHECK(!gemm_tuning_from_schedule(odd));
+    // the search keeps the fastest candidate and skips those that cannot run
+    const double inf = std::numeric_limits<double>::infinity();
+    const double table[6] = {5e-6, 3e-6, 4e-6, inf, 2e-6, 2.5e-6};
+    int calls = 0;
+    BenchmarkFn fake = [&](const Schedule& s) {
+        ++calls;
+        for (usize i = 0; i < space.size(); ++i)
+            if (space.schedules()[i] == s) return table[i];
+        return inf;
+    };
+    const AutotuneResult r = bayesian_autotune(space, fake);
+    CHECK(r.total_benchmarks == 6 && calls == 6 && r.runtime_history.size() == 6);
+    CHECK(r.best_runtime == 2e-6 && r.best_schedule == space.schedules()[4]);
+    CHECK(bayesian_autotune(space, fake, 2).total_benchmarks == 2);
+    // Runtime::autotune_and_cache: the winner's tiles reach the plan record, and the second call is a cache hit
+    const auto dir = std::filesystem::temp_directory_path() / "cg_b200_autotune_cache_test";
+    std::filesystem::remove_all(dir);
+    Runtime rt(dir.string());
+    NvidiaBackend backend;
+    TensorToCodegenLowering low;
+    Module m;
+    Function& f = m.create_function("mm");
+    Builder b(&f);
+    b.output_tensor(b.matmul(b.input_tensor({512, 256}, DType::BF16), b.input_tensor({256, 384}, DType::BF16)));
+    auto lower_best = [&](const Schedule& s) { return low.lower(m, s); };
+    const u64 key = KernelCache::compute_key("mm", "512x384x256", "bf16", "b200-tuned");
+    calls = 0;
+    auto first = rt.autotune_and_cache(key, space, fake, backend, lower_best);
+    CHECK(!first.cache_hit && first.executable && first.total_benchmarks == 6 && first.best_runtime == 2e-6);
+    if (first.executable) {
+        auto plan = LaunchPlan::deserialize(first.executable->machine_code);
+        CHECK(plan && plan->records.size() == 1 && plan->records[0].kind == PlanRecord::Gemm);
+        if (plan && !plan->records.empty()) CHECK(plan->records[0].tuning.cta_pair == 2 && plan->records[0].tuning.tile_n == 128);
+    }
+    auto second = rt.autotune_and_cache(key, space, fake, backend, lower_best);
+    CHECK(second.cache_hit && second.executable && calls == 6);   // no further measurements
+    if (second.executable) {
+        auto plan = LaunchPlan::deserialize(second.executable->machine_code);
+        CHECK(plan && plan->records.size() == 1 && plan->records[0].tuning.tile_n == 128);
+    }
+    // a schedule with a tile the kernels do not have is refused by the lowering
+    CGModule bad = low.lower(m, odd);
+    CHECK(low.status() == CG_B200_ERR_UNSUPPORTED && bad.functions.empty());
+    std::filesystem::remove_all(dir);
+}
+
 static int run_cpu() {
     test_planner();
     test_backend_and_cache();
+    test_autotune_host_logic();
     int count = -1;
     if (cg_b200_device_count(&count) != CG_B200_OK) CHECK(make_cuda_device(0) == nullptr);
     std::printf("host_tests cpu: %d checks, %d failed\n", g_checks, g_failed);
@@ -375,6 +442,72 @@ static int run_gpu() {
             }
             CHECK(err <= 1e-4 * scale);
         }
+    }
+    {   // the autotuner's benchmark function on the real kernel, then the tuned executable against the oracle
+        const i64 M = 1024, N = 768, K = 512;
+        Module m;
+        Function& f = m.create_function("mm_tuned");
+        Builder b(&f);
+        b.output_tensor(b.matmul(b.input_tensor({M, K}, DType::F32), b.input_tensor({K, N}, DType::F32)));
+        Module m16;
+        Function& f16 = m16.create_function("mm16");
+        Builder b16(&f16);
+        b16.output_tensor(b16.matmul(b16.input_tensor({M, K}, DType::BF16), b16.input_tensor({K, N}, DType::BF16)));
+        CGModule cg16 = low.lower(m16);
+        CHECK(low.status() == CG_B200_OK);
+        const PlanRecord rec = record_of(cg16.functions[0].instructions[0]);
+        const ScheduleSpace space = ScheduleSpace::grid_matmul({128, 256}, {64, 128, 256}, {64}, {8});
+        BenchmarkFn bench = make_gemm_benchmark(rec.gemm, *dev, 10, 2);
+        int finite = 0;
+        for (usize i = 0; i < space.size(); ++i) {
+            const double t = bench(space.schedules()[i]);
+            const bool runnable = gemm_tuning_from_schedule(space.schedules()[i]).has_value();
+            CHECK(runnable == std::isfinite(t));
+            if (std::isfinite(t)) {
+                CHECK(t > 1e-7 && t < 1e-2);   // a 0.8 GFLOP GEMM: microseconds
+                ++finite;
+                std::printf("  tile m %lld n %lld: %.2f us\n", (long long)space.schedules()[i].transforms()[0].factor,
+                            (long long)space.schedules()[i].transforms()[1].factor, t * 1e6);
+            }
+        }
+        CHECK(finite == 5);
+        const auto dir = std::filesystem::temp_directory_path() / "cg_b200_autotune_gpu_cache";
+        std::filesystem::remove_all(dir);
+        Runtime rt2(dir.string());
+        rt2.add_device(make_cuda_device(0));
+        auto tuned = rt2.autotune_and_cache(KernelCache::compute_key("mm16", "1024x768x512", "bf16", "b200-tuned"), space, bench,
+                                            backend, [&](const Schedule& s) { return low.lower(m16, s); });
+        CHECK(tuned.executable && !tuned.cache_hit && tuned.total_benchmarks == 6 && std::isfinite(tuned.best_runtime));
+        auto bound = rt2.bind(tuned.executable, DeviceId::cuda(0));
+        CHECK(bound != nullptr);
+        if (bound) {
+            // bf16 operands as raw 16-bit words; the oracle multiplies the same words
+            std::vector<float> af = randn(M * K, 21), bf = randn(K * N, 22);
+            std::vector<uint16_t> a16(M * K), b16w(K * N), y16(M * N), want16(M * N);
+            cgo_f32_to_bf16(af.data(), a16.data(), M * K);
+            cgo_f32_to_bf16(bf.data(), b16w.data(), K * N);
+            DevTensor da(dev, {M, K}, DType::BF16), db(dev, {K, N}, DType::BF16), dy(dev, {M, N}, DType::BF16);
+            copy_to_device(da.t, a16.data(), da.t.num_bytes, *stream);
+            copy_to_device(db.t, b16w.data(), db.t.num_bytes, *stream);
+            std::vector<Tensor*> in = {&da.t, &db.t}, out = {&dy.t};
+            bound->launch(Span<Tensor*>(in), Span<Tensor*>(out), *stream);
+            CHECK(bound->status() == CG_B200_OK);
+            copy_to_host(y16.data(), dy.t, dy.t.num_bytes, *stream);
+            stream->sync();
+            cgo_gemm(&rec.gemm, a16.data(), b16w.data(), nullptr, nullptr, want16.data(), nullptr, 0, 0);
+            std::vector<float> y(M * N), want(M * N);
+            cgo_bf16_to_f32(y16.data(), y.data(), M * N);
+            cgo_bf16_to_f32(want16.data(), want.data(), M * N);
+            double err = 0, scale = 0;
+            for (usize i = 0; i < y.size(); ++i) {
+                err = std::fmax(err, std::fabs(static_cast<double>(y[i]) - want[i]));
+                scale = std::fmax(scale, std::fabs(static_cast<double>(want[i])));
+            }
+            std::printf("tuned bf16 gemm max-normalised error %.3e\n", err / scale);
+            CHECK(err <= 1e-2 * scale);   // the path's 16-bit bound
+        }
+        std::filesystem::remove_all(dir);
+        (void)m;
     }
     {   // a vendor kernel that really executes
         VendorDispatcher& vd = VendorDispatcher::instance();
