@@ -282,7 +282,9 @@ static void test_autotune_host_logic() {
     Module m;
     Function& f = m.create_function("mm");
     Builder b(&f);
-    b.output_tensor(b.matmul(b.input_tensor({512, 256}, DType::BF16), b.input_tensor({256, 384}, DType::BF16)));
+    const Value a_in = b.input_tensor({512, 256}, DType::BF16);
+    const Value b_in = b.input_tensor({256, 384}, DType::BF16);
+    b.output_tensor(b.matmul(a_in, b_in));
     auto lower_best = [&](const Schedule& s) { return low.lower(m, s); };
     const u64 key = KernelCache::compute_key("mm", "512x384x256", "bf16", "b200-tuned");
     calls = 0;
@@ -445,14 +447,12 @@ static int run_gpu() {
     }
     {   // the autotuner's benchmark function on the real kernel, then the tuned executable against the oracle
         const i64 M = 1024, N = 768, K = 512;
-        Module m;
-        Function& f = m.create_function("mm_tuned");
-        Builder b(&f);
-        b.output_tensor(b.matmul(b.input_tensor({M, K}, DType::F32), b.input_tensor({K, N}, DType::F32)));
         Module m16;
         Function& f16 = m16.create_function("mm16");
         Builder b16(&f16);
-        b16.output_tensor(b16.matmul(b16.input_tensor({M, K}, DType::BF16), b16.input_tensor({K, N}, DType::BF16)));
+        const Value a_in = b16.input_tensor({M, K}, DType::BF16);   // separate statements: argument evaluation
+        const Value b_in = b16.input_tensor({K, N}, DType::BF16);   // order would otherwise pick the input order
+        b16.output_tensor(b16.matmul(a_in, b_in));
         CGModule cg16 = low.lower(m16);
         CHECK(low.status() == CG_B200_OK);
         const PlanRecord rec = record_of(cg16.functions[0].instructions[0]);
@@ -491,6 +491,7 @@ static int run_gpu() {
             copy_to_device(db.t, b16w.data(), db.t.num_bytes, *stream);
             std::vector<Tensor*> in = {&da.t, &db.t}, out = {&dy.t};
             bound->launch(Span<Tensor*>(in), Span<Tensor*>(out), *stream);
+            if (bound->status() != CG_B200_OK) std::printf("tuned launch status %d (%s)\n", bound->status(), cg_b200_status_string(bound->status()));
             CHECK(bound->status() == CG_B200_OK);
             copy_to_host(y16.data(), dy.t, dy.t.num_bytes, *stream);
             stream->sync();
@@ -507,7 +508,6 @@ static int run_gpu() {
             CHECK(err <= 1e-2 * scale);   // the path's 16-bit bound
         }
         std::filesystem::remove_all(dir);
-        (void)m;
     }
     {   // a vendor kernel that really executes
         VendorDispatcher& vd = VendorDispatcher::instance();
