@@ -156,13 +156,29 @@ class EltwiseWorkload(Workload):
     def e2e_step(self):
         import ctypes as C
         from cantors_gift_b200 import capi
+        # ranges of the arrays are independent: eight of them in flight on three streams
         r = self.runner
-        d = [r.h2d(f"in{k}", h) for k, h in enumerate(self.h_in)]
+        L = capi.lib()
+        d = [r.dev(f"in{k}", 4 * self.n) for k in range(3)]
         o = r.dev("out", 4 * self.n)
-        arr = (C.c_void_p * 3)(*[p.value for p in d])
-        capi.check(capi.lib().cg_b200_eltwise(C.byref(self.desc), arr, 3, o, self.n, r.stream), "eltwise")
-        r.d2h(self.h_out, o)
-        r.sync()
+        slabs = 8
+        per = self.n // slabs
+        assert per * slabs == self.n and (per * 4) % 16 == 0
+        nb = 4 * per
+        hin, hout = [h.data_ptr() for h in self.h_in], self.h_out.data_ptr()
+
+        def copy_in(i, s):
+            for k in range(3):
+                capi.check(L.cg_b200_memcpy_h2d(C.c_void_p(d[k].value + i * nb), C.c_void_p(hin[k] + i * nb), nb, s), "h2d")
+
+        def compute(i, s):
+            arr = (C.c_void_p * 3)(*[p.value + i * nb for p in d])
+            capi.check(L.cg_b200_eltwise(C.byref(self.desc), arr, 3, C.c_void_p(o.value + i * nb), per, s), "eltwise")
+
+        def copy_out(i, s):
+            capi.check(L.cg_b200_memcpy_d2h(C.c_void_p(hout + i * nb), C.c_void_p(o.value + i * nb), nb, s), "d2h")
+
+        r.run_slabs(slabs, copy_in, compute, copy_out)
 
     def cpu_baseline(self, budget_s, prefer_ref=True):
         from oracle import oracle as O
@@ -225,15 +241,30 @@ class RowReduceWorkload(Workload):
         return nb, nb
 
     def e2e_step(self):
+        # rows are independent: eight row blocks in flight on three streams
+        import ctypes as C
         from cantors_gift_b200 import capi
         r = self.runner
-        nb = 2 * self.rows * self.cols
-        d = r.h2d("x", self.h_x)
-        o = r.dev("y", nb)
-        capi.check(capi.lib().cg_b200_softmax_layernorm(capi.BF16, d, None, None, 1e-5, o, self.rows, self.cols,
-                                                        r.stream), "softmax_layernorm")
-        r.d2h(self.h_y, o)
-        r.sync()
+        L = capi.lib()
+        total = 2 * self.rows * self.cols
+        d, o = r.dev("x", total), r.dev("y", total)
+        slabs = 8
+        per = self.rows // slabs
+        assert per * slabs == self.rows
+        nb = 2 * per * self.cols
+        hx, hy = self.h_x.data_ptr(), self.h_y.data_ptr()
+
+        def copy_in(i, s):
+            capi.check(L.cg_b200_memcpy_h2d(C.c_void_p(d.value + i * nb), C.c_void_p(hx + i * nb), nb, s), "h2d")
+
+        def compute(i, s):
+            capi.check(L.cg_b200_softmax_layernorm(capi.BF16, C.c_void_p(d.value + i * nb), None, None, 1e-5,
+                                                   C.c_void_p(o.value + i * nb), per, self.cols, s), "softmax_layernorm")
+
+        def copy_out(i, s):
+            capi.check(L.cg_b200_memcpy_d2h(C.c_void_p(hy + i * nb), C.c_void_p(o.value + i * nb), nb, s), "d2h")
+
+        r.run_slabs(slabs, copy_in, compute, copy_out)
 
     def cpu_baseline(self, budget_s, prefer_ref=True):
         from oracle import oracle as O
@@ -358,16 +389,40 @@ class GemmWorkload(Workload):
         return (self.h_A.numel() + self.h_B.numel() + self.h_bias.numel()) * es, self.h_C.numel() * es
 
     def e2e_step(self):
+        # B and the bias go first; then row slabs of A are copied, multiplied and copied back on three
+        # streams, so the step costs about the host-to-device time of A and B, not the sum of the copies
+        # and the kernel (HostRunner.run_slabs).
         import ctypes as C
         from cantors_gift_b200 import capi
         r = self.runner
-        a, b, bias = r.h2d("A", self.h_A), r.h2d("B", self.h_B), r.h2d("bias", self.h_bias)
-        c = r.dev("C", self.h_C.numel() * self.h_C.element_size())
+        L = capi.lib()
+        es_in, es_out = self.h_A.element_size(), self.h_C.element_size()
+        b, bias = r.h2d("B", self.h_B), r.h2d("bias", self.h_bias)
+        a = r.dev("A", self.h_A.numel() * es_in)
+        c = r.dev("C", self.h_C.numel() * es_out)
         ws = r.dev("ws", self.ws_bytes) if self.ws_bytes else None
-        capi.check(capi.lib().cg_b200_gemm(C.byref(self.desc), a, b, bias if self.epilogue != "none" else None, None,
-                                           c, ws, self.ws_bytes, r.stream), "gemm")
-        r.d2h(self.h_C, c)
-        r.sync()
+        slabs = 1 if self.ws_bytes else max(1, min(8, self.Ms // 512))   # the fp32 path would split B once per slab
+        rows = self.Ms // slabs
+        assert rows * slabs == self.Ms
+        if getattr(self, "_slab_desc_rows", None) != rows:
+            self._slab_desc = capi.make_gemm_desc(rows, self.N, self.K, self.desc.in_dtype, self.desc.out_dtype,
+                                                  epilogue=self.epilogue)
+            self._slab_desc_rows = rows
+        a_bytes, c_bytes = rows * self.K * es_in, rows * self.N * es_out
+        hA, hC = self.h_A.data_ptr(), self.h_C.data_ptr()
+
+        def copy_in(i, s):
+            capi.check(L.cg_b200_memcpy_h2d(C.c_void_p(a.value + i * a_bytes), C.c_void_p(hA + i * a_bytes), a_bytes, s), "h2d")
+
+        def compute(i, s):
+            capi.check(L.cg_b200_gemm(C.byref(self._slab_desc), C.c_void_p(a.value + i * a_bytes), b,
+                                      bias if self.epilogue != "none" else None, None, C.c_void_p(c.value + i * c_bytes),
+                                      ws, self.ws_bytes, s), "gemm")
+
+        def copy_out(i, s):
+            capi.check(L.cg_b200_memcpy_d2h(C.c_void_p(hC + i * c_bytes), C.c_void_p(c.value + i * c_bytes), c_bytes, s), "d2h")
+
+        r.run_slabs(slabs, copy_in, compute, copy_out)
 
     def cpu_baseline(self, budget_s, prefer_ref=True):
         from oracle import oracle as O
@@ -472,23 +527,34 @@ class BlockWorkload(Workload):
         self.d_x = torch.empty_like(self.x)
         self.d_y = torch.empty_like(self.x)
 
-        class _R:   # same close() protocol as HostRunner
-            def close(self_inner):
-                pass
-        self.runner = _R()
+        from cantors_gift_b200 import ops
+        self.runner = ops.HostRunner()
         return self.h_x.numel() * 2, self.h_y.numel() * 2
 
     def e2e_step(self):
+        # sequences are independent: slabs of the batch are copied in, run and copied out on three streams
         import ctypes as C
         import torch
         from cantors_gift_b200 import capi
         L = capi.lib()
-        st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-        nb = self.h_x.numel() * 2
-        capi.check(L.cg_b200_memcpy_h2d(C.c_void_p(self.d_x.data_ptr()), C.c_void_p(self.h_x.data_ptr()), nb, st), "h2d")
-        self.block.forward(self.d_x, out=self.d_y)
-        capi.check(L.cg_b200_memcpy_d2h(C.c_void_p(self.h_y.data_ptr()), C.c_void_p(self.d_y.data_ptr()), nb, st), "d2h")
-        capi.check(L.cg_b200_stream_sync(st), "sync")
+        Bl = self.h_x.shape[0]
+        slabs = max(1, min(8, Bl))
+        per = Bl // slabs
+        assert per * slabs == Bl
+        nb = per * self.S * self.D * 2
+        dx, dy, hx, hy = self.d_x.data_ptr(), self.d_y.data_ptr(), self.h_x.data_ptr(), self.h_y.data_ptr()
+
+        def copy_in(i, s):
+            capi.check(L.cg_b200_memcpy_h2d(C.c_void_p(dx + i * nb), C.c_void_p(hx + i * nb), nb, s), "h2d")
+
+        def compute(i, s):
+            self.block.forward(self.d_x[i * per:(i + 1) * per], out=self.d_y[i * per:(i + 1) * per],
+                               stream=torch.cuda.ExternalStream(s.value))
+
+        def copy_out(i, s):
+            capi.check(L.cg_b200_memcpy_d2h(C.c_void_p(hy + i * nb), C.c_void_p(dy + i * nb), nb, s), "d2h")
+
+        self.runner.run_slabs(slabs, copy_in, compute, copy_out)
 
     def cpu_baseline(self, budget_s, prefer_ref=True):
         from oracle import oracle as O

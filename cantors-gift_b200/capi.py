@@ -103,6 +103,7 @@ SIGNATURES = {
     "cg_b200_event_destroy": (_i, [_vp]),
     "cg_b200_event_record": (_i, [_vp, _vp]),
     "cg_b200_event_sync": (_i, [_vp]),
+    "cg_b200_stream_wait_event": (_i, [_vp, _vp]),
     "cg_b200_event_elapsed_sec": (_i, [_vp, _vp, C.POINTER(C.c_double)]),
     "cg_b200_eltwise_validate": (_i, [C.POINTER(EltwiseDesc), _i]),
     "cg_b200_eltwise": (_i, [C.POINTER(EltwiseDesc), _vpp, _i, _vp, _sz, _vp]),

@@ -229,6 +229,12 @@ int cg_b200_event_sync(void* event) {
     return CG_B200_OK;
 }
 
+int cg_b200_stream_wait_event(void* stream, void* event) {
+    if (!event) return CG_B200_ERR_NULL_POINTER;
+    CGB_CUDA(cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)event, 0));
+    return CG_B200_OK;
+}
+
 int cg_b200_event_elapsed_sec(void* earlier, void* later, double* seconds) {
     if (!earlier || !later || !seconds) return CG_B200_ERR_NULL_POINTER;
     float ms = 0.f;

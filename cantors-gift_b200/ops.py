@@ -142,10 +142,56 @@ class HostRunner:
     def sync(self):
         check(lib().cg_b200_stream_sync(self.stream), "stream_sync")
 
+    # ---- slab pipeline: copy in, compute, copy out on three streams ------------------------------
+    # PCIe moves data in both directions at once and the copy engines run beside the SMs, so a step
+    # whose input splits into independent slabs (row blocks of A, sequences of a batch, ranges of an
+    # elementwise array) costs about max(copy in, compute, copy out) instead of their sum.
+    def _pipeline_streams(self):
+        if not hasattr(self, "_s_compute"):
+            self._s_compute, self._s_out = C.c_void_p(), C.c_void_p()
+            check(lib().cg_b200_stream_create(C.byref(self._s_compute)), "stream_create")
+            check(lib().cg_b200_stream_create(C.byref(self._s_out)), "stream_create")
+            self._events = []
+        return self._s_compute, self._s_out
+
+    def _event(self, i):
+        while len(self._events) <= i:
+            e = C.c_void_p()
+            check(lib().cg_b200_event_create(C.byref(e)), "event_create")
+            self._events.append(e)
+        return self._events[i]
+
+    def run_slabs(self, n_slabs, copy_in, compute, copy_out):
+        """copy_in(i, stream), compute(i, stream), copy_out(i, stream) enqueue slab i's work on the
+        stream they are given; anything all slabs share (weights, B) is copied on self.stream by the
+        caller before this. Returns after everything has finished."""
+        s_in = self.stream
+        s_compute, s_out = self._pipeline_streams()
+        for i in range(n_slabs):
+            copy_in(i, s_in)
+            ev_in = self._event(2 * i)
+            check(lib().cg_b200_event_record(ev_in, s_in), "event_record")
+            check(lib().cg_b200_stream_wait_event(s_compute, ev_in), "stream_wait_event")
+            compute(i, s_compute)
+            ev_done = self._event(2 * i + 1)
+            check(lib().cg_b200_event_record(ev_done, s_compute), "event_record")
+            check(lib().cg_b200_stream_wait_event(s_out, ev_done), "stream_wait_event")
+            copy_out(i, s_out)
+        check(lib().cg_b200_stream_sync(s_out), "stream_sync")
+        check(lib().cg_b200_stream_sync(s_compute), "stream_sync")
+        check(lib().cg_b200_stream_sync(s_in), "stream_sync")
+
     def close(self):
         for p, _ in self._dev.values():
             lib().cg_b200_free(p)
         self._dev = {}
+        for e in getattr(self, "_events", []):
+            lib().cg_b200_event_destroy(e)
+        self._events = []
+        for name in ("_s_compute", "_s_out"):
+            if hasattr(self, name):
+                lib().cg_b200_stream_destroy(getattr(self, name))
+                delattr(self, name)
         if self.stream:
             lib().cg_b200_stream_destroy(self.stream)
             self.stream = C.c_void_p()

@@ -99,6 +99,10 @@ int cg_b200_event_create(void** event);
 int cg_b200_event_destroy(void* event);
 int cg_b200_event_record(void* event, void* stream);
 int cg_b200_event_sync(void* event);
+/* Work submitted to `stream` after this call starts only when `event` has completed; the host does
+ * not block. With it a caller overlaps the copy of one slab with the kernel on the previous one
+ * (Event::wait, runtime.hpp:61, blocks the host and is cg_b200_event_sync above). */
+int cg_b200_stream_wait_event(void* stream, void* event);
 /* Seconds between two recorded events (Event::elapsed_sec_since, runtime.hpp:62). */
 int cg_b200_event_elapsed_sec(void* earlier, void* later, double* seconds);
 
