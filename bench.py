@@ -401,7 +401,14 @@ class GemmWorkload(Workload):
         a = r.dev("A", self.h_A.numel() * es_in)
         c = r.dev("C", self.h_C.numel() * es_out)
         ws = r.dev("ws", self.ws_bytes) if self.ws_bytes else None
-        slabs = 1 if self.ws_bytes else max(1, min(8, self.Ms // 512))   # the fp32 path would split B once per slab
+        if self.ws_bytes:   # fp32: the operand split would run once per slab; one GEMM on one stream
+            a = r.h2d("A", self.h_A)
+            capi.check(L.cg_b200_gemm(C.byref(self.desc), a, b, bias if self.epilogue != "none" else None, None, c, ws,
+                                      self.ws_bytes, r.stream), "gemm")
+            r.d2h(self.h_C, c)
+            r.sync()
+            return
+        slabs = max(1, min(4, self.Ms // 512))
         rows = self.Ms // slabs
         assert rows * slabs == self.Ms
         if getattr(self, "_slab_desc_rows", None) != rows:
