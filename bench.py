@@ -486,7 +486,7 @@ class BlockWorkload(Workload):
         return {"workload": "cfg5: pre-LN transformer encoder block, bf16, batch 32, seq 2048, d_model 1024, 16 heads, "
                             "FFN 4096, GELU(tanh), weights ~N(0,0.02)",
                 "l2": "activations (over 6 GiB per step) larger than L2",
-                "parallelism": "1 GPU" if world == 1 else f"batch-sharded x{world}, in-place NCCL all-gather of y"}
+                "parallelism": "1 GPU" if world == 1 else f"batch-sharded x{world}, y gathered by the last GEMM's peer stores"}
 
     def setup(self, rank, world):
         import torch
@@ -503,13 +503,31 @@ class BlockWorkload(Workload):
         x = torch.randn(self.B, self.S, D, device="cuda", generator=g2).to(torch.bfloat16)
         self.x = x[rank * self.Bs:(rank + 1) * self.Bs].contiguous()
         self.y = torch.empty(self.B, self.S, D, device="cuda", dtype=torch.bfloat16)
-        self.comm = make_comm(rank, world) if world > 1 else None
+        self.comm, self.gather = None, None
         self.launches_per_step = self.block.launches_per_forward
+        if world > 1 and os.environ.get("CG_B200_BENCH_ALLGATHER", "fused") == "nccl":
+            self.comm = make_comm(rank, world)
+        elif world > 1:
+            # y lives in a buffer every rank maps; the block's last GEMM stores its rows into all of them
+            import ctypes as C
+            from cantors_gift_b200 import capi
+            raw, tables = share_buffers(rank, world, 1, self.B * self.S * D * 2)
+            _, flag_tables = share_buffers(rank, world, 1, 256)
+            self.barrier = C.c_void_p()
+            capi.check(capi.lib().cg_b200_peer_barrier_create(C.byref(self.barrier), flag_tables[0], world, rank),
+                       "peer_barrier_create")
+            self.gather = (raw[0], tables[0], world, rank)
+            self.launches_per_step += 1   # the flag barrier
 
     def step(self, i):
         import ctypes as C
         import torch
         from cantors_gift_b200 import capi
+        if self.gather is not None:
+            self.block.forward(self.x, gather=self.gather)
+            capi.check(capi.lib().cg_b200_peer_barrier(self.barrier, C.c_void_p(torch.cuda.current_stream().cuda_stream)),
+                       "peer_barrier")
+            return
         ys = self.y[self.rank * self.Bs:(self.rank + 1) * self.Bs]
         self.block.forward(self.x, out=ys)
         if self.comm is not None:

@@ -49,8 +49,14 @@ class EncoderBlock:
         (src/analysis/arithmetic_intensity.cpp:73-89)."""
         return 2.0 * B * S * (3 * D * D + D * D + 2 * D * F) + 2.0 * 2 * B * H * S * S * (D // H)
 
-    def forward(self, x, out=None, stream=None):
-        """x: [B, S, D] contiguous CUDA tensor. Returns y of the same shape."""
+    def forward(self, x, out=None, stream=None, gather=None):
+        """x: [B, S, D] contiguous CUDA tensor. Returns y of the same shape.
+
+        gather: for a batch-sharded block, (y_full_ptr, peer_table, world, rank): the last GEMM then
+        writes this rank's rows of y into the full-size y of every rank (its own at y_full_ptr, the
+        peers' through the `world` pointers of peer_table, mapped with cg_b200_ipc_open) as its tiles
+        are produced, instead of an all-gather after the block. `out` is ignored; the caller runs one
+        cg_b200_peer_barrier before y is read."""
         B, S, D = x.shape
         H, dh, F, dt = self.H, self.dh, self.F, self.dt
         dev = x.device
@@ -66,7 +72,7 @@ class EncoderBlock:
         h = self._buf("h", (rows, D), dev)
         ln2 = self._buf("ln2", (rows, D), dev)
         ff = self._buf("ff", (rows, F), dev)
-        y = torch.empty_like(x) if out is None else out
+        y = None if gather is not None else (torch.empty_like(x) if out is None else out)
 
         def gemm(desc, a, b, c, bias=None, res=None, a_off=0, b_off=0):
             es = a.element_size()
@@ -89,9 +95,14 @@ class EncoderBlock:
         gemm(capi.make_gemm_desc(rows, D, D, dt, dt, epilogue="residual"), ctx, self.w_o, h, res=x2)
         check(L.cg_b200_layernorm(dt, p(h), None, None, self.eps, p(ln2), rows, D, st), "layernorm")
         gemm(capi.make_gemm_desc(rows, F, D, dt, dt, epilogue="bias_gelu_tanh"), ln2, self.w_1, ff, bias=self.b_1)
-        gemm(capi.make_gemm_desc(rows, D, F, dt, dt, epilogue="bias_residual"), ff, self.w_2, y.view(rows, D),
-             bias=self.b_2, res=h)
-        return y
+        d_out = capi.make_gemm_desc(rows, D, F, dt, dt, epilogue="bias_residual")
+        if gather is None:
+            gemm(d_out, ff, self.w_2, y.view(rows, D), bias=self.b_2, res=h)
+            return y
+        y_full, table, world, rank = gather
+        check(L.cg_b200_gemm_allgather(C.byref(d_out), p(ff), p(self.w_2), p(self.b_2), p(h), y_full, table, world, rank,
+                                       None, 0, st), "gemm_allgather")
+        return None
 
     def _unfused_attention(self, qkv, scores, ctx, B, S, gemm, p, st):
         D, H, dh, dt = self.D, self.H, self.dh, self.dt
