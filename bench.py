@@ -341,7 +341,7 @@ class GemmWorkload(Workload):
             self.barrier = C.c_void_p()
             capi.check(capi.lib().cg_b200_peer_barrier_create(C.byref(self.barrier), flag_tables[0], world, rank),
                        "peer_barrier_create")
-        self.launches_per_step = 1 if self.in_dtype_name == "BF16" else 3
+        self.launches_per_step = 1 if self.in_dtype_name == "BF16" else 2
 
     def step(self, i):
         import ctypes as C

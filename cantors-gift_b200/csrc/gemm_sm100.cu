@@ -513,47 +513,97 @@ __device__ __forceinline__ void tf32_split(float x, float& h, float& l) {
     l = __uint_as_float(__float_as_uint(x - h) & 0xffffe000u);
 }
 
-__global__ void __launch_bounds__(256)
-tf32_split_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo, long long rows,
-                  long long cols, long long ld_src, long long ld_dst, long long batch, long long bs_src,
-                  long long bs_dst) {
-    const long long per = rows * ld_dst;
-    const long long total = per * batch;
-    const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+// Both operands in ONE launch (the whole fp32 GEMM of 1024^3 takes 40 us, a launch a tenth of that):
+// blocks [0, a_blocks) split A row-wise; the others handle B, row-wise when it is stored [N, K], through
+// 32 x 32 shared-memory tiles when it is [K, N] and has to be transposed. The GEMM behind it is
+// launched as a programmatic dependent, so its CTAs may set up while this grid drains.
+struct SplitOperand {
+    const float* src;
+    float *hi, *lo;
+    long long rows, cols, ld_src, ld_dst, batch, bs_src, bs_dst;
+};
+
+__device__ __forceinline__ void tf32_split_rows(const SplitOperand& o, long long first, long long stride) {
+    // four columns per thread where rows, batches and bases are 16-byte tiled (ld_dst always is)
+    const bool vec = ((o.ld_src | o.bs_src | o.bs_dst | o.ld_dst) & 3) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(o.src) | reinterpret_cast<uintptr_t>(o.hi) |
+                       reinterpret_cast<uintptr_t>(o.lo)) & 15) == 0;
+    if (vec) {
+        const long long q = o.ld_dst >> 2;
+        const long long per = o.rows * q;
+        const long long total = per * o.batch;
+        for (long long i = first; i < total; i += stride) {
+            const long long b = i / per;
+            const long long r = (i - b * per) / q;
+            const long long c = (i - b * per - r * q) << 2;
+            const float* sp = o.src + b * o.bs_src + r * o.ld_src + c;
+            float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (c + 3 < o.cols) {
+                x = *reinterpret_cast<const float4*>(sp);
+            } else {   // the last, partly padded group of a row
+                if (c < o.cols) x.x = sp[0];
+                if (c + 1 < o.cols) x.y = sp[1];
+                if (c + 2 < o.cols) x.z = sp[2];
+            }
+            float4 h, l;
+            tf32_split(x.x, h.x, l.x);
+            tf32_split(x.y, h.y, l.y);
+            tf32_split(x.z, h.z, l.z);
+            tf32_split(x.w, h.w, l.w);
+            const long long d = b * o.bs_dst + r * o.ld_dst + c;
+            *reinterpret_cast<float4*>(o.hi + d) = h;
+            if (o.lo) *reinterpret_cast<float4*>(o.lo + d) = l;
+        }
+        return;
+    }
+    const long long per = o.rows * o.ld_dst;
+    const long long total = per * o.batch;
+    for (long long i = first; i < total; i += stride) {
         const long long b = i / per;
-        const long long r = (i - b * per) / ld_dst;
-        const long long c = i - b * per - r * ld_dst;
+        const long long r = (i - b * per) / o.ld_dst;
+        const long long c = i - b * per - r * o.ld_dst;
         float x = 0.0f;
-        if (c < cols) x = src[b * bs_src + r * ld_src + c];
+        if (c < o.cols) x = o.src[b * o.bs_src + r * o.ld_src + c];
         float h, l;
         tf32_split(x, h, l);
-        hi[b * bs_dst + r * ld_dst + c] = h;
-        if (lo) lo[b * bs_dst + r * ld_dst + c] = l;
+        o.hi[b * o.bs_dst + r * o.ld_dst + c] = h;
+        if (o.lo) o.lo[b * o.bs_dst + r * o.ld_dst + c] = l;
     }
 }
 
-// Same, transposing: src is [rows, cols] (row stride ld_src), dst is [cols, ld_dst] with ld_dst >= rows.
-// 32 x 32 tiles through shared memory; grid = (ceil(cols/32), ceil(ld_dst/32), batch), block = (32, 8).
+// `bo` describes B as stored: [rows = K, cols = N]; the destination is [N, ld_dst >= K].
 __global__ void __launch_bounds__(256)
-tf32_split_transpose_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo,
-                            long long rows, long long cols, long long ld_src, long long ld_dst, long long bs_src,
-                            long long bs_dst) {
+tf32_split_operands_kernel(const SplitOperand ao, const SplitOperand bo, int a_blocks, int b_transpose, int tiles_x,
+                           int tiles_y) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __shared__ float tile[32][33];
-    const long long b = blockIdx.z;
-    const long long c0 = (long long)blockIdx.x * 32, r0 = (long long)blockIdx.y * 32;
-    for (int j = threadIdx.y; j < 32; j += 8) {
-        const long long r = r0 + j, c = c0 + threadIdx.x;
-        tile[j][threadIdx.x] = (r < rows && c < cols) ? src[b * bs_src + r * ld_src + c] : 0.0f;
+    if ((int)blockIdx.x < a_blocks) {
+        tf32_split_rows(ao, (long long)blockIdx.x * 256 + threadIdx.x, (long long)a_blocks * 256);
+        return;
+    }
+    const long long blk = (long long)blockIdx.x - a_blocks;
+    if (!b_transpose) {
+        const long long b_blocks = (long long)gridDim.x - a_blocks;
+        tf32_split_rows(bo, blk * 256 + threadIdx.x, b_blocks * 256);
+        return;
+    }
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const long long per_batch = (long long)tiles_x * tiles_y;
+    const long long b = blk / per_batch;
+    const long long t = blk - b * per_batch;
+    const long long c0 = (t % tiles_x) * 32, r0 = (t / tiles_x) * 32;
+    for (int j = ty; j < 32; j += 8) {
+        const long long r = r0 + j, c = c0 + tx;
+        tile[j][tx] = (r < bo.rows && c < bo.cols) ? bo.src[b * bo.bs_src + r * bo.ld_src + c] : 0.0f;
     }
     __syncthreads();
-    for (int j = threadIdx.y; j < 32; j += 8) {
-        const long long c = c0 + j, r = r0 + threadIdx.x;   // dst row = source column
-        if (c < cols && r < ld_dst) {
+    for (int j = ty; j < 32; j += 8) {
+        const long long c = c0 + j, r = r0 + tx;   // destination row = source column
+        if (c < bo.cols && r < bo.ld_dst) {
             float h, l;
-            tf32_split(tile[threadIdx.x][j], h, l);
-            hi[b * bs_dst + c * ld_dst + r] = h;
-            if (lo) lo[b * bs_dst + c * ld_dst + r] = l;
+            tf32_split(tile[tx][j], h, l);
+            bo.hi[b * bo.bs_dst + c * bo.ld_dst + r] = h;
+            if (bo.lo) bo.lo[b * bo.bs_dst + c * bo.ld_dst + r] = l;
         }
     }
 }
@@ -730,7 +780,7 @@ static int launch_bn(int bn, const CUtensorMap& ta, const CUtensorMap& ta_lo, co
         if (bn == 128) return launch_variant<2, kTF32, kSplit, 128, OutT>(ta, ta_lo, tb, tb_lo, p, s);
         return launch_variant<2, kTF32, kSplit, 256, OutT>(ta, ta_lo, tb, tb_lo, p, s);
     } else if constexpr (kSplit) {
-        (void)bn;
+        if (bn == 64) return launch_variant<1, kTF32, true, 64, OutT>(ta, ta_lo, tb, tb_lo, p, s);
         return launch_variant<1, kTF32, true, 128, OutT>(ta, ta_lo, tb, tb_lo, p, s);
     } else {
         if (bn == 64) return launch_variant<1, kTF32, false, 64, OutT>(ta, ta_lo, tb, tb_lo, p, s);
@@ -749,7 +799,11 @@ static bool pair_enabled() {
 }
 
 static int choose_bn(const cg_b200_gemm_desc* d, bool split) {
-    if (split) return 128;
+    if (split) {
+        // 3xTF32: 128 x 128 tiles, or 128 x 64 when the wider tiles would leave half of the SMs idle
+        const long long tiles = ((d->M + kBM - 1) / kBM) * ((d->N + 127) / 128) * d->batch;
+        return (d->N <= 64 || 2 * tiles <= sm_count()) ? 64 : 128;
+    }
     if (d->N <= 64) return 64;
     if (d->N <= 128) return 128;
     return 256;
@@ -872,7 +926,7 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
         if (t.cta_pair != 0) cta = t.cta_pair;
         else if (t.tile_n == 64) cta = 1;                                     // a 64-wide tile exists for one CTA only
         if (t.tile_n != 0) {
-            if (split && t.tile_n != 128) return CG_B200_ERR_UNSUPPORTED;     // the 3xTF32 kernel has one tile
+            if (split && t.tile_n == 256) return CG_B200_ERR_UNSUPPORTED;     // the 3xTF32 kernel: 64 or 128 wide
             bn = t.tile_n;
         } else if (cta == 2 && bn < 128) {
             bn = 128;
@@ -904,19 +958,27 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
         float* wb_hi = w + sp.copies * sp.a_elems;
         float* wb_lo = sp.copies == 2 ? wb_hi + sp.b_elems : nullptr;
         const long long a_batches = p.a_in ? d.batch : 1, b_batches = p.b_in ? d.batch : 1;
-        const int blocks = sm_count() * 8;
         if (d.K > 0) {
-            tf32_split_kernel<<<blocks, 256, 0, s>>>(static_cast<const float*>(A), wa_hi, wa_lo, d.M, d.K, d.lda,
-                                                     sp.ldk, a_batches, d.batch_stride_a, d.M * sp.ldk);
-            if (d.b_transposed) {
-                tf32_split_kernel<<<blocks, 256, 0, s>>>(static_cast<const float*>(B), wb_hi, wb_lo, d.N, d.K, d.ldb,
-                                                         sp.ldk, b_batches, d.batch_stride_b, d.N * sp.ldk);
-            } else {
-                dim3 grid((unsigned)((d.N + 31) / 32), (unsigned)((sp.ldk + 31) / 32), (unsigned)b_batches);
-                tf32_split_transpose_kernel<<<grid, dim3(32, 8), 0, s>>>(static_cast<const float*>(B), wb_hi, wb_lo,
-                                                                         d.K, d.N, d.ldb, sp.ldk, d.batch_stride_b,
-                                                                         d.N * sp.ldk);
+            const long long row_blocks = (long long)sm_count() * 4;
+            const SplitOperand ao = {static_cast<const float*>(A), wa_hi, wa_lo, d.M, d.K, d.lda, sp.ldk, a_batches,
+                                     d.batch_stride_a, d.M * sp.ldk};
+            SplitOperand bo;
+            long long b_blocks, tiles_x = 0, tiles_y = 0;
+            if (d.b_transposed) {   // [N, K]: same row-wise rewrite as A
+                bo = {static_cast<const float*>(B), wb_hi, wb_lo, d.N, d.K, d.ldb, sp.ldk, b_batches, d.batch_stride_b,
+                      d.N * sp.ldk};
+                b_blocks = row_blocks;
+            } else {                // [K, N]: transposed into [N, ldk]
+                bo = {static_cast<const float*>(B), wb_hi, wb_lo, d.K, d.N, d.ldb, sp.ldk, b_batches, d.batch_stride_b,
+                      d.N * sp.ldk};
+                tiles_x = (d.N + 31) / 32;
+                tiles_y = (sp.ldk + 31) / 32;
+                b_blocks = tiles_x * tiles_y * b_batches;
             }
+            if (row_blocks + b_blocks > 0x7fffffffLL || tiles_x > 0x7fffffffLL || tiles_y > 0x7fffffffLL)
+                return CG_B200_ERR_UNSUPPORTED;
+            tf32_split_operands_kernel<<<(unsigned)(row_blocks + b_blocks), 256, 0, s>>>(
+                ao, bo, (int)row_blocks, d.b_transposed ? 0 : 1, (int)tiles_x, (int)tiles_y);
             CGB_CUDA(cudaGetLastError());
         }
         a_hi = wa_hi; a_lo = wa_lo ? wa_lo : wa_hi; b_hi = wb_hi; b_lo = wb_lo ? wb_lo : wb_hi;

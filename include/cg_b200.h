@@ -254,7 +254,7 @@ int cg_b200_gemm(const cg_b200_gemm_desc* desc, const void* A, const void* B,
  * take such a function and today receive a stub). Every field 0 = library default. Results do not
  * depend on the choice (the K order of the accumulation is the same in every variant).
  * CG_B200_ERR_UNSUPPORTED for a combination no kernel has: CTA pairs with fp32 inputs or with a
- * 64-wide tile, any tile but 128 for the 3xTF32 path. */
+ * 64-wide tile, a 256-wide tile for the 3xTF32 path. */
 typedef struct cg_b200_gemm_tuning {
     int32_t tile_n;      /* 0, 64, 128 or 256 output columns per tile                          */
     int32_t cta_pair;    /* 0 = default, 1 = one CTA per 128-row tile, 2 = CTA pair, 256 rows   */
