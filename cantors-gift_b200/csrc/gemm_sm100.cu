@@ -912,12 +912,9 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
     int bn = choose_bn(desc, split);
     // CTA pairs (256 x 256 tiles) for 16-bit inputs once the problem spans more than one such tile row
     int cta = (!tf32 && bn == 256 && d.M > kBM && pair_enabled()) ? 2 : 1;
-    if (cta == 2) {
-        // too few 256 x 256 tiles to occupy half of the SM pairs (a small shard of a sharded GEMM):
-        // halve the tile width so that twice as many pairs have work
-        const long long tiles = ((d.M + 2 * kBM - 1) / (2 * kBM)) * ((d.N + 255) / 256) * d.batch;
-        if (2 * tiles <= sm_count() / 2) bn = 128;
-    }
+    // (Halving the tile width when few 256 x 256 tiles exist - a small shard of a sharded GEMM - was
+    // measured slower than leaving SM pairs idle: 512 x 4096 x 4096 takes 24.7 us with 32 full tiles and
+    // 27.0 us with 64 half-width ones. The narrower tile stays available through cg_b200_gemm_tuned.)
     p.tail_split = 0;
     if (tuning) {
         // an autotuner's choice replaces the heuristic above; combinations the kernels do not have are refused
@@ -930,8 +927,6 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
             bn = t.tile_n;
         } else if (cta == 2 && bn < 128) {
             bn = 128;
-        } else if (cta == 1 && t.cta_pair == 1) {
-            bn = choose_bn(desc, split);
         }
         if (cta == 2 && bn == 64) return CG_B200_ERR_UNSUPPORTED;             // a pair's tile is 128 or 256 wide
         p.tail_split = t.tail_split;
