@@ -298,7 +298,10 @@ __device__ __forceinline__ float packet_max(const Vec16<T>& v) {
 // FULL: the row is exactly THREADS * CHUNKS packets, so no packet needs a bounds predicate (the
 // predicates and the re-convergence points around them were a seventh of the instructions issued,
 // and this kernel is bound by instruction issue, not by DRAM).
-template <typename T, int THREADS, int CHUNKS, int MIN_CTAS, bool FULL>
+// AFFINE: gamma or beta is given. Without them their code must not exist at all: the compiler turns the
+// "if (gamma)" blocks into predicated instructions, which are issued (and counted) even when the
+// predicate is false - a quarter of this kernel's issue slots.
+template <typename T, int THREADS, int CHUNKS, int MIN_CTAS, bool FULL, bool AFFINE>
 __global__ void __launch_bounds__(THREADS, MIN_CTAS) softmax_layernorm_reg_kernel(const __grid_constant__ RowParams p) {
     constexpr int L = 16 / sizeof(T);
     constexpr int P = L / 2;   // pairs per packet
@@ -390,17 +393,19 @@ __global__ void __launch_bounds__(THREADS, MIN_CTAS) softmax_layernorm_reg_kerne
                 const long long pk = (long long)j * THREADS + threadIdx.x;
 #pragma unroll
                 for (int l = 0; l < P; ++l) x[j][l] = __ffma2_rn(x[j][l], rstd2, shift2);
-                if (gamma) {
-                    float2 g[P];
-                    unpack_pairs<T>(ld_keep(gamma + pk * L), g);
+                if constexpr (AFFINE) {
+                    if (gamma) {
+                        float2 g[P];
+                        unpack_pairs<T>(ld_keep(gamma + pk * L), g);
 #pragma unroll
-                    for (int l = 0; l < P; ++l) x[j][l] = __fmul2_rn(x[j][l], g[l]);
-                }
-                if (beta) {
-                    float2 b[P];
-                    unpack_pairs<T>(ld_keep(beta + pk * L), b);
+                        for (int l = 0; l < P; ++l) x[j][l] = __fmul2_rn(x[j][l], g[l]);
+                    }
+                    if (beta) {
+                        float2 b[P];
+                        unpack_pairs<T>(ld_keep(beta + pk * L), b);
 #pragma unroll
-                    for (int l = 0; l < P; ++l) x[j][l] = __fadd2_rn(x[j][l], b[l]);
+                        for (int l = 0; l < P; ++l) x[j][l] = __fadd2_rn(x[j][l], b[l]);
+                    }
                 }
                 st_stream(out + pk * L, pack_pairs<T>(x[j]));
             }
@@ -476,10 +481,11 @@ static void launch_reg(const RowParams& p, int blocks, cudaStream_t s) {
         const int g = (int)(p.rows < cap ? p.rows : cap);
         (void)blocks;
         constexpr int L = 16 / sizeof(T);
-        if (p.cols / L == (long long)THREADS * CHUNKS)
-            softmax_layernorm_reg_kernel<T, THREADS, CHUNKS, kMinCtas, true><<<g, THREADS, 0, s>>>(p);
-        else
-            softmax_layernorm_reg_kernel<T, THREADS, CHUNKS, kMinCtas, false><<<g, THREADS, 0, s>>>(p);
+        const bool full = p.cols / L == (long long)THREADS * CHUNKS, affine = p.gamma || p.beta;
+        if (full && !affine) softmax_layernorm_reg_kernel<T, THREADS, CHUNKS, kMinCtas, true, false><<<g, THREADS, 0, s>>>(p);
+        else if (full) softmax_layernorm_reg_kernel<T, THREADS, CHUNKS, kMinCtas, true, true><<<g, THREADS, 0, s>>>(p);
+        else if (!affine) softmax_layernorm_reg_kernel<T, THREADS, CHUNKS, kMinCtas, false, false><<<g, THREADS, 0, s>>>(p);
+        else softmax_layernorm_reg_kernel<T, THREADS, CHUNKS, kMinCtas, false, true><<<g, THREADS, 0, s>>>(p);
     }
     else
         row_reg_kernel<T, THREADS, CHUNKS, MODE><<<blocks, THREADS, 0, s>>>(p);
