@@ -51,7 +51,8 @@ def test_attention_contiguous_heads(ops, cgb, oracle, dtype_name, B, H, Sq, Skv)
 # The kernel's CTAs are persistent (one per SM) over units of 256 query rows, with rings of 5 K/V
 # stages and 3 score buffers: more units than SMs, key-tile counts that wrap the rings, a second
 # query tile that lies wholly past the end, and both ragged edges at once.
-@pytest.mark.parametrize("B,H,Sq,Skv", [(40, 4, 256, 256), (1, 2, 300, 1000), (3, 50, 64, 640), (1, 1, 257, 129)])
+@pytest.mark.parametrize("B,H,Sq,Skv", [(40, 4, 256, 256), (1, 2, 300, 1000), (3, 50, 64, 640), (1, 1, 257, 129),
+                                         (4, 40, 100, 100), (2, 80, 130, 300)])
 def test_attention_persistent_units_and_ring_wraps(ops, cgb, oracle, B, H, Sq, Skv):
     _run_contiguous(ops, cgb, oracle, "BF16", B, H, Sq, Skv)
 
