@@ -73,7 +73,7 @@ HOST_TESTS = os.path.join(LIB_DIR, "host_tests")
 def build_host(force=False):
     """Builds the C++ host layer (libcg_b200_host.so) and its test executable (lib/host_tests,
     which also links the CPU oracle as its checker). Needs libcg_b200.so and oracle/libcg_oracle.so."""
-    cxx = os.environ.get("CXX", "g++")
+    cxx = os.environ.get("CG_B200_CXX", "g++")   # the system compiler: its libstdc++ is the shared one torch also loads
     srcs = sorted(os.path.join(HOST, "src", f) for f in os.listdir(os.path.join(HOST, "src")) if f.endswith(".cpp"))
     hdr = os.path.join(HOST, "include", "cg", "b200_host.hpp")
     newest = max([os.path.getmtime(p) for p in srcs + [hdr, os.path.join(ROOT, "include", "cg_b200.h")]])
@@ -93,7 +93,35 @@ def build_host(force=False):
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"host tests build failed:\n{r.stdout}\n{r.stderr}")
+    build_host_python(force, newest)
     return HOST_LIB
+
+
+def host_python_module_path():
+    import sysconfig
+    return os.path.join(LIB_DIR, "cg_b200_host" + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_host_python(force=False, newest=0.0):
+    """The pybind11 module over libcg_b200_host.so (skipped, with a note, where pybind11 is absent)."""
+    try:
+        import pybind11
+    except ImportError:
+        print("pybind11 not importable: the Python module of the host layer is not built")
+        return None
+    import sysconfig
+    cxx = os.environ.get("CG_B200_CXX", "g++")   # the system compiler: its libstdc++ is the shared one torch also loads
+    src = os.path.join(HOST, "python", "bindings.cpp")
+    out = host_python_module_path()
+    if not force and os.path.exists(out) and os.path.getmtime(out) >= max(newest, os.path.getmtime(src), os.path.getmtime(HOST_LIB)):
+        return out
+    cmd = [cxx, "-std=c++20", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-I" + pybind11.get_include(),
+           "-I" + sysconfig.get_paths()["include"], "-I" + os.path.join(HOST, "include"), "-I" + os.path.join(ROOT, "include"),
+           "-o", out, src, "-L" + LIB_DIR, "-lcg_b200_host", "-lcg_b200", "-Wl,-rpath,$ORIGIN"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"host python module build failed:\n{r.stdout}\n{r.stderr}")
+    return out
 
 
 if __name__ == "__main__":

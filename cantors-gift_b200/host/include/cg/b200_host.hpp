@@ -20,6 +20,7 @@
 #pragma once
 
 #include <cstdint>
+#include <deque>
 #include <functional>
 #include <limits>
 #include <map>
@@ -93,7 +94,7 @@ public:
 
 class Module {
 public:
-    std::vector<Function> functions;
+    std::deque<Function> functions;   // a deque: create_function must not move the functions handed out before
     Function& create_function(std::string name) {
         functions.emplace_back();
         functions.back().name = std::move(name);
