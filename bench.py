@@ -67,6 +67,10 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def mark(self):
+        """Samples taken before this call (start-up, warm-up) are left out of the summary."""
+        self.first = len(self.lines)
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -77,7 +81,7 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         sm, mx, reasons, power = [], [], set(), []
-        for ln in self.lines:
+        for ln in self.lines[getattr(self, "first", 0):]:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -672,6 +676,8 @@ def time_workload(w, steps, warmup, rank, world, sample_clocks):
     if world > 1:
         dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if sampler:
+        sampler.mark()
     e0.record()
     for i in range(steps):
         w.step(warmup + i)
@@ -683,7 +689,19 @@ def time_workload(w, steps, warmup, rank, world, sample_clocks):
         t = torch.tensor([secs], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         secs = float(t.item())
+    if secs < 0.6:   # on every rank, sampling or not: the steps of a sharded workload meet in a barrier
+        # nvidia-smi delivers a sample every 100 ms and the timed region of a 0.1 ms kernel is over in a few
+        # milliseconds: the same steps run on, untimed, until the sampler has seen 0.6 s of this load
+        # (every rank runs the same number, computed from the max-reduced time)
+        extra = int(0.6 / max(secs / steps, 1e-7)) + 1
+        for i in range(extra):
+            w.step(warmup + steps + i)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
     clocks = sampler.stop() if sampler else None
+    if clocks is not None:
+        clocks["window"] = "the timed steps and the same steps continued, untimed, to 0.6 s of load"
     return secs, clocks
 
 
