@@ -758,6 +758,11 @@ def run_workload(name, steps, warmup, rank, world, peaks, sample_clocks, with_cp
                      "note": "per rank; achieved = algorithmic work per launch / mean step time on the device"
                              + (" (includes the all-gather)" if world > 1 and name in ("gemm", "matmul_f32", "block") else "")},
     }
+    if w.bound == "tensor":
+        # the timed steps run back to back, so the sustained cuBLAS figure is the denominator; the burst
+        # figure (one kernel timed alone) is given beside it
+        res["roofline"]["peak_burst"] = peaks["bf16_tflops"]
+        res["roofline"]["frac_of_burst"] = achieved / peaks["bf16_tflops"]
     if clocks is not None:
         res["clocks"] = clocks
     if with_cpu and rank == 0:
