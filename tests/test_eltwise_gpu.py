@@ -146,3 +146,44 @@ def test_full_size_config_properties(ops, cgb, oracle):
     sa, sb, sc = (t[idx].cpu().numpy() for t in (a, b, c))
     want = oracle.eltwise(oracle.make_eltwise_desc(oracle.F32, PROG_CHAIN, ["full"] * 3), [sa, sb, sc], sa.size)
     assert np.array_equal(_bits(y[idx].cpu().numpy()), _bits(want))
+
+
+def test_host_buffers_through_the_slab_pipeline(ops, cgb, oracle):
+    """Host arrays in, host array out, in eight slabs on three streams chained by events
+    (HostRunner.run_slabs, cg_b200_stream_wait_event): every slab's kernel must see its own copy-in
+    and every copy-out its own kernel, so the result is the oracle's, bit for bit."""
+    import ctypes as C
+    import torch
+    capi, O = cgb.capi, oracle
+    L = capi.lib()
+    n, slabs = (1 << 20), 8
+    per = n // slabs
+    rng = np.random.default_rng(5)
+    prog = [("input", 0), ("input", 1), "mul", ("input", 2), "add", "relu", ("imm", 0.5), "mul"]
+    host_in = [torch.from_numpy(rng.standard_normal(n, dtype=np.float32)).pin_memory() for _ in range(3)]
+    host_out = torch.zeros(n, dtype=torch.float32).pin_memory()
+    want = O.eltwise(O.make_eltwise_desc(O.F32, prog, ["full"] * 3), [t.numpy() for t in host_in], n)
+    desc = capi.make_eltwise_desc(capi.F32, prog, ["full"] * 3)
+    r = ops.HostRunner()
+    try:
+        for rep in range(3):   # the buffers are reused: a slab of one pass must not meet the next pass's copies
+            host_out.zero_()
+            d = [r.dev(f"in{k}", 4 * n) for k in range(3)]
+            o = r.dev("out", 4 * n)
+            nb = 4 * per
+
+            def copy_in(i, s):
+                for k in range(3):
+                    capi.check(L.cg_b200_memcpy_h2d(C.c_void_p(d[k].value + i * nb), C.c_void_p(host_in[k].data_ptr() + i * nb), nb, s))
+
+            def compute(i, s):
+                arr = (C.c_void_p * 3)(*[p.value + i * nb for p in d])
+                capi.check(L.cg_b200_eltwise(C.byref(desc), arr, 3, C.c_void_p(o.value + i * nb), per, s))
+
+            def copy_out(i, s):
+                capi.check(L.cg_b200_memcpy_d2h(C.c_void_p(host_out.data_ptr() + i * nb), C.c_void_p(o.value + i * nb), nb, s))
+
+            r.run_slabs(slabs, copy_in, compute, copy_out)
+            assert np.array_equal(host_out.numpy().view(np.uint32), want.view(np.uint32)), f"pass {rep}"
+    finally:
+        r.close()
