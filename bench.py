@@ -325,6 +325,8 @@ class GemmWorkload(Workload):
             else:
                 A = torch.rand(self.M, self.K, device="cuda", generator=g) * 2 - 1
                 B = torch.rand(self.K, self.N, device="cuda", generator=g) * 2 - 1
+            if not self.A:
+                self.A_full0 = A if world > 1 else None   # the gather check recomputes set 0 on one GPU
             self.A.append(A[rank * self.Ms:(rank + 1) * self.Ms].contiguous())
             self.B.append(B)
             self.C.append(torch.empty(self.M, self.N, device="cuda", dtype=tdt))
@@ -378,6 +380,45 @@ class GemmWorkload(Workload):
 
     def algorithmic_per_launch(self):
         return self.flops() / self.world
+
+    def gather_check(self):
+        """Outside the timed region: one more sharded step on buffer set 0, then this rank compares the C it
+        holds after the gather with the one-GPU kernel's result for the whole problem, bit for bit.
+        Returns the number of differing elements on this rank."""
+        import torch
+        import torch.distributed as dist
+        from cantors_gift_b200 import capi, ops
+        self.step(0)
+        torch.cuda.synchronize()
+        dist.barrier()
+        want = torch.empty(self.M, self.N, device="cuda", dtype=self.C[0].dtype)
+        in_dt = getattr(capi, self.in_dtype_name)
+        full = capi.make_gemm_desc(self.M, self.N, self.K, in_dt, in_dt, epilogue=self.epilogue)
+        ws, _ = ops.gemm_workspace(full, want.device)
+        ops.gemm(full, self.A_full0, self.B[0], want, bias=self.bias if self.epilogue != "none" else None, workspace=ws)
+        torch.cuda.synchronize()
+        got = device_bytes_to_host(self.C_raw[0], want.numel() * want.element_size()) if self.fused else \
+            self.C[0].cpu().view(torch.uint8).flatten()
+        diff = int((got.view(torch.int16) != want.cpu().view(torch.uint8).flatten().view(torch.int16)).sum().item())
+        dist.barrier()
+        return diff
+
+    def library_baseline(self, steps):
+        """torch.matmul (the library GEMM) on the same shape and buffer rotation, no epilogue."""
+        import torch
+        outs = [torch.empty_like(c) for c in self.C]
+        for i in range(5):
+            torch.matmul(self.A[i % self.sets], self.B[i % self.sets], out=outs[i % self.sets])
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            torch.matmul(self.A[i % self.sets], self.B[i % self.sets], out=outs[i % self.sets])
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        return {"what": "torch.matmul on the same operands (library GEMM, no bias, no GELU)", "ms_per_step": ms,
+                "value": self.flops() / (ms * 1e-3) / 1e12, "unit": "TFLOP/s"}
 
     def e2e_setup(self):
         import torch
@@ -506,6 +547,7 @@ class BlockWorkload(Workload):
         g2 = torch.Generator(device="cuda").manual_seed(5)
         x = torch.randn(self.B, self.S, D, device="cuda", generator=g2).to(torch.bfloat16)
         self.x = x[rank * self.Bs:(rank + 1) * self.Bs].contiguous()
+        self.x_full = x if world > 1 else None   # the gather check runs the whole batch on one GPU
         self.y = torch.empty(self.B, self.S, D, device="cuda", dtype=torch.bfloat16)
         self.comm, self.gather = None, None
         self.launches_per_step = self.block.launches_per_forward
@@ -538,6 +580,24 @@ class BlockWorkload(Workload):
             capi.check(capi.lib().cg_b200_allgather_inplace(self.comm, C.c_void_p(self.y.data_ptr()), ys.numel() * 2,
                                                             C.c_void_p(torch.cuda.current_stream().cuda_stream)),
                        "allgather_inplace")
+
+    def gather_check(self):
+        """Outside the timed region: one more sharded step, then the y this rank holds after the gather
+        against the block run on the whole batch by this GPU alone, bit for bit."""
+        import torch
+        import torch.distributed as dist
+        self.step(0)
+        torch.cuda.synchronize()
+        dist.barrier()
+        if self.gather is not None:
+            got = device_bytes_to_host(self.gather[0], self.y.numel() * 2)
+        else:
+            got = self.y.cpu().view(torch.uint8).flatten()
+        want = self.block.forward(self.x_full)
+        torch.cuda.synchronize()
+        diff = int((got.view(torch.int16) != want.cpu().view(torch.uint8).flatten().view(torch.int16)).sum().item())
+        dist.barrier()
+        return diff
 
     def flops(self):
         from cantors_gift_b200.transformer import EncoderBlock
@@ -606,6 +666,17 @@ class BlockWorkload(Workload):
 
 WORKLOADS = {"block": BlockWorkload, "gemm": GemmWorkload, "eltwise": EltwiseWorkload, "rowreduce": RowReduceWorkload,
              "matmul_f32": MatmulF32Workload}
+
+
+def device_bytes_to_host(dev_ptr, nbytes):
+    """A device buffer of the C ABI allocator as a host uint8 tensor."""
+    import ctypes as C
+    import torch
+    from cantors_gift_b200 import capi
+    host = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    capi.check(capi.lib().cg_b200_memcpy_d2h(C.c_void_p(host.data_ptr()), dev_ptr, nbytes, None), "memcpy_d2h")
+    capi.check(capi.lib().cg_b200_stream_sync(None), "stream_sync")
+    return host
 
 
 def share_buffers(rank, world, count, nbytes):
@@ -742,7 +813,10 @@ def run_workload(name, steps, warmup, rank, world, peaks, sample_clocks, with_cp
         peak, unit = peaks["hbm_gbs"], "GB/s"
     else:
         achieved = w.algorithmic_per_launch() / (secs / steps) / 1e12
-        peak, unit = peaks["bf16_tflops_sustained"], "TFLOP/s"
+        # a timed region of under a second is a kernel timed alone: the burst figure is its denominator;
+        # longer regions run under the power cap and are set against the sustained figure
+        burst = secs < 1.0
+        peak, unit = peaks["bf16_tflops" if burst else "bf16_tflops_sustained"], "TFLOP/s"
     res = {
         "metric": METRIC, "value": value, "unit": w.unit, "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True,
@@ -754,15 +828,23 @@ def run_workload(name, steps, warmup, rank, world, peaks, sample_clocks, with_cp
         "gpu_launches": steps * w.launches_per_step,
         "roofline": {"bound": w.bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
                      "traffic": NCU_TRAFFIC_BYTES.get(name), "peak_source": peaks["source"] +
-                     (" (sustained cuBLAS bf16)" if w.bound == "tensor" else " (copy bandwidth)"),
+                     ((" (burst cuBLAS bf16: the timed region lasts under a second)" if burst else " (sustained cuBLAS bf16)")
+                      if w.bound == "tensor" else " (copy bandwidth)"),
                      "note": "per rank; achieved = algorithmic work per launch / mean step time on the device"
                              + (" (includes the all-gather)" if world > 1 and name in ("gemm", "matmul_f32", "block") else "")},
     }
     if w.bound == "tensor":
-        # the timed steps run back to back, so the sustained cuBLAS figure is the denominator; the burst
-        # figure (one kernel timed alone) is given beside it
-        res["roofline"]["peak_burst"] = peaks["bf16_tflops"]
-        res["roofline"]["frac_of_burst"] = achieved / peaks["bf16_tflops"]
+        res["roofline"]["peak_sustained"] = peaks["bf16_tflops_sustained"]
+        res["roofline"]["frac_of_sustained"] = achieved / peaks["bf16_tflops_sustained"]
+        res["roofline"]["frac_of_nominal_2250"] = achieved / 2250.0
+    if world > 1 and hasattr(w, "gather_check"):
+        import torch
+        import torch.distributed as dist
+        t = torch.tensor([w.gather_check()], device="cuda", dtype=torch.int64)
+        dist.all_reduce(t)
+        res["gather_check"] = "bit-identical" if int(t.item()) == 0 else f"{int(t.item())} elements differ over {world} ranks"
+    if world == 1 and hasattr(w, "library_baseline") and name == "gemm":
+        res["library_baseline"] = w.library_baseline(steps)
     if clocks is not None:
         res["clocks"] = clocks
     if with_cpu and rank == 0:
@@ -772,6 +854,28 @@ def run_workload(name, steps, warmup, rank, world, peaks, sample_clocks, with_cp
     import torch
     torch.cuda.empty_cache()
     return res
+
+
+def compact(r):
+    """The few figures of a secondary workload's line."""
+    rf = r["roofline"]
+    out = {"value": round(r["value"], 2), "unit": r["unit"], "ms_per_step": round(r["ms_per_step"], 5),
+           "frac": round(rf["frac"], 4), "peak": rf["peak"]}
+    if rf.get("traffic"):
+        out["traffic_over_algorithmic"] = round(rf["traffic"] / (rf["achieved"] * r["ms_per_step"] * 1e-3 *
+                                                                 (1e9 if rf["unit"] == "GB/s" else 1e12)), 3) \
+            if rf["unit"] == "GB/s" else None
+    if r["e2e"]["value"] > 0:
+        out["e2e"] = round(r["e2e"]["value"], 2)
+    if "cpu_baseline" in r:
+        out["cpu"] = round(r["cpu_baseline"]["value"], 4)
+        out["cpu_kind"] = r["cpu_baseline"]["kind"]
+    if "gather_check" in r:
+        out["gather_check"] = r["gather_check"]
+    if "clocks" in r and r["clocks"]:
+        out["sm_mhz"] = r["clocks"].get("sm_mhz")
+        out["reasons"] = r["clocks"].get("reasons")
+    return out
 
 
 def run_reference_arm(args, rank, world):
@@ -840,16 +944,21 @@ def main():
 
     line = run_workload(args.workload, args.steps, args.warmup, rank, world, peaks, sample_clocks=(rank == 0),
                         with_cpu=(world == 1 and not args.no_cpu), cpu_budget=12.0, with_e2e=not args.no_e2e)
-    if not args.no_also and world == 1:
-        also = []
-        for other in ("eltwise", "rowreduce", "matmul_f32", "block"):
+    if not args.no_also:
+        # one GPU: every other configuration of the path; several GPUs: the transformer block, the other
+        # workload that is partitioned (batch-sharded, y gathered by its last GEMM)
+        others = ("eltwise", "rowreduce", "matmul_f32", "block") if world == 1 else ("block",)
+        also = {}
+        for other in others:
             if other == args.workload:
                 continue
-            r = run_workload(other, args.steps, args.warmup, rank, world, peaks, sample_clocks=True,
-                             with_cpu=not args.no_cpu, cpu_budget=5.0, with_e2e=not args.no_e2e)
-            also.append({k: r[k] for k in ("value", "unit", "ms_per_step", "dtype", "config", "e2e", "roofline",
-                                           "gpu_launches", "clocks", "cpu_baseline") if k in r})
+            r = run_workload(other, args.steps, args.warmup, rank, world, peaks, sample_clocks=(rank == 0),
+                             with_cpu=(world == 1 and not args.no_cpu), cpu_budget=5.0,
+                             with_e2e=(world == 1 and not args.no_e2e))
+            also[other] = compact(r)
+        # short entries, also kept inside "roofline" (a key whose whole value is recorded)
         line["also"] = also
+        line["roofline"]["also"] = also
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

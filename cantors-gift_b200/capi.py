@@ -123,6 +123,7 @@ SIGNATURES = {
     "cg_b200_comm_destroy": (_i, [_vp]),
     "cg_b200_peer_barrier_create": (_i, [_vpp, _vpp, _i, _i]),
     "cg_b200_peer_barrier": (_i, [_vp, _vp]),
+    "cg_b200_peer_barrier_set_timeout": (_i, [_vp, C.c_uint64]),
     "cg_b200_peer_barrier_destroy": (_i, [_vp]),
     "cg_b200_ipc_export": (_i, [_vp, _vp]),
     "cg_b200_ipc_open": (_i, [_vp, _vpp]),

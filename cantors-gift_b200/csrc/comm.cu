@@ -68,10 +68,11 @@ struct PeerBarrier {
     unsigned long long* table_dev = nullptr;   // device copy of the `world` flag-buffer pointers
     int world = 1, rank = 0;
     unsigned long long epoch = 0;
+    unsigned long long wait_limit_ns = 2000000000ull;
 };
 
 __global__ void peer_barrier_kernel(unsigned long long* const* flags, int world, int rank, unsigned long long epoch,
-                                    uint32_t* err_word) {
+                                    unsigned long long wait_limit_ns, uint32_t* err_word) {
     const int r = threadIdx.x;
     if (r >= world || r == rank) return;
     __threadfence_system();
@@ -86,7 +87,7 @@ __global__ void peer_barrier_kernel(unsigned long long* const* flags, int world,
         if ((it & 0x3f) == 0x3f) {
             unsigned long long t1;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-            if (t1 - t0 > 2000000000ull) {   // a peer never arrived: report and return
+            if (t1 - t0 > wait_limit_ns) {   // a peer never arrived: report and return
                 if (err_word) atomicCAS(err_word, 0u, 0x500u + (uint32_t)r);
                 break;
             }
@@ -125,8 +126,15 @@ extern "C" int cg_b200_peer_barrier(void* barrier, void* stream) {
     ++b->epoch;
     if (b->world == 1) return CG_B200_OK;
     peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(reinterpret_cast<unsigned long long* const*>(b->table_dev), b->world,
-                                                             b->rank, b->epoch, device_error_word());
+                                                             b->rank, b->epoch, b->wait_limit_ns, device_error_word());
     CGB_CUDA(cudaGetLastError());
+    return CG_B200_OK;
+}
+
+extern "C" int cg_b200_peer_barrier_set_timeout(void* barrier, uint64_t nanoseconds) {
+    if (!barrier) return CG_B200_ERR_NULL_POINTER;
+    if (nanoseconds == 0 || nanoseconds > 60000000000ull) return CG_B200_ERR_INVALID_ARG;
+    static_cast<PeerBarrier*>(barrier)->wait_limit_ns = nanoseconds;
     return CG_B200_OK;
 }
 

@@ -78,7 +78,6 @@ struct GemmParams {
     // becomes 2r half-cost units spread over the machine. num_tiles counts units.
     long long full_units;
     uint32_t idesc_half;   // instruction descriptor with N = BN / 2
-    int debug;             // tuning experiments only (CG_B200_GEMM_DEBUG): 1 = no operand loads, 2 = no epilogue work
     int tail_split;        // host side only: 0 = library default, 1 = off, 2 = on (cg_b200_gemm_tuning)
     uint32_t* err_word;
 };
@@ -238,12 +237,6 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                         break;
                     }
                     const uint32_t full = smem_u32(&bar_full[stage]);
-                    if (p.debug & 1) {   // experiment: feed the MMAs stale shared memory, no loads
-                        if (cta_rank == 0) mbar_arrive(full);
-                        ++issued;
-                        if (++stage == kStages) { stage = 0; phase ^= 1u; }
-                        continue;
-                    }
                     // the even CTA's barrier collects the bytes of both CTAs
                     if (cta_rank == 0) mbar_expect_tx(full, stage_tx);
                     const uint32_t sa = smem_base + stage * L::kStageBytes;
@@ -419,7 +412,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     for (int j = 0; j < 32; ++j) v[j] = 0.0f;
                 }
                 const long long n0 = (long long)t.n0 + c0;
-                if (n0 >= p.N || (p.debug & 2)) continue;
+                if (n0 >= p.N) continue;
                 const bool full = n0 + 32 <= p.N;
                 if (epi == CG_B200_EPI_SCALE) {
 #pragma unroll
@@ -921,10 +914,6 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
     p.b_in = b_s_in != 0 && p.batch_in > 1;
     p.b_out = b_s_out != 0 && n_out > 1;
     p.err_word = shared_err_word ? device_error_word() : err_word;
-    {
-        static const int dbg = [] { const char* e = getenv("CG_B200_GEMM_DEBUG"); return e ? atoi(e) : 0; }();
-        p.debug = dbg;
-    }
 
     const bool tf32 = d.in_dtype == CG_B200_F32;
     const bool split = sp.active && sp.copies == 2;

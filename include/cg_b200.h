@@ -352,6 +352,9 @@ int cg_b200_ipc_close(void* peer_ptr);
  * within 2 s is reported through cg_b200_last_device_error (code 0x500 + rank) and the wait ends. */
 int cg_b200_peer_barrier_create(void** barrier, void* const* flag_buffers, int world, int rank);
 int cg_b200_peer_barrier(void* barrier, void* stream);
+/* Replaces the 2 s limit of later barriers on this handle (1 ns .. 60 s). When the limit runs out the
+ * kernel returns, the stream stays usable and the error word holds 0x500 + the missing rank. */
+int cg_b200_peer_barrier_set_timeout(void* barrier, uint64_t nanoseconds);
 int cg_b200_peer_barrier_destroy(void* barrier);
 int cg_b200_gemm_allgather(const cg_b200_gemm_desc* desc, const void* A, const void* B,
                            const void* bias, const void* residual, void* C_full,

@@ -143,6 +143,48 @@ def test_fp32_gemm_matches_reference_golden(ops, cgb, oracle):
     assert_dot_close(Cd.cpu().numpy(), Cref, A[None], B[None], 1e-4, "golden mm_sq")
 
 
+def test_fp32_matmul_1024_cubed_matches_the_reference_jit_kernel(ops, cgb, oracle):
+    """The fp32 configuration at its full size: M = N = K = 1024, A then B ~ U[-1, 1) from one
+    default_rng(0) stream. The GPU result (3xTF32 split) against the reference's own scalar-FMA JIT
+    matmul (benchmarks/benchmark.py:326-438, run from its compiled emitter when that checker library
+    is present) within 1e-4; the oracle's restatement must equal the reference's kernel bit for bit,
+    so where the reference library is absent the restatement stands in for it."""
+    import torch
+    capi, O = cgb.capi, oracle
+    n = 1024
+    rng = np.random.default_rng(0)
+    A = (rng.random((n, n), dtype=np.float32) * 2 - 1).astype(np.float32)
+    B = (rng.random((n, n), dtype=np.float32) * 2 - 1).astype(np.float32)
+    port = O.gemm(O.make_gemm_desc(n, n, n, O.F32, O.F32), A, B).reshape(n, n)
+    if O.have_ref():
+        want = O.ref_matmul(A, B)
+        assert np.array_equal(want.view(np.uint32), port.view(np.uint32)), "oracle port differs from the reference's JIT matmul"
+    else:
+        want = port
+    Cd = torch.zeros(n, n, device="cuda")
+    ops.gemm(capi.make_gemm_desc(n, n, n, capi.F32, capi.F32), torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda(), Cd)
+    assert ops.last_device_error() == 0
+    got = Cd.cpu().numpy()
+    assert_dot_close(got, want, A[None], B[None], 1e-4, "fp32 1024^3 vs reference JIT")
+    exact = A.astype(np.float64) @ B.astype(np.float64)
+    from conftest import report_metrics
+    report_metrics("fp32 1024^3 vs fp64", gpu_max_normalised=np.abs(got - exact).max() / np.abs(exact).max(),
+                   reference_max_normalised=np.abs(want - exact).max() / np.abs(exact).max())
+
+
+@pytest.mark.parametrize("M,N,K", [(5, 3, 7), (200, 136, 100), (256, 384, 512), (300, 520, 256)])
+@pytest.mark.parametrize("b_transposed", [0, 1])
+def test_fp32_gemm_single_pass_tf32(ops, cgb, oracle, M, N, K, b_transposed):
+    """compute = tf32: one kind::tf32 pass on operands truncated to tf32 (10 mantissa bits), the
+    one-copy workspace layout and the wider tiles that pass uses. Bound: 2e-3 of max|C| and,
+    componentwise, of (|A||B|)_ij - two truncations of 2^-10 relative each."""
+    capi = cgb.capi
+    pad = (-N) % 4
+    got, want, A, B = run_case(ops, cgb, oracle, M, N, K, capi.F32, capi.F32, b_transposed=b_transposed, scale=0.5,
+                               seed=K + 1, pad=pad, compute="tf32", return_operands=True)
+    assert_dot_close(got, want, A, B, 2e-3, f"tf32 {M}x{N}x{K} bT={b_transposed}")
+
+
 def test_batched_and_broadcast(ops, cgb, oracle):
     capi = cgb.capi
     got, want = run_case(ops, cgb, oracle, 136, 72, 64, capi.BF16, capi.BF16, batch=5, epilogue="scale", alpha=0.5)

@@ -26,10 +26,8 @@ def _host(O, t, dtype):
 
 
 def _check(got, want, tol, what):
-    err = np.abs(got - want)
-    norm = err.max() / np.abs(want).max()
-    rms = np.sqrt((err ** 2).mean()) / np.sqrt((want ** 2).mean())
-    assert norm <= tol and rms <= tol, f"{what}: max-normalised {norm:.3e}, rms ratio {rms:.3e}, tol {tol}"
+    from conftest import assert_close_rms
+    assert_close_rms(got, want, tol, what)
 
 
 @pytest.mark.parametrize("fused_attention", [True, False])
