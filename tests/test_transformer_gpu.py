@@ -1,6 +1,6 @@
 """Pre-LN encoder block (config 5 of the path) against the CPU oracle composition, through the
-C ABI. Tolerance: the path's bf16 bound, 1e-2, on max|y-ref|/max|ref| and on the RMS ratio (nine
-chained bf16 ops: per-element relative error near zero crossings is not meaningful)."""
+C ABI. Tolerance: the path's bf16 bound, 1e-2, on max|y-ref|/max|ref| and on the RMS ratio; the
+per-element 99.9th-percentile metric is asserted too, at 1e-2 where it holds (see the test)."""
 import numpy as np
 import pytest
 
@@ -25,9 +25,9 @@ def _host(O, t, dtype):
     return O.to_f32(c.view(torch.int16).numpy().view(np.uint16 if dtype == O.BF16 else np.float16), dtype)
 
 
-def _check(got, want, tol, what):
+def _check(got, want, tol, what, p999_tol=None):
     from conftest import assert_close_rms
-    assert_close_rms(got, want, tol, what)
+    assert_close_rms(got, want, tol, what, p999_tol=p999_tol)
 
 
 @pytest.mark.parametrize("fused_attention", [True, False])
@@ -47,7 +47,12 @@ def test_block_matches_oracle(ops, cgb, oracle, dtype_name, B, S, D, H, F, fused
     y = blk.forward(_dev(ops, x, dtype))
     torch.cuda.synchronize()
     assert ops.last_device_error() == 0
-    _check(_host(O, y, dtype), want, 1e-2, f"block {dtype_name} B{B} S{S} D{D} H{H} F{F} fused={fused_attention}")
+    # The per-element 99.9th-percentile metric holds at 1e-2 wherever the kernels round where the oracle
+    # rounds (the nine-launch form) and for f16; the fused attention kernel keeps P in 16 bits and the
+    # oracle's attention in fp32, so with bf16 the elements at zero crossings land at 1.4e-2 .. 2.8e-2.
+    strict = 1e-2 if (not fused_attention or dtype_name == "F16") else 5e-2
+    _check(_host(O, y, dtype), want, 1e-2, f"block {dtype_name} B{B} S{S} D{D} H{H} F{F} fused={fused_attention}",
+           p999_tol=strict)
 
 
 def test_full_size_block_sequences_are_independent_and_match(ops, cgb, oracle):
