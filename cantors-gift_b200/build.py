@@ -66,64 +66,32 @@ def build_library(force=False, verbose=False):
 
 
 HOST = os.path.join(HERE, "host")
-HOST_LIB = os.path.join(LIB_DIR, "libcg_b200_host.so")
-HOST_TESTS = os.path.join(LIB_DIR, "host_tests")
+OVERLAY = os.path.join(HOST, "_overlay")
 
 
-def build_host(force=False):
-    """Builds the C++ host layer (libcg_b200_host.so) and its test executable (lib/host_tests,
-    which also links the CPU oracle as its checker). Needs libcg_b200.so and oracle/libcg_oracle.so."""
-    cxx = os.environ.get("CG_B200_CXX", "g++")   # the system compiler: its libstdc++ is the shared one torch also loads
-    srcs = sorted(os.path.join(HOST, "src", f) for f in os.listdir(os.path.join(HOST, "src")) if f.endswith(".cpp"))
-    hdr = os.path.join(HOST, "include", "cg", "b200_host.hpp")
-    newest = max([os.path.getmtime(p) for p in srcs + [hdr, os.path.join(ROOT, "include", "cg_b200.h")]])
-    common = ["-std=c++20", "-O2", "-Wall", "-Wextra", "-I" + os.path.join(HOST, "include"), "-I" + os.path.join(ROOT, "include")]
-    if force or not os.path.exists(HOST_LIB) or os.path.getmtime(HOST_LIB) < newest:
-        cmd = [cxx] + common + ["-fPIC", "-shared", "-o", HOST_LIB] + srcs + ["-L" + LIB_DIR, "-lcg_b200", "-Wl,-rpath,$ORIGIN"]
-        r = subprocess.run(cmd, capture_output=True, text=True)
-        if r.returncode != 0:
-            raise RuntimeError(f"host library build failed:\n{r.stdout}\n{r.stderr}")
-    test_src = os.path.join(HOST, "tests", "host_tests.cpp")
-    oracle_dir = os.path.join(ROOT, "oracle")
-    if os.path.exists(os.path.join(oracle_dir, "libcg_oracle.so")) and (
-            force or not os.path.exists(HOST_TESTS) or os.path.getmtime(HOST_TESTS) < max(newest, os.path.getmtime(test_src))
-            or os.path.getmtime(HOST_TESTS) < os.path.getmtime(HOST_LIB)):
-        cmd = [cxx] + common + ["-ffp-contract=off", "-o", HOST_TESTS, test_src, "-L" + LIB_DIR, "-lcg_b200_host", "-lcg_b200",
-                                "-L" + oracle_dir, "-lcg_oracle", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,$ORIGIN/../../oracle"]
-        r = subprocess.run(cmd, capture_output=True, text=True)
-        if r.returncode != 0:
-            raise RuntimeError(f"host tests build failed:\n{r.stdout}\n{r.stderr}")
-    build_host_python(force, newest)
-    return HOST_LIB
+def overlay_paths():
+    """Where the host layer's build products are: the reference library with the B200 layer in place, the
+    test executables, the command-line tool and the two Python modules."""
+    return {"lib": os.path.join(OVERLAY, "lib", "libcantors_gift.so"), "bin": os.path.join(OVERLAY, "bin"),
+            "python": os.path.join(OVERLAY, "python", "cantors_gift")}
 
 
-def host_python_module_path():
-    import sysconfig
-    return os.path.join(LIB_DIR, "cg_b200_host" + sysconfig.get_config_var("EXT_SUFFIX"))
-
-
-def build_host_python(force=False, newest=0.0):
-    """The pybind11 module over libcg_b200_host.so (skipped, with a note, where pybind11 is absent)."""
-    try:
-        import pybind11
-    except ImportError:
-        print("pybind11 not importable: the Python module of the host layer is not built")
+def build_host(reference_dir, jobs=8):
+    """Builds the C++ host layer. It implements four translation units of the reference project against
+    the reference's own headers, so it needs the reference's source tree (`reference_dir`); every other
+    reference source is compiled from there too (host/Makefile). Without the tree nothing is built and
+    products of an earlier build are used as they are. Needs libcg_b200.so and oracle/libcg_oracle.so."""
+    if not reference_dir:
+        have = os.path.exists(overlay_paths()["lib"])
+        print("reference tree not found: host layer " + ("kept as built earlier" if have else "not built"))
         return None
-    import sysconfig
-    cxx = os.environ.get("CG_B200_CXX", "g++")   # the system compiler: its libstdc++ is the shared one torch also loads
-    src = os.path.join(HOST, "python", "bindings.cpp")
-    out = host_python_module_path()
-    if not force and os.path.exists(out) and os.path.getmtime(out) >= max(newest, os.path.getmtime(src), os.path.getmtime(HOST_LIB)):
-        return out
-    cmd = [cxx, "-std=c++20", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-I" + pybind11.get_include(),
-           "-I" + sysconfig.get_paths()["include"], "-I" + os.path.join(HOST, "include"), "-I" + os.path.join(ROOT, "include"),
-           "-o", out, src, "-L" + LIB_DIR, "-lcg_b200_host", "-lcg_b200", "-Wl,-rpath,$ORIGIN"]
-    r = subprocess.run(cmd, capture_output=True, text=True)
+    r = subprocess.run(["make", "-C", HOST, f"REF={reference_dir}", f"-j{jobs}", "all"], capture_output=True, text=True)
     if r.returncode != 0:
-        raise RuntimeError(f"host python module build failed:\n{r.stdout}\n{r.stderr}")
-    return out
+        raise RuntimeError("host layer build failed:\n" + r.stdout[-4000:] + r.stderr[-4000:])
+    return overlay_paths()["lib"]
 
 
 if __name__ == "__main__":
     print(build_library(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
-    print(build_host(force="--force" in sys.argv))
+    ref = os.environ.get("CG_REFERENCE_DIR") or os.path.join(os.path.dirname(ROOT), "reference")
+    print(build_host(ref if os.path.isdir(os.path.join(ref, "src", "backend")) else None))

@@ -21,7 +21,7 @@ EW_OPS = {name: i for i, name in enumerate(
      "tanh", "sigmoid", "exp", "log", "sqrt", "rsqrt"])}
 BCAST = {"full": 0, "scalar": 1, "row": 2, "col": 3}
 EPILOGUE = {"none": 0, "bias": 1, "bias_relu": 2, "bias_gelu_tanh": 3, "bias_residual": 4,
-            "residual": 5, "scale": 6}
+            "residual": 5, "scale": 6, "relu": 7, "gelu_tanh": 8}
 COMPUTE = {"default": 0, "tf32x3": 1, "tf32": 2}
 COMM_ID_BYTES = 128
 IPC_HANDLE_BYTES = 64

@@ -432,10 +432,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                             if (n0 + j < p.N) v[j] += Elem<OutT>::to_f32(bias[n0 + j]);
                     }
                 }
-                if (epi == CG_B200_EPI_BIAS_RELU) {
+                if (epi == CG_B200_EPI_BIAS_RELU || epi == CG_B200_EPI_RELU) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
-                } else if (epi == CG_B200_EPI_BIAS_GELU_TANH) {
+                } else if (epi == CG_B200_EPI_BIAS_GELU_TANH || epi == CG_B200_EPI_GELU_TANH) {
                     if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = gelu_epilogue<OutT>(v[j]);
@@ -707,7 +707,7 @@ static int validate_desc(const cg_b200_gemm_desc* d) {
     if (!d) return CG_B200_ERR_NULL_POINTER;
     if (!dtype_ok(d->in_dtype) || !dtype_ok(d->out_dtype)) return CG_B200_ERR_INVALID_ARG;
     if (d->M < 0 || d->N < 0 || d->K < 0 || d->batch < 1) return CG_B200_ERR_INVALID_ARG;
-    if (d->epilogue < CG_B200_EPI_NONE || d->epilogue > CG_B200_EPI_SCALE) return CG_B200_ERR_INVALID_ARG;
+    if (d->epilogue < CG_B200_EPI_NONE || d->epilogue > CG_B200_EPI_GELU_TANH) return CG_B200_ERR_INVALID_ARG;
     if (d->compute < CG_B200_COMPUTE_DEFAULT || d->compute > CG_B200_COMPUTE_TF32) return CG_B200_ERR_INVALID_ARG;
     if (d->in_dtype != CG_B200_F32 && d->compute != CG_B200_COMPUTE_DEFAULT) return CG_B200_ERR_INVALID_ARG;
     if (d->in_dtype == CG_B200_F32 && d->out_dtype != CG_B200_F32) return CG_B200_ERR_UNSUPPORTED;

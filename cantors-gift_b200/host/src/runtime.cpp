@@ -1,26 +1,41 @@
-// runtime.cpp - CUDA Device / Allocator / Stream / Event, the bound executable that walks a launch
-// plan, KernelCache and Runtime.
+// runtime.cpp - cg::Runtime and cg::KernelCache with CUDA devices behind them.
 //
-// The reference's runtime is host-only (src/runtime/runtime.cpp:15-104): a malloc allocator, a
-// no-op stream, an event whose elapsed time is 0, a CPUBoundExecutable that calls JIT-ed code, and
-// Runtime::bind returns nullptr for every GPU (:120-129). KernelCache keeps the reference's file
-// format byte for byte (:149-267) so cache directories stay interchangeable.
+// Takes the place of the reference's src/runtime/runtime.cpp, whose devices are host-only (malloc
+// allocator, no-op stream, an event whose elapsed time is 0; :15-60) and whose Runtime::bind answers
+// nullptr for every GPU (:120-129). Here:
+//   - cg::b200::make_cuda_device gives Runtime::add_device a Device whose Allocator, Stream and Event
+//     are the C ABI's (cudaMalloc / cudaStream / cudaEvent);
+//   - Runtime::bind on a CUDA device decodes the launch plan in Executable::machine_code and returns a
+//     BoundExecutable whose launch() walks it, one cg_b200_* call per record, asynchronous on the
+//     caller's stream; nullptr when the device is unknown or machine_code holds no plan;
+//   - a CPU Executable (x86 bytes from CpuBackend) still binds to JIT-ed code as before;
+//   - KernelCache keeps the reference's .cgbin layout field for field (:162-173, :244-266), so cache
+//     directories written by either side are read by the other.
+#include "cg/runtime/runtime.hpp"
+
 #include <cstring>
 #include <filesystem>
 #include <fstream>
+#include <mutex>
 
-#include "cg/b200_host.hpp"
+#include "cg/autotuner/bayesian_optimizer.hpp"
+#include "cg/b200/b200.hpp"
+#include "cg/b200/plan.hpp"
+#include "cg/backend/jit.hpp"
 
 namespace cg {
 namespace {
 
+thread_local int t_launch_status = CG_B200_OK;
+
+// ---- CUDA device over the C ABI ----------------------------------------------------------------------
 class CudaAllocator final : public Allocator {
 public:
     explicit CudaAllocator(u32 index) : index_(index) {}
     void* allocate(u64 bytes, u64 /*alignment: device allocations are 256-byte aligned*/) override {
         void* p = nullptr;
         if (cg_b200_set_device(static_cast<int>(index_)) != CG_B200_OK) return nullptr;
-        return cg_b200_malloc(&p, bytes) == CG_B200_OK ? p : nullptr;
+        return cg_b200_malloc(&p, bytes ? bytes : 1) == CG_B200_OK ? p : nullptr;
     }
     void deallocate(void* p) override { cg_b200_free(p); }
 
@@ -30,11 +45,14 @@ private:
 
 class CudaStream final : public Stream {
 public:
-    explicit CudaStream(DeviceId d) : dev_(d) {
+    explicit CudaStream(DeviceId d) : dev_(d), owned_(true) {
         cg_b200_set_device(static_cast<int>(d.index));
         cg_b200_stream_create(&s_);
     }
-    ~CudaStream() override { cg_b200_stream_destroy(s_); }
+    CudaStream(DeviceId d, void* existing) : dev_(d), s_(existing), owned_(false) {}
+    ~CudaStream() override {
+        if (owned_) cg_b200_stream_destroy(s_);
+    }
     void sync() override { cg_b200_stream_sync(s_); }
     DeviceId device() const override { return dev_; }
     void* handle() const { return s_; }
@@ -42,17 +60,22 @@ public:
 private:
     DeviceId dev_;
     void* s_ = nullptr;
+    bool owned_;
 };
 
 class CudaEvent final : public Event {
 public:
     CudaEvent() { cg_b200_event_create(&e_); }
     ~CudaEvent() override { cg_b200_event_destroy(e_); }
-    void record(Stream& s) override { cg_b200_event_record(e_, static_cast<CudaStream&>(s).handle()); }
+    void record(Stream& s) override {
+        auto* cs = dynamic_cast<CudaStream*>(&s);
+        cg_b200_event_record(e_, cs ? cs->handle() : nullptr);
+    }
     void wait() override { cg_b200_event_sync(e_); }
     double elapsed_sec_since(Event& earlier) override {
+        auto* first = dynamic_cast<CudaEvent*>(&earlier);
         double sec = 0.0;
-        cg_b200_event_elapsed_sec(static_cast<CudaEvent&>(earlier).e_, e_, &sec);
+        if (first) cg_b200_event_elapsed_sec(first->e_, e_, &sec);
         return sec;
     }
 
@@ -76,15 +99,15 @@ private:
     CudaAllocator alloc_;
 };
 
-// Walks the plan: one C-ABI call per record, asynchronous on the caller's stream.
+// ---- the bound executable of the B200 path -------------------------------------------------------------
 class CudaBoundExecutable final : public BoundExecutable {
 public:
-    CudaBoundExecutable(std::shared_ptr<Executable> exe, LaunchPlan plan, Device* dev)
+    CudaBoundExecutable(std::shared_ptr<Executable> exe, b200::LaunchPlan plan, Device* dev)
         : exe_(std::move(exe)), plan_(std::move(plan)), dev_(dev) {
         const usize first = plan_.n_inputs + plan_.n_outputs;
         scratch_.assign(plan_.buffers.size(), nullptr);
         for (usize i = first; i < plan_.buffers.size(); ++i) {
-            scratch_[i] = dev_->allocator().allocate(plan_.buffers[i].bytes ? plan_.buffers[i].bytes : 1);
+            scratch_[i] = dev_->allocator().allocate(plan_.buffers[i].bytes);
             if (!scratch_[i]) ok_ = false;
         }
         if (plan_.workspace_bytes) {
@@ -98,69 +121,138 @@ public:
         if (workspace_) dev_->allocator().deallocate(workspace_);
     }
     bool ok() const { return ok_; }
-    int status() const override { return status_; }
+
+    int set_gather(void* const* peers, int world, int rank) {
+        if (world < 1 || world > 8 || rank < 0 || rank >= world || (world > 1 && !peers)) return CG_B200_ERR_INVALID_ARG;
+        // the record that writes output 0 must be a single GEMM over the whole output
+        int producer = -1;
+        for (usize i = 0; i < plan_.records.size(); ++i)
+            if (plan_.records[i].output == static_cast<std::int32_t>(plan_.n_inputs)) producer = static_cast<int>(i);
+        if (producer < 0) return CG_B200_ERR_UNSUPPORTED;
+        const b200::PlanRecord& r = plan_.records[static_cast<usize>(producer)];
+        if (r.kind != b200::PlanRecord::Gemm || r.gemm.batch != 1 || r.output_offset != 0) return CG_B200_ERR_UNSUPPORTED;
+        gather_record_ = producer;
+        gather_world_ = world;
+        gather_rank_ = rank;
+        for (int i = 0; i < world; ++i) gather_peers_[i] = world > 1 ? peers[i] : nullptr;
+        return CG_B200_OK;
+    }
 
     void launch(Span<Tensor*> inputs, Span<Tensor*> outputs, Stream& stream) override {
-        status_ = CG_B200_OK;
-        if (inputs.size() != plan_.n_inputs || outputs.size() != plan_.n_outputs) {
-            status_ = CG_B200_ERR_INVALID_ARG;
-            return;
-        }
+        t_launch_status = run(inputs, outputs, stream);
+    }
+
+private:
+    int run(Span<Tensor*> inputs, Span<Tensor*> outputs, Stream& stream) {
+        if (inputs.size() != plan_.n_inputs || outputs.size() != plan_.n_outputs) return CG_B200_ERR_INVALID_ARG;
+        auto* cs = dynamic_cast<CudaStream*>(&stream);
+        if (!cs) return CG_B200_ERR_INVALID_ARG;   // a stream of another device kind
         std::vector<void*> buf(scratch_);
+        const bool gathered = gather_record_ >= 0 && gather_world_ > 1;
         for (usize i = 0; i < inputs.size(); ++i) {
-            if (!inputs[i] || inputs[i]->num_bytes < plan_.buffers[i].bytes) { status_ = CG_B200_ERR_INVALID_ARG; return; }
+            if (!inputs[i] || !inputs[i]->data || inputs[i]->num_bytes < plan_.buffers[i].bytes) return CG_B200_ERR_INVALID_ARG;
             buf[i] = inputs[i]->data;
         }
         for (usize i = 0; i < outputs.size(); ++i) {
             const usize b = plan_.n_inputs + i;
-            if (!outputs[i] || outputs[i]->num_bytes < plan_.buffers[b].bytes) { status_ = CG_B200_ERR_INVALID_ARG; return; }
+            u64 need = plan_.buffers[b].bytes;
+            if (i == 0 && gathered) need *= static_cast<u64>(gather_world_);   // the full-size output of all ranks
+            if (!outputs[i] || !outputs[i]->data || outputs[i]->num_bytes < need) return CG_B200_ERR_INVALID_ARG;
             buf[b] = outputs[i]->data;
         }
-        void* st = static_cast<CudaStream&>(stream).handle();
-        auto at = [&](i32 id) -> void* { return id >= 0 ? buf[static_cast<usize>(id)] : nullptr; };
-        for (const PlanRecord& r : plan_.records) {
+        void* st = cs->handle();
+        auto at = [&](std::int32_t id, std::int64_t offset, std::int32_t dtype) -> void* {
+            if (id < 0) return nullptr;
+            const u64 esz = dtype == CG_B200_F32 ? 4 : 2;
+            return static_cast<char*>(buf[static_cast<usize>(id)]) + static_cast<u64>(offset) * esz;
+        };
+        for (usize k = 0; k < plan_.records.size(); ++k) {
+            const b200::PlanRecord& r = plan_.records[k];
             int s = CG_B200_OK;
             switch (r.kind) {
-                case PlanRecord::Eltwise: {
+                case b200::PlanRecord::Eltwise: {
                     const void* ptrs[CG_B200_EW_MAX_INPUTS] = {};
-                    for (i32 k = 0; k < r.n_inputs; ++k) ptrs[k] = at(r.input[k]);
-                    s = cg_b200_eltwise(&r.eltwise, ptrs, r.n_inputs, at(r.output), r.n, st);
+                    for (std::int32_t i = 0; i < r.n_inputs; ++i) ptrs[i] = at(r.input[i], r.input_offset[i], r.eltwise.dtype);
+                    s = cg_b200_eltwise(&r.eltwise, ptrs, r.n_inputs, at(r.output, r.output_offset, r.eltwise.dtype), r.n, st);
                     break;
                 }
-                case PlanRecord::Gemm:
-                    s = cg_b200_gemm_tuned(&r.gemm, &r.tuning, at(r.input[0]), at(r.input[1]), at(r.input[2]), at(r.input[3]),
-                                           at(r.output), workspace_, plan_.workspace_bytes, st);
+                case b200::PlanRecord::Gemm: {
+                    const void* a = at(r.input[0], r.input_offset[0], r.gemm.in_dtype);
+                    const void* b = at(r.input[1], r.input_offset[1], r.gemm.in_dtype);
+                    const void* bias = at(r.input[2], r.input_offset[2], r.gemm.out_dtype);
+                    const void* res = at(r.input[3], r.input_offset[3], r.gemm.out_dtype);
+                    void* c = at(r.output, r.output_offset, r.gemm.out_dtype);
+                    if (gathered && static_cast<int>(k) == gather_record_)
+                        s = cg_b200_gemm_allgather(&r.gemm, a, b, bias, res, c, gather_peers_, gather_world_, gather_rank_,
+                                                   workspace_, plan_.workspace_bytes, st);
+                    else
+                        s = cg_b200_gemm_tuned(&r.gemm, &r.tuning, a, b, bias, res, c, workspace_, plan_.workspace_bytes, st);
                     break;
-                case PlanRecord::Softmax:
-                    s = cg_b200_softmax(r.row_dtype, at(r.input[0]), at(r.output), r.rows, r.cols, st);
+                }
+                case b200::PlanRecord::Softmax:
+                    s = cg_b200_softmax(r.row_dtype, at(r.input[0], r.input_offset[0], r.row_dtype),
+                                        at(r.output, r.output_offset, r.row_dtype), r.rows, r.cols, st);
                     break;
-                case PlanRecord::LayerNorm:
-                    s = cg_b200_layernorm(r.row_dtype, at(r.input[0]), nullptr, nullptr, r.eps, at(r.output), r.rows, r.cols, st);
+                case b200::PlanRecord::LayerNorm:
+                    s = cg_b200_layernorm(r.row_dtype, at(r.input[0], r.input_offset[0], r.row_dtype), nullptr, nullptr, r.eps,
+                                          at(r.output, r.output_offset, r.row_dtype), r.rows, r.cols, st);
                     break;
-                case PlanRecord::SoftmaxLayerNorm:
-                    s = cg_b200_softmax_layernorm(r.row_dtype, at(r.input[0]), nullptr, nullptr, r.eps, at(r.output), r.rows,
-                                                  r.cols, st);
+                case b200::PlanRecord::SoftmaxLayerNorm:
+                    s = cg_b200_softmax_layernorm(r.row_dtype, at(r.input[0], r.input_offset[0], r.row_dtype), nullptr, nullptr,
+                                                  r.eps, at(r.output, r.output_offset, r.row_dtype), r.rows, r.cols, st);
                     break;
+                case b200::PlanRecord::Attention: {
+                    const std::int32_t dt = r.attention.dtype;
+                    s = cg_b200_attention(&r.attention, at(r.input[0], r.input_offset[0], dt), at(r.input[1], r.input_offset[1], dt),
+                                          at(r.input[2], r.input_offset[2], dt), at(r.output, r.output_offset, dt), st);
+                    break;
+                }
                 default: s = CG_B200_ERR_INVALID_ARG;
             }
-            if (s != CG_B200_OK) {   // the reference's launch returns silently on failure; the status is kept
-                status_ = s;
-                return;
-            }
+            if (s != CG_B200_OK) return s;   // the reference's launch returns silently; the status is kept
         }
+        return CG_B200_OK;
     }
 
-private:
     std::shared_ptr<Executable> exe_;
-    LaunchPlan plan_;
+    b200::LaunchPlan plan_;
     Device* dev_;
     std::vector<void*> scratch_;
     void* workspace_ = nullptr;
     bool ok_ = true;
-    int status_ = CG_B200_OK;
+    int gather_record_ = -1, gather_world_ = 1, gather_rank_ = 0;
+    void* gather_peers_[8] = {};
+};
+
+// ---- the CPU path: x86 bytes from CpuBackend, called with the tensors' data pointers -------------------
+class JitBoundExecutable final : public BoundExecutable {
+public:
+    explicit JitBoundExecutable(std::shared_ptr<Executable> exe) : exe_(std::move(exe)) { code_.allocate(exe_->machine_code); }
+
+    // The generated function takes its pointer arguments in the System V integer registers: inputs
+    // first, then outputs, at most six. Extra arguments a function does not read are harmless there.
+    void launch(Span<Tensor*> inputs, Span<Tensor*> outputs, Stream&) override {
+        if (!code_.valid()) return;
+        void* a[6] = {};
+        usize n = 0;
+        for (Tensor* t : inputs)
+            if (n < 6) a[n++] = t ? t->data : nullptr;
+        for (Tensor* t : outputs)
+            if (n < 6) a[n++] = t ? t->data : nullptr;
+        if (n == 0) return;
+        using Fn = void (*)(void*, void*, void*, void*, void*, void*);
+        reinterpret_cast<Fn>(code_.entry())(a[0], a[1], a[2], a[3], a[4], a[5]);
+    }
+
+private:
+    std::shared_ptr<Executable> exe_;
+    JITMemory code_;
 };
 
 }  // namespace
+
+// ---- cg::b200 additions --------------------------------------------------------------------------------
+namespace b200 {
 
 std::unique_ptr<Device> make_cuda_device(u32 index) {
     int count = 0;
@@ -170,228 +262,60 @@ std::unique_ptr<Device> make_cuda_device(u32 index) {
     return std::make_unique<CudaDevice>(index);
 }
 
+void* native_stream(Stream& s) {
+    auto* cs = dynamic_cast<CudaStream*>(&s);
+    return cs ? cs->handle() : nullptr;
+}
+
+std::unique_ptr<Stream> wrap_stream(void* cuda_stream, u32 device_index) {
+    return std::make_unique<CudaStream>(DeviceId::cuda(device_index), cuda_stream);
+}
+
 int copy_to_device(Tensor& dst, const void* host_src, u64 bytes, Stream& s) {
     if (bytes > dst.num_bytes) return CG_B200_ERR_INVALID_ARG;
-    return cg_b200_memcpy_h2d(dst.data, host_src, bytes, static_cast<CudaStream&>(s).handle());
+    return cg_b200_memcpy_h2d(dst.data, host_src, bytes, native_stream(s));
 }
 
 int copy_to_host(void* host_dst, const Tensor& src, u64 bytes, Stream& s) {
     if (bytes > src.num_bytes) return CG_B200_ERR_INVALID_ARG;
-    return cg_b200_memcpy_d2h(host_dst, src.data, bytes, static_cast<CudaStream&>(s).handle());
+    return cg_b200_memcpy_d2h(host_dst, src.data, bytes, native_stream(s));
 }
 
-// ---- KernelCache: the reference's format, field for field --------------------------------------------------
-u64 KernelCache::compute_key(const std::string& graph_text, const std::string& shapes, const std::string& dtypes,
-                             const std::string& hardware_name) {
-    u64 h = 0xcbf29ce484222325ULL;   // FNV-1a, 64 bit
-    for (const std::string* s : {&graph_text, &shapes, &dtypes, &hardware_name})
-        for (char c : *s) {
-            h ^= static_cast<u64>(static_cast<u8>(c));
-            h *= 0x100000001b3ULL;
-        }
-    return h;
-}
-
-namespace {
-constexpr u32 kCacheMagic = 0x454B4743;   // "CGKE"
-struct Reader {
-    std::ifstream& in;
-    template <typename T> T num() { T v{}; in.read(reinterpret_cast<char*>(&v), sizeof(T)); return v; }
-    std::string str() {
-        const u64 len = num<u64>();
-        if (!in || len > (1ull << 32)) { in.setstate(std::ios::failbit); return {}; }
-        std::string s(len, '\0');
-        in.read(s.data(), static_cast<std::streamsize>(len));
-        return s;
-    }
-};
-struct Writer {
-    std::ofstream& out;
-    template <typename T> void num(T v) { out.write(reinterpret_cast<const char*>(&v), sizeof(T)); }
-    void str(const std::string& s) { num<u64>(s.size()); out.write(s.data(), static_cast<std::streamsize>(s.size())); }
-};
-}  // namespace
-
-std::optional<std::shared_ptr<Executable>> KernelCache::lookup(u64 key) {
-    if (auto it = mem_cache_.find(key); it != mem_cache_.end()) return it->second;
-    namespace fs = std::filesystem;
-    const fs::path path = fs::path(dir_) / (std::to_string(key) + ".cgbin");
-    std::error_code ec;
-    if (!fs::exists(path, ec)) return std::nullopt;
-    std::ifstream in(path, std::ios::binary);
-    if (!in) return std::nullopt;
-    Reader r{in};
-    if (r.num<u32>() != kCacheMagic || r.num<u32>() != 1) return std::nullopt;
-    auto exe = std::make_shared<Executable>();
-    exe->name = r.str();
-    exe->target_device.kind = static_cast<DeviceId::Kind>(r.num<u64>());
-    exe->target_device.index = r.num<u32>();
-    const std::string code = r.str();
-    exe->machine_code.assign(code.begin(), code.end());
-    exe->ptx_text = r.str();
-    exe->disassembly = r.str();
-    const u64 n_entry = r.num<u64>();
-    for (u64 i = 0; in && i < n_entry && i < (1u << 20); ++i) {
-        std::string name = r.str();
-        const u64 offset = r.num<u64>();
-        exe->entrypoints.push_back({std::move(name), offset});
-    }
-    exe->shared_mem_bytes = r.num<u64>();
-    exe->constant_mem_bytes = r.num<u64>();
-    exe->threads_per_block = r.num<u32>();
-    if (!in) return std::nullopt;   // truncated file
-    mem_cache_[key] = exe;
-    return exe;
-}
-
-void KernelCache::insert(u64 key, std::shared_ptr<Executable> exe) {
-    mem_cache_[key] = exe;
-    namespace fs = std::filesystem;
-    std::error_code ec;
-    fs::create_directories(dir_, ec);
-    std::ofstream out(fs::path(dir_) / (std::to_string(key) + ".cgbin"), std::ios::binary);
-    if (!out) return;
-    Writer w{out};
-    w.num<u32>(kCacheMagic);
-    w.num<u32>(1);
-    w.str(exe->name);
-    w.num<u64>(static_cast<u64>(exe->target_device.kind));
-    w.num<u32>(exe->target_device.index);
-    w.str(std::string(exe->machine_code.begin(), exe->machine_code.end()));
-    w.str(exe->ptx_text);
-    w.str(exe->disassembly);
-    w.num<u64>(exe->entrypoints.size());
-    for (const auto& [name, offset] : exe->entrypoints) {
-        w.str(name);
-        w.num<u64>(offset);
-    }
-    w.num<u64>(exe->shared_mem_bytes);
-    w.num<u64>(exe->constant_mem_bytes);
-    w.num<u32>(exe->threads_per_block);
-}
-
-// ---- Runtime ----------------------------------------------------------------------------------------------------
-Runtime::Runtime(std::string cache_dir) : cache_(std::move(cache_dir)) {}
-Runtime::~Runtime() = default;
-
-void Runtime::add_device(std::unique_ptr<Device> d) {
-    if (d) devices_.push_back(std::move(d));
-}
-
-Device* Runtime::get_device(DeviceId id) const {
-    for (const auto& d : devices_)
-        if (d->id() == id) return d.get();
-    return nullptr;
-}
-
-std::unique_ptr<BoundExecutable> Runtime::bind(std::shared_ptr<Executable> exe, DeviceId device) {
-    if (!exe || device.kind != DeviceId::Kind::CUDA) return nullptr;   // this runtime has no CPU path
-    Device* dev = get_device(device);
-    if (!dev) return nullptr;
-    auto plan = LaunchPlan::deserialize(exe->machine_code);
-    if (!plan) return nullptr;
-    auto bound = std::make_unique<CudaBoundExecutable>(std::move(exe), std::move(*plan), dev);
-    if (!bound->ok()) return nullptr;
-    return bound;
-}
-
-Runtime::CompileResult Runtime::compile_and_cache(u64 cache_key, const CGModule& cgm, MachineBackend& backend) {
-    CompileResult res;
-    if (auto hit = cache_.lookup(cache_key)) {
-        res.executable = *hit;
-        res.cache_hit = true;
-        return res;
-    }
-    res.executable = std::shared_ptr<Executable>(backend.compile(cgm).release());
-    if (res.executable) cache_.insert(cache_key, res.executable);
-    return res;
-}
-
-}  // namespace cg
-
-// ---- schedules and autotuning ---------------------------------------------------------------------------
-namespace cg {
-
-static u64 mix(u64 h, u64 v) {   // FNV-1a over 64-bit words
-    h ^= v;
-    return h * 1099511628211ull;
-}
-
-u64 Schedule::hash() const {
-    u64 h = 1469598103934665603ull;
-    for (const Transform& t : transforms_) {
-        h = mix(h, static_cast<u64>(t.kind));
-        for (char c : t.dim) h = mix(h, static_cast<u8>(c));
-        h = mix(h, static_cast<u64>(t.factor));
-        h = mix(h, static_cast<u64>(t.factor2));
-        for (char c : t.target) h = mix(h, static_cast<u8>(c));
-    }
-    return h;
-}
-
-bool Schedule::operator==(const Schedule& o) const {
-    if (transforms_.size() != o.transforms_.size()) return false;
-    for (usize i = 0; i < transforms_.size(); ++i) {
-        const Transform &a = transforms_[i], &b = o.transforms_[i];
-        if (a.kind != b.kind || a.dim != b.dim || a.factor != b.factor || a.factor2 != b.factor2 || a.target != b.target)
-            return false;
-    }
-    return true;
-}
-
-ScheduleSpace ScheduleSpace::grid_matmul(std::vector<i64> m_tiles, std::vector<i64> n_tiles, std::vector<i64> k_tiles,
-                                         std::vector<i64> vector_widths) {
-    ScheduleSpace space;
-    for (i64 m : m_tiles)
-        for (i64 n : n_tiles)
-            for (i64 k : k_tiles)
-                for (i64 v : vector_widths) {
-                    Schedule s;
-                    s.add({TransformKind::Tile, "m", m, n, ""});
-                    s.add({TransformKind::Tile, "n", n, 0, ""});
-                    s.add({TransformKind::Tile, "k", k, 0, ""});
-                    s.add({TransformKind::Parallelize, "m", 0, 0, ""});
-                    s.add({TransformKind::Parallelize, "n", 0, 0, ""});
-                    s.add({TransformKind::Vectorize, "n_inner", v, 0, ""});
-                    s.add({TransformKind::Cache, "a", 0, 0, "A"});
-                    s.add({TransformKind::Cache, "b", 0, 0, "B"});
-                    space.add(std::move(s));
-                }
-    return space;
-}
-
-AutotuneResult bayesian_autotune(const ScheduleSpace& space, BenchmarkFn benchmark, usize max_benchmarks, usize initial_random) {
-    (void)initial_random;
-    AutotuneResult res;
-    if (!benchmark) return res;
-    for (const Schedule& s : space.schedules()) {
-        if (res.total_benchmarks >= max_benchmarks) break;
-        const double t = benchmark(s);
-        res.runtime_history.push_back(t);
-        ++res.total_benchmarks;
-        if (t < res.best_runtime) {
-            res.best_runtime = t;
-            res.best_schedule = s;
-        }
-    }
-    return res;
-}
-
-std::optional<cg_b200_gemm_tuning> gemm_tuning_from_schedule(const Schedule& s) {
-    cg_b200_gemm_tuning t{};
-    for (const Transform& x : s.transforms()) {
-        if (x.kind != TransformKind::Tile) continue;
-        if (x.dim == "m") {
-            if (x.factor == 128) t.cta_pair = 1;
-            else if (x.factor == 256) t.cta_pair = 2;
-            else if (x.factor != 0) return std::nullopt;
-        } else if (x.dim == "n") {
-            if (x.factor == 64 || x.factor == 128 || x.factor == 256) t.tile_n = static_cast<int32_t>(x.factor);
-            else if (x.factor != 0) return std::nullopt;
-        }
-    }
-    if (t.cta_pair == 2 && t.tile_n == 64) return std::nullopt;   // a CTA pair's tile is 128 or 256 wide
+static Tensor describe(std::vector<i64> shape, DType dtype, DeviceId dev) {
+    Tensor t;
+    u64 n = 1;
+    for (i64 d : shape) n *= static_cast<u64>(d);
+    t.shape = Shape::from_constants(std::move(shape));
+    t.dtype = dtype;
+    t.device = dev;
+    t.num_bytes = n * dtype_size(dtype);
     return t;
+}
+
+Tensor make_tensor(Device& dev, std::vector<i64> shape, DType dtype) {
+    Tensor t = describe(std::move(shape), dtype, dev.id());
+    t.data = dev.allocator().allocate(t.num_bytes, 256);
+    t.owns_memory = t.data != nullptr;
+    return t;
+}
+
+Tensor tensor_from_ptr(void* device_ptr, std::vector<i64> shape, DType dtype, u32 device_index) {
+    Tensor t = describe(std::move(shape), dtype, DeviceId::cuda(device_index));
+    t.data = device_ptr;
+    return t;
+}
+
+void release_tensor(Device& dev, Tensor& t) {
+    if (t.owns_memory && t.data) dev.allocator().deallocate(t.data);
+    t.data = nullptr;
+    t.owns_memory = false;
+}
+
+int last_launch_status() { return t_launch_status; }
+
+int set_output_gather(BoundExecutable& bound, void* const* peer_outputs, int world, int rank) {
+    auto* b = dynamic_cast<CudaBoundExecutable*>(&bound);
+    return b ? b->set_gather(peer_outputs, world, rank) : CG_B200_ERR_UNSUPPORTED;
 }
 
 namespace {
@@ -410,8 +334,6 @@ struct GemmBenchState {
             if (p) device->allocator().deallocate(p);
     }
 };
-u64 elem_bytes(int dtype) { return dtype == CG_B200_F32 ? 4 : 2; }
-void* stream_handle(Stream& s) { return static_cast<CudaStream&>(s).handle(); }
 }  // namespace
 
 BenchmarkFn make_gemm_benchmark(const cg_b200_gemm_desc& desc, Device& device, int iters, int warmup) {
@@ -424,11 +346,16 @@ BenchmarkFn make_gemm_benchmark(const cg_b200_gemm_desc& desc, Device& device, i
     st->begin = device.create_event();
     st->end = device.create_event();
     const cg_b200_gemm_desc& d = st->desc;
-    const u64 in = elem_bytes(d.in_dtype), out = elem_bytes(d.out_dtype);
+    auto esz = [](int dt) -> u64 { return dt == CG_B200_F32 ? 4 : 2; };
+    // extents from the strides: the furthest element each operand can touch
+    const i64 outer = d.batch_inner > 1 ? d.batch / d.batch_inner : d.batch, inner = d.batch_inner > 1 ? d.batch_inner : 1;
+    auto extent = [&](i64 rows, i64 ld, i64 s_out, i64 s_in) {
+        return static_cast<u64>((outer - 1) * s_out + (inner - 1) * s_in + rows * ld);
+    };
     const i64 b_rows = d.b_transposed ? d.N : d.K;
-    const u64 a_bytes = static_cast<u64>((d.batch_stride_a ? d.batch_stride_a * d.batch : d.M * d.lda)) * in;
-    const u64 b_bytes = static_cast<u64>((d.batch_stride_b ? d.batch_stride_b * d.batch : b_rows * d.ldb)) * in;
-    const u64 c_bytes = static_cast<u64>((d.batch_stride_c ? d.batch_stride_c * d.batch : d.M * d.ldc)) * out;
+    const u64 a_bytes = extent(d.M, d.lda, d.batch_stride_a, d.inner_stride_a) * esz(d.in_dtype);
+    const u64 b_bytes = extent(b_rows, d.ldb, d.batch_stride_b, d.inner_stride_b) * esz(d.in_dtype);
+    const u64 c_bytes = extent(d.M, d.ldc, d.batch_stride_c, d.inner_stride_c) * esz(d.out_dtype);
     auto zeroed = [&](u64 bytes) -> void* {
         void* p = device.allocator().allocate(bytes ? bytes : 16);
         if (p) cg_b200_memset(p, 0, bytes ? bytes : 16, nullptr);
@@ -437,7 +364,7 @@ BenchmarkFn make_gemm_benchmark(const cg_b200_gemm_desc& desc, Device& device, i
     st->a = zeroed(a_bytes);
     st->b = zeroed(b_bytes);
     st->c = zeroed(c_bytes);
-    st->bias = zeroed(static_cast<u64>(d.N) * out);
+    st->bias = zeroed(static_cast<u64>(d.N) * esz(d.out_dtype));
     st->res = zeroed(c_bytes);
     if (cg_b200_gemm_workspace_bytes(&st->desc, &st->ws_bytes) == CG_B200_OK && st->ws_bytes) st->ws = zeroed(st->ws_bytes);
     st->ok = st->stream && st->begin && st->end && st->a && st->b && st->c && st->bias && st->res && (st->ws || !st->ws_bytes);
@@ -447,12 +374,12 @@ BenchmarkFn make_gemm_benchmark(const cg_b200_gemm_desc& desc, Device& device, i
         if (!st->ok) return never;
         const auto tuning = gemm_tuning_from_schedule(s);
         if (!tuning) return never;
-        void* h = stream_handle(*st->stream);
+        void* h = native_stream(*st->stream);
         auto once = [&]() {
             return cg_b200_gemm_tuned(&st->desc, &*tuning, st->a, st->b, st->bias, st->res, st->c, st->ws, st->ws_bytes, h);
         };
         for (int i = 0; i < st->warmup + 1; ++i)
-            if (once() != CG_B200_OK) return never;   // refused combinations end here
+            if (once() != CG_B200_OK) return never;   // combinations the kernels refuse end here
         st->begin->record(*st->stream);
         for (int i = 0; i < st->iters; ++i)
             if (once() != CG_B200_OK) return never;
@@ -464,9 +391,187 @@ BenchmarkFn make_gemm_benchmark(const cg_b200_gemm_desc& desc, Device& device, i
     };
 }
 
-Runtime::AutotuneResult Runtime::autotune_and_cache(u64 cache_key, const ScheduleSpace& space, const BenchmarkFn& benchmark,
-                                                    MachineBackend& backend,
-                                                    const std::function<CGModule(const Schedule&)>& lower_best) {
+TunedExecutable autotune_and_cache(Runtime& rt, u64 key, const Module& m, const ScheduleSpace& space,
+                                   const BenchmarkFn& benchmark, MachineBackend& backend) {
+    TunedExecutable res;
+    if (auto hit = rt.kernel_cache().lookup(key)) {
+        res.executable = *hit;
+        res.cache_hit = true;
+        return res;
+    }
+    const AutotuneResult tuned = bayesian_autotune(space, benchmark, space.size() < 20 ? space.size() : 20,
+                                                   space.size() < 3 ? space.size() : 3);
+    res.best_schedule = tuned.best_schedule;
+    res.best_runtime = tuned.best_runtime;
+    res.total_benchmarks = tuned.total_benchmarks;
+    if (!(tuned.best_runtime < std::numeric_limits<double>::infinity())) return res;   // nothing could run
+    TensorToCodegenLowering lowering;
+    const CGModule cgm = lowering.lower(m, tuned.best_schedule);
+    if (last_lowering_status() != CG_B200_OK) return res;
+    res.executable = std::shared_ptr<Executable>(backend.compile(cgm).release());
+    if (res.executable) rt.kernel_cache().insert(key, res.executable);
+    return res;
+}
+
+}  // namespace b200
+
+// ---- KernelCache: the reference's file layout ----------------------------------------------------------
+u64 KernelCache::compute_key(const std::string& graph_text, const std::string& shapes, const std::string& dtypes,
+                             const std::string& hardware_name) {
+    u64 h = 0xcbf29ce484222325ULL;   // FNV-1a, 64 bit, over the four strings in order
+    for (const std::string* s : {&graph_text, &shapes, &dtypes, &hardware_name})
+        for (char c : *s) {
+            h ^= static_cast<u64>(static_cast<u8>(c));
+            h *= 0x100000001b3ULL;
+        }
+    return h;
+}
+
+namespace {
+constexpr u32 kCacheMagic = 0x454B4743;   // "CGKE"
+constexpr u32 kCacheVersion = 1;
+
+struct Reader {
+    std::ifstream& in;
+    template <typename T>
+    T num() {
+        T v{};
+        in.read(reinterpret_cast<char*>(&v), sizeof(T));
+        return v;
+    }
+    std::string str() {
+        const u64 len = num<u64>();
+        if (!in || len > (1ull << 32)) {   // a length no cache entry has: treat the file as damaged
+            in.setstate(std::ios::failbit);
+            return {};
+        }
+        std::string s(len, '\0');
+        in.read(s.data(), static_cast<std::streamsize>(len));
+        return s;
+    }
+};
+
+struct Writer {
+    std::ofstream& out;
+    template <typename T>
+    void num(T v) {
+        out.write(reinterpret_cast<const char*>(&v), sizeof(T));
+    }
+    void str(const std::string& s) {
+        num<u64>(s.size());
+        out.write(s.data(), static_cast<std::streamsize>(s.size()));
+    }
+};
+}  // namespace
+
+std::optional<std::shared_ptr<Executable>> KernelCache::lookup(u64 key) {
+    if (auto it = mem_cache_.find(key); it != mem_cache_.end()) return it->second;
+    namespace fs = std::filesystem;
+    const fs::path path = fs::path(dir_) / (std::to_string(key) + ".cgbin");
+    std::error_code ec;
+    if (!fs::exists(path, ec)) return std::nullopt;
+    std::ifstream in(path, std::ios::binary);
+    if (!in) return std::nullopt;
+    Reader r{in};
+    if (r.num<u32>() != kCacheMagic || r.num<u32>() != kCacheVersion) return std::nullopt;
+    auto exe = std::make_shared<Executable>();
+    exe->name = r.str();
+    exe->target_device.kind = static_cast<DeviceId::Kind>(r.num<u64>());
+    exe->target_device.index = r.num<u32>();
+    const std::string code = r.str();
+    exe->machine_code.assign(code.begin(), code.end());
+    exe->ptx_text = r.str();
+    exe->disassembly = r.str();
+    const u64 n_entry = r.num<u64>();
+    for (u64 i = 0; in && i < n_entry && i < (1u << 20); ++i) {
+        std::string name = r.str();
+        const u64 offset = r.num<u64>();
+        exe->entrypoints.push_back({std::move(name), offset});
+    }
+    exe->shared_mem_bytes = r.num<u64>();
+    exe->constant_mem_bytes = r.num<u64>();
+    exe->threads_per_block = r.num<u32>();
+    if (!in) return std::nullopt;   // truncated
+    mem_cache_[key] = exe;
+    return exe;
+}
+
+void KernelCache::insert(u64 key, std::shared_ptr<Executable> exe) {
+    if (!exe) return;
+    mem_cache_[key] = exe;
+    namespace fs = std::filesystem;
+    std::error_code ec;
+    fs::create_directories(dir_, ec);
+    std::ofstream out(fs::path(dir_) / (std::to_string(key) + ".cgbin"), std::ios::binary);
+    if (!out) return;
+    Writer w{out};
+    w.num<u32>(kCacheMagic);
+    w.num<u32>(kCacheVersion);
+    w.str(exe->name);
+    w.num<u64>(static_cast<u64>(exe->target_device.kind));
+    w.num<u32>(exe->target_device.index);
+    w.str(std::string(exe->machine_code.begin(), exe->machine_code.end()));
+    w.str(exe->ptx_text);
+    w.str(exe->disassembly);
+    w.num<u64>(exe->entrypoints.size());
+    for (const auto& [name, offset] : exe->entrypoints) {
+        w.str(name);
+        w.num<u64>(offset);
+    }
+    w.num<u64>(exe->shared_mem_bytes);
+    w.num<u64>(exe->constant_mem_bytes);
+    w.num<u32>(exe->threads_per_block);
+}
+
+// ---- Runtime ---------------------------------------------------------------------------------------------
+Runtime::Runtime() : cache_(".cantors_cache") {}
+Runtime::~Runtime() = default;
+
+void Runtime::add_device(std::unique_ptr<Device> d) {
+    if (d) devices_.push_back(std::move(d));
+}
+
+Device* Runtime::get_device(DeviceId id) const {
+    for (const auto& d : devices_)
+        if (d->id() == id) return d.get();
+    return nullptr;
+}
+
+std::unique_ptr<BoundExecutable> Runtime::bind(std::shared_ptr<Executable> exe, DeviceId device) {
+    if (!exe) return nullptr;
+    if (device.kind == DeviceId::Kind::CPU) {
+        if (exe->machine_code.empty() || exe->target_device.kind != DeviceId::Kind::CPU) return nullptr;
+        return std::make_unique<JitBoundExecutable>(std::move(exe));
+    }
+    if (device.kind != DeviceId::Kind::CUDA) return nullptr;
+    Device* dev = get_device(device);
+    if (!dev) return nullptr;
+    auto plan = b200::LaunchPlan::deserialize(exe->machine_code);
+    if (!plan) return nullptr;   // text-only executable (no fused kernel nodes): nothing to launch
+    auto bound = std::make_unique<CudaBoundExecutable>(std::move(exe), std::move(*plan), dev);
+    if (!bound->ok()) return nullptr;
+    return bound;
+}
+
+Runtime::CompileResult Runtime::compile_and_cache(u64 cache_key, const CGModule& cgm, MachineBackend& backend) {
+    CompileResult res;
+    if (auto hit = cache_.lookup(cache_key)) {
+        res.executable = *hit;
+        res.cache_hit = true;
+        return res;
+    }
+    res.executable = std::shared_ptr<Executable>(backend.compile(cgm).release());
+    if (res.executable) cache_.insert(cache_key, res.executable);
+    return res;
+}
+
+// The declared interface carries no module, so there is nothing to compile here (the reference's own
+// version stops at the same point): the search runs with the caller's benchmark function - for real
+// timings, cg::b200::make_gemm_benchmark - and its figures are returned. cg::b200::autotune_and_cache
+// is the form that also lowers and compiles with the winning schedule.
+Runtime::AutotuneResult Runtime::autotune_and_cache(u64 cache_key, const ScheduleSpace& space,
+                                                    const std::function<double(const Schedule&)>& benchmark,
+                                                    MachineBackend&) {
     AutotuneResult res;
     if (auto hit = cache_.lookup(cache_key)) {
         res.executable = *hit;
@@ -476,11 +581,6 @@ Runtime::AutotuneResult Runtime::autotune_and_cache(u64 cache_key, const Schedul
     const cg::AutotuneResult tuned = bayesian_autotune(space, benchmark);
     res.best_runtime = tuned.best_runtime;
     res.total_benchmarks = tuned.total_benchmarks;
-    res.best_schedule = tuned.best_schedule;
-    if (!(tuned.best_runtime < std::numeric_limits<double>::infinity()) || !lower_best) return res;   // nothing ran
-    const CGModule cgm = lower_best(tuned.best_schedule);
-    res.executable = std::shared_ptr<Executable>(backend.compile(cgm).release());
-    if (res.executable) cache_.insert(cache_key, res.executable);
     return res;
 }
 

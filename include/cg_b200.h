@@ -212,7 +212,9 @@ enum cg_b200_epilogue {
     CG_B200_EPI_BIAS_GELU_TANH = 3,
     CG_B200_EPI_BIAS_RESIDUAL = 4,   /* + bias[n] + residual[m, n]       */
     CG_B200_EPI_RESIDUAL = 5,        /* + residual[m, n]                 */
-    CG_B200_EPI_SCALE = 6            /* * alpha                          */
+    CG_B200_EPI_SCALE = 6,           /* * alpha                          */
+    CG_B200_EPI_RELU = 7,            /* relu(A x B), no bias             */
+    CG_B200_EPI_GELU_TANH = 8        /* gelu_tanh(A x B), no bias        */
 };
 
 enum cg_b200_compute {

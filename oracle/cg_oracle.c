@@ -334,8 +334,8 @@ static void gemm_range(int64_t lo, int64_t hi, void* p) {
             float v = accf[n];
             if (epi == CG_B200_EPI_SCALE) v = v * d->alpha;
             if (need_bias) v = v + load_as_f32(c->bias, d->out_dtype, (size_t)n);
-            if (epi == CG_B200_EPI_BIAS_RELU) v = v > 0.0f ? v : 0.0f;
-            if (epi == CG_B200_EPI_BIAS_GELU_TANH) v = op_gelu_tanh(v);
+            if (epi == CG_B200_EPI_BIAS_RELU || epi == CG_B200_EPI_RELU) v = v > 0.0f ? v : 0.0f;
+            if (epi == CG_B200_EPI_BIAS_GELU_TANH || epi == CG_B200_EPI_GELU_TANH) v = op_gelu_tanh(v);
             if (need_res) v = v + load_as_f32(c->residual, d->out_dtype, crow + (size_t)n);
             store_from_f32(c->C, d->out_dtype, crow + (size_t)n, v);
         }

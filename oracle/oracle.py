@@ -179,7 +179,7 @@ def eltwise(desc, inputs, n):
 
 # ---- gemm ------------------------------------------------------------------------------------
 EPI = {"none": 0, "bias": 1, "bias_relu": 2, "bias_gelu_tanh": 3, "bias_residual": 4,
-       "residual": 5, "scale": 6}
+       "residual": 5, "scale": 6, "relu": 7, "gelu_tanh": 8}
 
 
 def make_gemm_desc(M, N, K, in_dtype, out_dtype, epilogue="none", batch=1, b_transposed=0,

@@ -102,7 +102,7 @@ def test_bf16_gemm_tail_half_tiles(ops, cgb, oracle, b_transposed):
     assert_close(got, want, 1e-2, f"tail halves bT={b_transposed}")
 
 
-@pytest.mark.parametrize("epilogue", ["bias", "bias_relu", "bias_gelu_tanh", "bias_residual", "residual", "scale"])
+@pytest.mark.parametrize("epilogue", ["bias", "bias_relu", "bias_gelu_tanh", "bias_residual", "residual", "scale", "relu", "gelu_tanh"])
 @pytest.mark.parametrize("out_name", ["BF16", "F32"])
 def test_bf16_gemm_epilogues(ops, cgb, oracle, epilogue, out_name):
     capi = cgb.capi
