@@ -531,7 +531,9 @@ class BlockWorkload(Workload):
         return {"workload": "cfg5: pre-LN transformer encoder block, bf16, batch 32, seq 2048, d_model 1024, 16 heads, "
                             "FFN 4096, GELU(tanh), weights ~N(0,0.02)",
                 "l2": "activations (over 6 GiB per step) larger than L2",
-                "parallelism": "1 GPU" if world == 1 else f"batch-sharded x{world}, y gathered by the last GEMM's peer stores"}
+                "parallelism": "1 GPU" if world == 1 else f"batch-sharded x{world}, y gathered by the last GEMM's peer stores",
+                "driver": "Tensor-IR graph -> TensorToCodegenLowering -> NvidiaBackend -> Runtime.bind -> BoundExecutable.launch"
+                if getattr(self, "graph", None) is not None else "C-ABI calls from cantors_gift_b200.transformer (host layer not built)"}
 
     def setup(self, rank, world):
         import torch
@@ -551,6 +553,14 @@ class BlockWorkload(Workload):
         self.y = torch.empty(self.B, self.S, D, device="cuda", dtype=torch.bfloat16)
         self.comm, self.gather = None, None
         self.launches_per_step = self.block.launches_per_forward
+        # The step goes through the reference's own interfaces when the host layer is built: the block as a
+        # Tensor-IR graph -> TensorToCodegenLowering -> NvidiaBackend -> Runtime.bind -> BoundExecutable.launch.
+        # Otherwise the same seven C-ABI calls are issued from cantors_gift_b200.transformer.
+        self.graph = None
+        try:
+            self.graph = GraphBlock(self, torch.cuda.current_device())
+        except ImportError as e:
+            self.graph_unavailable = str(e).split(";")[0]
         if world > 1 and os.environ.get("CG_B200_BENCH_ALLGATHER", "fused") == "nccl":
             self.comm = make_comm(rank, world)
         elif world > 1:
@@ -564,18 +574,26 @@ class BlockWorkload(Workload):
                        "peer_barrier_create")
             self.gather = (raw[0], tables[0], world, rank)
             self.launches_per_step += 1   # the flag barrier
+            if self.graph is not None:
+                self.graph.gather_into(raw[0].value, [tables[0][r] for r in range(world)], world, rank)
 
     def step(self, i):
         import ctypes as C
         import torch
         from cantors_gift_b200 import capi
         if self.gather is not None:
-            self.block.forward(self.x, gather=self.gather)
+            if self.graph is not None:
+                self.graph.launch(self.x, None)
+            else:
+                self.block.forward(self.x, gather=self.gather)
             capi.check(capi.lib().cg_b200_peer_barrier(self.barrier, C.c_void_p(torch.cuda.current_stream().cuda_stream)),
                        "peer_barrier")
             return
         ys = self.y[self.rank * self.Bs:(self.rank + 1) * self.Bs]
-        self.block.forward(self.x, out=ys)
+        if self.graph is not None:
+            self.graph.launch(self.x, ys)
+        else:
+            self.block.forward(self.x, out=ys)
         if self.comm is not None:
             capi.check(capi.lib().cg_b200_allgather_inplace(self.comm, C.c_void_p(self.y.data_ptr()), ys.numel() * 2,
                                                             C.c_void_p(torch.cuda.current_stream().cuda_stream)),
@@ -637,8 +655,12 @@ class BlockWorkload(Workload):
             capi.check(L.cg_b200_memcpy_h2d(C.c_void_p(dx + i * nb), C.c_void_p(hx + i * nb), nb, s), "h2d")
 
         def compute(i, s):
-            self.block.forward(self.d_x[i * per:(i + 1) * per], out=self.d_y[i * per:(i + 1) * per],
-                               stream=torch.cuda.ExternalStream(s.value))
+            if self.graph is not None:
+                self.graph.launch(self.d_x[i * per:(i + 1) * per], self.d_y[i * per:(i + 1) * per],
+                                  stream=torch.cuda.ExternalStream(s.value))
+            else:
+                self.block.forward(self.d_x[i * per:(i + 1) * per], out=self.d_y[i * per:(i + 1) * per],
+                                   stream=torch.cuda.ExternalStream(s.value))
 
         def copy_out(i, s):
             capi.check(L.cg_b200_memcpy_d2h(C.c_void_p(hy + i * nb), C.c_void_p(dy + i * nb), nb, s), "d2h")
@@ -666,6 +688,61 @@ class BlockWorkload(Workload):
 
 WORKLOADS = {"block": BlockWorkload, "gemm": GemmWorkload, "eltwise": EltwiseWorkload, "rowreduce": RowReduceWorkload,
              "matmul_f32": MatmulF32Workload}
+
+
+class GraphBlock:
+    """The encoder block compiled from its Tensor-IR graph and bound through the reference's Runtime."""
+
+    def __init__(self, w, device_index):
+        import torch
+        from cantors_gift_b200 import graphs
+        cg, ext = graphs.host_modules()
+        self.cg, self.ext, self.dev = cg, ext, device_index
+        self.rt = cg.Runtime()
+        if not ext.add_cuda_device(self.rt, device_index):
+            raise RuntimeError("no usable sm_100 device for the host layer")
+        self.w = w
+        self.bound = {}
+        blk = w.block
+        # weights stored [out, in] and read through a transpose in the graph: the K-contiguous operand layout
+        self.weights = [blk._wt["qkv"], blk._wt["o"], blk._wt["1"], blk.b_1, blk._wt["2"], blk.b_2]
+        self.stream_of = {}
+        self._t = lambda t: ext.Tensor.from_ptr(t.data_ptr(), list(t.shape), cg.DType.BF16, device_index)  # noqa: E731
+        self.wt = [self._t(t) for t in self.weights]
+        self.gather = None
+        self._bind(w.Bs)
+        torch.cuda.synchronize()
+
+    def _bind(self, batch):
+        from cantors_gift_b200 import graphs
+        w = self.w
+        exe = graphs.compile_for_b200(self.cg, self.ext, graphs.encoder_block_graph(
+            self.cg, batch, w.S, w.D, w.H, w.F, self.cg.DType.BF16, weights_out_in=True))
+        assert self.ext.plan_summary(exe) == ["layernorm", "gemm", "attention", "gemm", "layernorm", "gemm", "gemm"]
+        b = self.ext.bind(self.rt, exe, self.dev)
+        if b is None:
+            raise RuntimeError("Runtime.bind returned None")
+        self.bound[batch] = b
+        return b
+
+    def gather_into(self, y_full_ptr, peer_ptrs, world, rank):
+        st = self.bound[self.w.Bs].set_output_gather([int(p) for p in peer_ptrs], world, rank)
+        if st != 0:
+            raise RuntimeError("set_output_gather: " + self.ext.status_string(st))
+        self.gather = self.ext.Tensor.from_ptr(int(y_full_ptr), [self.w.B, self.w.S, self.w.D], self.cg.DType.BF16, self.dev)
+
+    def launch(self, x, y, stream=None):
+        import torch
+        s = torch.cuda.current_stream() if stream is None else stream
+        h = self.stream_of.get(s.cuda_stream)
+        if h is None:
+            h = self.stream_of[s.cuda_stream] = self.ext.wrap_stream(s.cuda_stream, self.dev)
+        batch = x.shape[0]
+        b = self.bound.get(batch) or self._bind(batch)
+        out = self.gather if y is None else self._t(y)
+        st = b.launch([self._t(x)] + self.wt, [out], h)
+        if st != 0:
+            raise RuntimeError("launch: " + self.ext.status_string(st))
 
 
 def device_bytes_to_host(dev_ptr, nbytes):
