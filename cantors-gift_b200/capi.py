@@ -129,6 +129,9 @@ SIGNATURES = {
     "cg_b200_ipc_open": (_i, [_vp, _vpp]),
     "cg_b200_ipc_close": (_i, [_vp]),
     "cg_b200_gemm_allgather": (_i, [C.POINTER(GemmDesc), _vp, _vp, _vp, _vp, _vp, _vpp, _i, _i, _vp, _sz, _vp]),
+    "cg_b200_gemm_allgather_sync": (_i, [C.POINTER(GemmDesc), C.POINTER(GemmTuning), _vp, _vp, _vp, _vp, _vp, _vpp, _i, _i, _vp,
+                                         _vp, _sz, _vp]),
+    "cg_b200_peer_push": (_i, [_vp, _vpp, _i, _i, _sz, _vp, _vp]),
 }
 
 _lib = None

@@ -5,27 +5,30 @@
 // the path - matmul, softmax, matmul (src/ir/ops.cpp) - whose [B, H, S, S] intermediate makes three
 // trips through HBM. Here the scores never leave the SM.
 //
-// A work unit is (batch, head, 256 query rows = two query tiles); persistent CTAs of 320 threads, one per
+// A work unit is (batch, head, 256 query rows = two query tiles); persistent CTAs of 384 threads, one per
 // SM, take units blockIdx.x, blockIdx.x + gridDim.x, ... and carry the whole pipeline - K/V ring, score
 // buffers, barrier phases - across units, so the loads and the first scores of the next unit are under
 // way while the softmax groups finish the current one (no fill and drain per unit; the Q tiles are
 // double-buffered for that). Both query tiles meet each
 // K/V tile while it is in shared memory, which halves the K/V traffic from L2 - the first limit of a
 // one-tile CTA at head_dim 64. Work item w = 2 j + g is (key tile j, query tile g):
-//   warp 0     TMA: the two Q tiles of a unit, then K and V tiles of 128 key rows through a 5-stage ring
-//   warp 1     issues S_w = Q_g K_j^T (128 x 128 x 64) into TMEM score buffer w%3 and
-//              T_w = P_w V_j (128 x 64 x 128, P_w read from TMEM) into TMEM output-tile buffer g.
-//              The warp runs its loop converged and one elected lane issues, which keeps descriptors
-//              and addresses in uniform registers. S_{w+3} is issued right behind T_w, so the scores
-//              of a group's next item are complete before the group asks for them.
-//   warps 2-5  softmax group 0: query tile 0;  warps 6-9  softmax group 1: query tile 1.
-//              One thread per query row, so no exchange between threads: pass 1 reads the 128 scores
-//              of the row from TMEM for the row max, pass 2 reads them again, p = 2^(s - m), row sum,
-//              and writes P_w as bf16/f16 pairs over the first 64 columns of the same score buffer
-//              (the writes trail the reads). Running output row in registers:
-//              O = O * 2^(m_old - m_new) + T_w. The two warps that share a scheduler belong to
-//              different groups, i.e. to different items in different phases: one runs its
-//              exponentials while the other loads, reduces or waits.
+//   warp 8     TMA: the two Q tiles of a unit, then K and V tiles of 128 key rows through a 5-stage ring
+//   warp 9     issues S_w = Q_g K_j^T (128 x 128 x 64) into TMEM score buffer w%3 and
+//              O_g += P_w V_j (128 x 64 x 128, P_w read from TMEM) into the TMEM output accumulator of
+//              query tile g (the first product of a unit starts it). The warp runs its loop converged
+//              and one elected lane issues, which keeps descriptors and addresses in uniform
+//              registers. S_{w+3} is issued right behind the product of item w, so the scores of a
+//              group's next item are complete before the group asks for them.
+//   warps 0-3  softmax group 0: query tile 0;  warps 4-7  softmax group 1: query tile 1 (two whole
+//              warpgroups, which take the registers the third one gives up: 232 per thread).
+//              One thread per query row, so no exchange between threads: the row's 128 scores are read
+//              from TMEM once into registers, row max, p = 2^(s - m), row sum, and P_w is written as
+//              bf16/f16 pairs over the first 64 columns of the same score buffer. m is a reference
+//              maximum that follows the running maximum only when that has grown by more than 2^8, so
+//              the output accumulator in tensor memory is rescaled (O *= 2^(m_old - m_new), by the row's
+//              own thread) only on those rare occasions instead of on every key tile. The two warps that
+//              share a scheduler belong to different groups, i.e. to different items in different
+//              phases: one runs its exponentials while the other loads, reduces or waits.
 // Q, K, V are read in place from strided buffers (head = 64 contiguous columns of a row), so the
 // packed [rows, 3*d_model] output of a QKV projection needs no reshuffle. head_dim is 64.
 // The exponentials are the bound at this head size (one MUFU.EX2 per score).
@@ -45,12 +48,20 @@ constexpr int kAttnBN = 128;          // key rows per step
 constexpr int kAttnD = 64;            // head dim: 128 bytes of bf16 = one swizzle span
 constexpr int kAttnKVStages = 5;
 constexpr int kAttnSBufs = 3;
-constexpr int kAttnThreads = 320;
+constexpr int kAttnThreads = 384;        // three warpgroups: softmax group 0, softmax group 1, {TMA, MMA, two idle warps}
+constexpr int kAttnTmaWarp = 8, kAttnMmaWarp = 9;
+// Registers per thread after the warpgroups re-divide the register file. The kernel is launched with
+// 168 per thread (65536 / 384, rounded down to a multiple of 8); an increase waits in hardware, without
+// a time limit, until that many registers are free, so the new shares must fit in what the launch
+// allocated: 2 x 128 x 216 + 128 x 72 = 64512 = 384 x 168.
+constexpr int kAttnLaunchRegs = 168, kAttnSoftmaxRegs = 216, kAttnIssueRegs = 72;
+static_assert(2 * 128 * kAttnSoftmaxRegs + 128 * kAttnIssueRegs <= kAttnThreads * kAttnLaunchRegs,
+              "the re-divided register shares exceed the launch allocation: setmaxnreg.inc would never return");
 constexpr int kAttnTileBytes = 128 * 128;                 // a 128-row x 128-byte tile (Q, K or V)
 constexpr int kAttnSmem = 2 * 2 * kAttnTileBytes + kAttnKVStages * 2 * kAttnTileBytes + 1024;
 constexpr uint32_t kAttnTmemCols = 512;
 constexpr uint32_t kAttnSCol = 0;     // three score buffers of 128 columns; P over the first 64 of each
-constexpr uint32_t kAttnTCol = 384;   // two output-tile buffers of 64 columns
+constexpr uint32_t kAttnTCol = 384;   // two output accumulators (one per query tile) of 64 columns
 
 struct AttnParams {
     long long S_q, S_kv;
@@ -101,11 +112,13 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     // unit -> (batch, head, query rows): query tile fastest, so that the CTAs running at one time work on
     // few heads and share their K, V in L2
     struct Unit { int q0, h, b; };
-    auto decode = [&](long long unit) {
+    auto decode = [&](long long unit) {   // unit < 2^31 (checked on the host): 32-bit divisions
         Unit u;
-        u.q0 = (int)(unit % p.q_tiles) * kAttnQRows;
-        u.h = (int)((unit / p.q_tiles) % p.H);
-        u.b = (int)(unit / ((long long)p.q_tiles * p.H));
+        const uint32_t un = (uint32_t)unit, qt = (uint32_t)p.q_tiles, hh = (uint32_t)p.H;
+        const uint32_t rest = un / qt;
+        u.q0 = (int)(un - rest * qt) * kAttnQRows;
+        u.b = (int)(rest / hh);
+        u.h = (int)(rest - (uint32_t)u.b * hh);
         return u;
     };
     const int n_tiles = p.kv_tiles;
@@ -129,7 +142,7 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 1) {
+    if (warp == kAttnMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_u32(&tmem_base_slot)), "r"(kAttnTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -139,7 +152,12 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
 
-    if (warp == 0) {
+    // Registers follow the work: the softmax warpgroups hold a row of 128 scores per thread, the third
+    // warpgroup only issues copies and MMAs. Each role re-sizes its warpgroup's share of the register file
+    // as it enters its branch (see kAttnSoftmaxRegs / kAttnIssueRegs).
+    if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kAttnIssueRegs));   // one instruction for the whole third warpgroup
+    if (warp == kAttnTmaWarp) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             uint32_t k = 0;          // units this CTA has started
@@ -170,15 +188,15 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == kAttnMmaWarp) {
         // ---------------- MMA issuer ----------------
         // The whole warp runs the loop and waits; one elected lane issues (see elect_one()).
         // Items are numbered through all units of this CTA: W = k * n_items + 2 j + g. S_W goes into score
         // buffer W%3. The tensor pipe runs its instructions in issue order, and S_W is issued behind
         // T_{W-3}, the last reader of that buffer (P_{W-3} lives in it). Positions are kept as small
         // rotating counters: "s" for the scores being issued (three items ahead), "t" for the T behind.
-        long long my_units = p.units > (long long)blockIdx.x ? (p.units - 1 - blockIdx.x) / gridDim.x + 1 : 0;
-        const long long total = my_units * n_items;
+        const uint32_t my_units = (uint32_t)p.units > blockIdx.x ? ((uint32_t)p.units - 1u - blockIdx.x) / gridDim.x + 1u : 0u;
+        const long long total = (long long)my_units * n_items;
         struct Pos {
             int w;          // item within the unit
             uint32_t k;     // unit count
@@ -231,13 +249,13 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             const int g = pt.w & 1;
             // operands of the scores issued behind T_W
             if (issued_s < total && !prep_s(ps)) break;
-            // P_W is written and S_W read for the last time; before that the group took its previous
-            // T out of the output-tile buffer
+            // P_W is written and S_W read for the last time (and, for a unit's first item, the group has
+            // taken the previous unit's output out of its accumulator)
             bool ready = mbar_wait_poll(smem_u32(&bar_p_full[g]), tiles_done[g] & 1u, &abort_flag, p.err_word, 0x620u + g);
             ready = __all_sync(0xffffffffu, ready);
             if (!ready) break;
             tc_fence_after();
-            // T_W = P_W V_j: A = P_W in tensor memory, B = V_j ([key, d] with d contiguous: MN-major)
+            // O_g += P_W V_j: A = P_W in tensor memory, B = V_j ([key, d] with d contiguous: MN-major)
             const uint32_t tmem_p = tmem_base + kAttnSCol + (uint32_t)(pt.sb * kAttnBN);
             const uint32_t vb = s_kv + pt.st * 2 * kAttnTileBytes + kAttnTileBytes;
             const uint32_t tmem_t = tmem_base + kAttnTCol + (uint32_t)(g * kAttnD);
@@ -245,7 +263,7 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {   // 16 keys per MMA: 8 columns of P
                     const uint64_t db = make_smem_desc(vb + k * 2048, kAttnTileBytes, 1024);
-                    umma_ts(tmem_t, tmem_p + k * 8, db, p.idesc_t, k > 0 ? 1u : 0u);
+                    umma_ts(tmem_t, tmem_p + k * 8, db, p.idesc_t, (k > 0 || pt.w >= 2) ? 1u : 0u);   // O += P V; the unit's first product starts O
                 }
                 tc_commit<1>(smem_u32(&bar_t_full[g]));
                 if (g == 1) tc_commit<1>(smem_u32(&bar_kv_empty[pt.st]));   // both query tiles are through with the stage
@@ -259,50 +277,39 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 ++issued_s;
             }
         }
+    }   // (warps 10 and 11 have no role)
     } else {
-        // ---------------- softmax + output accumulation ----------------
-        // One thread per query row. (Two threads per row, sixteen softmax warps, was tried: the exchange of
-        // the row maximum and the tighter register budget cost more than the extra warps hid.)
-        constexpr int kKeys = kAttnBN, kCols = kAttnD, kChunks = kKeys / 32;
+        // ---------------- softmax; the output accumulates in tensor memory ----------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kAttnSoftmaxRegs));
+        // One thread per query row. The whole row of 128 scores is held in registers (one pass over
+        // tensor memory), p = 2^(s * scale * log2e - m) with m the row's REFERENCE maximum: it follows the
+        // true running maximum only when that has grown by more than 2^8 since m was last set, so P stays
+        // below 256 (exact in bf16 / f16 range, the row sum is fp32) and the output accumulator O - which
+        // the tensor cores add every P V product into, in tensor memory - has to be rescaled only on those
+        // rare occasions. A rescale is decided per warp (the tensor-memory loads and stores are warp-wide):
+        // O_row *= 2^(m_old - m_new), l *= the same, after the group's previous P V has completed.
+        constexpr int kKeys = kAttnBN, kCols = kAttnD;
+        constexpr float kGrowth = 8.0f;       // log2 of the largest P that is tolerated before m moves
         const int q = warp & 3;               // TMEM lane quarter this warp may access
-        const int g = (warp - 2) >> 2;        // group = query tile
+        const int g = warp >> 2;              // group = query tile = warpgroup
         const int row = q * 32 + lane;
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
-        const uint32_t t_addr = tmem_base + lane_base + kAttnTCol + (uint32_t)(g * kAttnD);
-        float o[kCols];
-        float m, l, alpha_prev;
+        const uint32_t o_addr = tmem_base + lane_base + kAttnTCol + (uint32_t)(g * kAttnD);
+        float m, l;
         bool ok = true;
         int sb = g;               // score buffer of the group's next item (items g, g+2, g+4, ... mod 3) and
         uint32_t sb_phase = 0;    // the parity of that buffer's current use
         uint32_t tcount = 0;      // key tiles this group has finished, over all units
-        auto add_tile = [&](uint32_t use) -> bool {   // o = o * alpha_prev + T (the group's last tile)
+        auto wait_pv = [&](uint32_t use) -> bool {   // the group's P V product number `use` has completed
             bool w = mbar_wait_poll(smem_u32(&bar_t_full[g]), use & 1u, &abort_flag, p.err_word, 0x660u + g);
             w = __all_sync(0xffffffffu, w);
-            if (!w) return false;
-            tc_fence_after();
-            const float2 a2 = make_float2(alpha_prev, alpha_prev);
-            float t[kCols / 32][32];
-#pragma unroll
-            for (int c = 0; c < kCols / 32; ++c) tmem_ld32_issue(t_addr + c * 32, t[c]);
-#pragma unroll
-            for (int c = 0; c < kCols / 32; ++c) {
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float2 r = __ffma2_rn(make_float2(o[c * 32 + i], o[c * 32 + i + 1]), a2, make_float2(t[c][i], t[c][i + 1]));
-                    o[c * 32 + i] = r.x;
-                    o[c * 32 + i + 1] = r.y;
-                }
-            }
-            return true;
+            if (w) tc_fence_after();
+            return w;
         };
         for (long long unit = blockIdx.x; ok && unit < p.units; unit += gridDim.x) {
             const Unit u = decode(unit);
-#pragma unroll
-            for (int i = 0; i < kCols; ++i) o[i] = 0.0f;
             m = -INFINITY;
             l = 0.0f;
-            alpha_prev = 0.0f;
             for (int j = 0; ok && j < n_tiles; ++j) {
                 const uint32_t s_addr = tmem_base + lane_base + kAttnSCol + (uint32_t)(sb * kAttnBN);
                 bool ready = mbar_wait_poll(smem_u32(&bar_s_full[sb]), sb_phase, &abort_flag, p.err_word, 0x670u + sb);
@@ -311,77 +318,91 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 tc_fence_after();
                 const long long kv0 = (long long)j * kAttnBN;
                 const bool ragged = kv0 + kKeys > p.S_kv;   // keys past S_kv are zero-filled rows of K
-                // pass 1: row maximum over the 128 keys of the tile
-                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;   // four chains
-                {
-                    float s[2][32];
-                    tmem_ld32_issue(s_addr, s[0]);
-                    tmem_ld32_issue(s_addr + 32, s[1]);
+                float s[kKeys / 32][32];
 #pragma unroll
-                    for (int c = 0; c < kChunks; ++c) {
-                        float (&cur)[32] = s[c & 1];
-                        tmem_ld_wait();
-                        if (ragged) {   // only the last key tile: mask the zero-filled keys
-                            const int valid = (int)(p.S_kv - kv0) - c * 32;
+                for (int c = 0; c < kKeys / 32; ++c) tmem_ld32_issue(s_addr + c * 32, s[c]);
+                tmem_ld_wait();
+                if (ragged) {   // only the last key tile: mask the zero-filled keys
 #pragma unroll
-                            for (int i = 0; i < 32; ++i)
-                                if (i >= valid) cur[i] = -INFINITY;
-                        }
-#pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            mx0 = fmax3(mx0, cur[i], cur[i + 1]);
-                            mx1 = fmax3(mx1, cur[i + 2], cur[i + 3]);
-                            mx2 = fmax3(mx2, cur[i + 4], cur[i + 5]);
-                            mx3 = fmax3(mx3, cur[i + 6], cur[i + 7]);
-                        }
-                        if (c + 2 < kChunks) tmem_ld32_issue(s_addr + (c + 2) * 32, cur);
-                    }
-                }
-                const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));   // finite: a tile holds at least one key
-                const float m_new = fmaxf(m, mx * p.scale_log2e);
-                const float alpha = (m == -INFINITY) ? 0.0f : ex2_approx(m - m_new);
-                // the previous tile, out of the T buffer before T_w is issued into it
-                if (j >= 1) {
-                    ok = add_tile(tcount - 1u);
-                    if (!ok) break;
-                }
-                // pass 2: p = 2^(s * scale * log2e - m_new). Pairs of keys per instruction where the ISA allows
-                // it (fp32x2 fma / add, packed convert). P goes over the first 64 columns of the score buffer:
-                // chunk c is written to columns 16c.. after columns up to 32c+31 have been read, and the chunk
-                // loaded ahead lies further right still.
-                float2 l2 = make_float2(0.0f, 0.0f);
-                const float2 sc2 = make_float2(p.scale_log2e, p.scale_log2e), nm2 = make_float2(-m_new, -m_new);
-                float s[2][32];
-                tmem_ld32_issue(s_addr, s[0]);
-#pragma unroll
-                for (int c = 0; c < kChunks; ++c) {
-                    float (&cur)[32] = s[c & 1];
-                    tmem_ld_wait();
-                    if (c + 1 < kChunks) tmem_ld32_issue(s_addr + (c + 1) * 32, s[(c + 1) & 1]);
-                    if (ragged) {
+                    for (int c = 0; c < kKeys / 32; ++c) {
                         const int valid = (int)(p.S_kv - kv0) - c * 32;
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
-                            if (i >= valid) cur[i] = -INFINITY;
+                            if (i >= valid) s[c][i] = -INFINITY;
                     }
+                }
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;   // four chains
+#pragma unroll
+                for (int c = 0; c < kKeys / 32; ++c) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        mx0 = fmax3(mx0, s[c][i], s[c][i + 1]);
+                        mx1 = fmax3(mx1, s[c][i + 2], s[c][i + 3]);
+                        mx2 = fmax3(mx2, s[c][i + 4], s[c][i + 5]);
+                        mx3 = fmax3(mx3, s[c][i + 6], s[c][i + 7]);
+                    }
+                }
+                // finite: a tile holds at least one key
+                const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2e;
+                bool pv_seen = j == 0;   // the group's previous P V is known to be complete (a unit's first item: waited at the end of the last unit)
+                if (j == 0) {
+                    m = mx;   // nothing accumulated yet: the first P V of the unit overwrites O
+                } else if (__any_sync(0xffffffffu, mx > m + kGrowth)) {
+                    // some row of this warp outgrew its reference maximum: bring O and l of the whole warp to the
+                    // rows' current maxima (factor 1 for rows that did not grow)
+                    ok = wait_pv(tcount - 1u);
+                    if (!ok) break;
+                    pv_seen = true;
+                    const float m_new = fmaxf(m, mx);
+                    const float alpha = ex2_approx(m - m_new);
+                    const float2 a2 = make_float2(alpha, alpha);
+                    // 32 columns at a time: the row of scores stays in registers meanwhile
+#pragma unroll 1
+                    for (int c = 0; c < kCols / 32; ++c) {
+                        float o[32];
+                        tmem_ld32(o_addr + c * 32, o);
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            const float2 r = __fmul2_rn(make_float2(o[i], o[i + 1]), a2);
+                            o[i] = r.x;
+                            o[i + 1] = r.y;
+                        }
+                        tmem_st32(o_addr + c * 32, reinterpret_cast<const uint32_t(&)[32]>(o));
+                    }
+                    l *= alpha;
+                    m = m_new;
+                }
+                // p = 2^(s * scale * log2e - m), two keys per instruction where the ISA allows it (fp32x2 fma /
+                // add, packed convert). P goes over the first 64 columns of the score buffer, two keys per column.
+                float2 l2 = make_float2(0.0f, 0.0f);
+                const float2 sc2 = make_float2(p.scale_log2e, p.scale_log2e), nm2 = make_float2(-m, -m);
+#pragma unroll
+                for (int c = 0; c < kKeys / 32; ++c) {
                     uint32_t pk[16];
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {   // two keys at a time
-                        const float2 t = __ffma2_rn(make_float2(cur[i], cur[i + 1]), sc2, nm2);
+                    for (int i = 0; i < 32; i += 2) {
+                        const float2 t = __ffma2_rn(make_float2(s[c][i], s[c][i + 1]), sc2, nm2);
                         const float2 ex = make_float2(ex2_approx(t.x), ex2_approx(t.y));   // 2^-inf = 0 for masked keys
                         l2 = __fadd2_rn(l2, ex);
                         pk[i >> 1] = pack_pair<T>(ex.x, ex.y);
                     }
-                    tmem_st16(s_addr + c * 16, pk);   // keys 32c .. 32c+31 of this row, two per column
+                    tmem_st16(s_addr + c * 16, pk);   // keys 32c .. 32c+31 of this row
                 }
-                // P is complete in tensor memory and the scores have been read for the last time
+                // P (and a rescaled O) are complete in tensor memory; the scores have been read
                 tmem_wait_st();
+                // A warp may not announce P of this item before the group's previous product has run: that
+                // product was issued only after all four warps of the group had announced their part of it, so
+                // this keeps a fast warp from arriving twice in one phase of the barrier (its arrival for this
+                // item counted in place of a slower warp's for the previous one). By now the product has
+                // normally long finished.
+                if (!pv_seen) {
+                    ok = wait_pv(tcount - 1u);
+                    if (!ok) break;
+                }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bar_p_full[g]));
-                l = fmaf(l, alpha, l2.x + l2.y);
-                alpha_prev = alpha;
-                m = m_new;
+                l += l2.x + l2.y;
                 ++tcount;
                 sb += 2;
                 if (sb >= kAttnSBufs) {
@@ -389,16 +410,23 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     sb_phase ^= 1u;
                 }
             }
-            if (ok && n_tiles > 0) ok = add_tile(tcount - 1u);
+            // the unit's output: O / l, once the last P V has landed
+            if (ok && n_tiles > 0) ok = wait_pv(tcount - 1u);
+            if (!ok) break;
+            float o[kCols / 32][32];
+#pragma unroll
+            for (int c = 0; c < kCols / 32; ++c) tmem_ld32_issue(o_addr + c * 32, o[c]);
+            tmem_ld_wait();
+            tc_fence_before();   // the loads are done before the group's next P arrival lets O be overwritten
             const long long qrow = (long long)u.q0 + g * kAttnBM + row;
-            if (ok && qrow < p.S_q) {
+            if (qrow < p.S_q) {
                 const float inv = l > 0.0f ? 1.0f / l : 0.0f;
                 T* orow = static_cast<T*>(p.O) + (long long)u.b * p.o_stride_b + (long long)u.h * p.o_stride_h + qrow * p.ldo;
 #pragma unroll
                 for (int gi = 0; gi < kCols / 8; ++gi) {
                     float e[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) e[i] = o[gi * 8 + i] * inv;
+                    for (int i = 0; i < 8; ++i) e[i] = o[gi >> 2][(gi & 3) * 8 + i] * inv;
                     const Vec16<T> o8 = pack16<T>(e);
                     *reinterpret_cast<int4*>(orow + gi * 8) = *reinterpret_cast<const int4*>(&o8);
                 }
@@ -413,7 +441,7 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == kAttnMmaWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kAttnTmemCols) : "memory");
     }
@@ -496,6 +524,7 @@ extern "C" int cg_b200_attention(const cg_b200_attention_desc* desc, const void*
     p.idesc_t = attn_idesc(d.dtype, true, kAttnD);
     p.err_word = device_error_word();
     p.units = (long long)p.q_tiles * p.H * p.B;
+    if (p.units > 0x7fffffffLL) return CG_B200_ERR_UNSUPPORTED;   // the kernel decodes a unit with 32-bit arithmetic
     const long long grid = p.units < sm_count() ? p.units : sm_count();   // one persistent CTA per SM
     cudaStream_t s = (cudaStream_t)stream;
     if (d.dtype == CG_B200_BF16) {

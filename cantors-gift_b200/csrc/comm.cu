@@ -59,41 +59,61 @@ struct Comm {
     void* token = nullptr;   // world * 8 bytes for cg_b200_comm_barrier
 };
 
-// ---- flag barrier over peer memory ------------------------------------------------------------------
-// One 64-bit slot per rank in every rank's flag buffer. A barrier is one tiny kernel: lane r
-// publishes this rank's epoch into rank r's buffer (release at system scope, after a system fence
-// that orders the preceding kernel's peer stores before it) and then waits, bounded, until rank r's
-// epoch has arrived in the local buffer. The kernels that wait on each other run on different GPUs.
-struct PeerBarrier {
-    unsigned long long* table_dev = nullptr;   // device copy of the `world` flag-buffer pointers
-    int world = 1, rank = 0;
-    unsigned long long epoch = 0;
-    unsigned long long wait_limit_ns = 2000000000ull;
-};
-
+// ---- flag barrier over peer memory (PeerBarrier, peer_flag_exchange: common.cuh) ---------------------
+// A barrier of its own is one tiny kernel: lane r handles peer r, after a system fence that orders the
+// preceding kernel's peer stores before the flags.
 __global__ void peer_barrier_kernel(unsigned long long* const* flags, int world, int rank, unsigned long long epoch,
                                     unsigned long long wait_limit_ns, uint32_t* err_word) {
     const int r = threadIdx.x;
     if (r >= world || r == rank) return;
     __threadfence_system();
-    unsigned long long* remote = flags[r] + rank;
-    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(remote), "l"(epoch) : "memory");
-    const unsigned long long* mine = flags[rank] + r;
-    unsigned long long t0 = 0, seen = 0;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-    for (uint32_t it = 0;; ++it) {
-        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(mine) : "memory");
-        if (seen >= epoch) break;
-        if ((it & 0x3f) == 0x3f) {
-            unsigned long long t1;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-            if (t1 - t0 > wait_limit_ns) {   // a peer never arrived: report and return
-                if (err_word) atomicCAS(err_word, 0u, 0x500u + (uint32_t)r);
-                break;
-            }
-            __nanosleep(100);
+    peer_flag_exchange(flags, rank, r, epoch, wait_limit_ns, err_word);
+}
+
+// Pushes `bytes` (a multiple of 16) from `src` into the same offset of up to 7 peer buffers: each 16-byte
+// packet is loaded once and stored to every peer. With a flag table it ends in the barrier: the last
+// CTA to finish publishes the epoch and waits for the peers'.
+struct PeerPointers {
+    int4* p[7];
+};
+
+__global__ void __launch_bounds__(512)
+peer_push_kernel(const int4* __restrict__ src, const PeerPointers peers, int n_peer, size_t packets,
+                 unsigned long long* const* flags, int world, int rank, unsigned long long epoch,
+                 unsigned long long wait_limit_ns, unsigned int* done_counter, uint32_t* err_word) {
+    __shared__ int4* dst[7];
+    __shared__ bool last;
+    if (threadIdx.x < 7) dst[threadIdx.x] = threadIdx.x < n_peer ? peers.p[threadIdx.x] : nullptr;
+    __syncthreads();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    constexpr int kUnroll = 4;   // independent loads in flight per thread
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + (kUnroll - 1) * stride < packets; i += kUnroll * stride) {
+        int4 v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) v[u] = __ldcs(src + i + u * stride);
+        for (int d = 0; d < n_peer; ++d) {
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) dst[d][i + u * stride] = v[u];
         }
     }
+    for (; i < packets; i += stride) {
+        const int4 v = __ldcs(src + i);
+        for (int d = 0; d < n_peer; ++d) dst[d][i] = v;
+    }
+    if (!flags) return;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int prev = atomicAdd(done_counter, 1u);
+        last = prev == gridDim.x - 1;
+        if (last) *done_counter = 0;   // every CTA has counted itself: ready for the next launch
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence_system();
+    const int r = threadIdx.x;
+    if (r < world && r != rank) peer_flag_exchange(flags, rank, r, epoch, wait_limit_ns, err_word);
 }
 
 }  // namespace cgb
@@ -111,11 +131,13 @@ extern "C" int cg_b200_peer_barrier_create(void** barrier, void* const* flag_buf
     PeerBarrier* b = new PeerBarrier;
     b->world = world;
     b->rank = rank;
-    if (cudaMalloc(&b->table_dev, 8 * sizeof(void*)) != cudaSuccess ||
+    // the flag table, then the done counter of the fused kernels, in one small allocation
+    if (cudaMalloc(&b->table_dev, 16 * sizeof(void*)) != cudaSuccess || cudaMemset(b->table_dev, 0, 16 * sizeof(void*)) != cudaSuccess ||
         cudaMemcpy(b->table_dev, flag_buffers, (size_t)world * sizeof(void*), cudaMemcpyHostToDevice) != cudaSuccess) {
         delete b;
         return CG_B200_ERR_CUDA;
     }
+    b->done_counter = reinterpret_cast<unsigned int*>(b->table_dev + 8);
     *barrier = b;
     return CG_B200_OK;
 }
@@ -127,6 +149,39 @@ extern "C" int cg_b200_peer_barrier(void* barrier, void* stream) {
     if (b->world == 1) return CG_B200_OK;
     peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(reinterpret_cast<unsigned long long* const*>(b->table_dev), b->world,
                                                              b->rank, b->epoch, b->wait_limit_ns, device_error_word());
+    CGB_CUDA(cudaGetLastError());
+    return CG_B200_OK;
+}
+
+extern "C" int cg_b200_peer_push(const void* src, void* const* peer_dst, int world, int rank, size_t bytes, void* barrier,
+                                 void* stream) {
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return CG_B200_ERR_INVALID_ARG;
+    if (bytes % 16) return CG_B200_ERR_INVALID_ARG;
+    PeerBarrier* b = static_cast<PeerBarrier*>(barrier);
+    if (b && (b->world != world || b->rank != rank)) return CG_B200_ERR_INVALID_ARG;
+    if (b) ++b->epoch;   // every rank calls with a barrier the same number of times, whatever its byte count
+    if (world == 1 || (bytes == 0 && !b)) return CG_B200_OK;
+    if (!peer_dst || (bytes && !src)) return CG_B200_ERR_NULL_POINTER;
+    if (!aligned_to(src, 16)) return CG_B200_ERR_MISALIGNED;
+    int st = require_sm100();
+    if (st) return st;
+    PeerPointers peers{};
+    int n = 0;
+    for (int r = 0; r < world; ++r) {
+        if (r == rank) continue;
+        if (!peer_dst[r]) return CG_B200_ERR_NULL_POINTER;
+        if (!aligned_to(peer_dst[r], 16)) return CG_B200_ERR_MISALIGNED;
+        peers.p[n++] = static_cast<int4*>(peer_dst[r]);
+    }
+    // a grid that fits beside a persistent compute kernel: at most one CTA of 512 threads per SM, fewer for
+    // small transfers (four packets per thread per pass)
+    const size_t packets = bytes / 16;
+    const size_t want = (packets + 512 * 4 - 1) / (512 * 4);
+    const size_t cap = (size_t)sm_count();
+    const unsigned grid = (unsigned)(want < 1 ? 1 : (want > cap ? cap : want));
+    peer_push_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(
+        static_cast<const int4*>(src), peers, n, packets, b ? reinterpret_cast<unsigned long long* const*>(b->table_dev) : nullptr,
+        world, rank, b ? b->epoch : 0ull, b ? b->wait_limit_ns : 0ull, b ? b->done_counter : nullptr, device_error_word());
     CGB_CUDA(cudaGetLastError());
     return CG_B200_OK;
 }

@@ -37,6 +37,44 @@ inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintp
 // Device error word shared by kernels with bounded waits (0 = no error).
 uint32_t* device_error_word();   // device pointer, lazily allocated per device; nullptr on failure
 
+// ---- flag barrier over peer memory ----------------------------------------------------------------
+// One 64-bit slot per rank in every rank's flag buffer. Rank `rank` publishes its epoch into slot `rank`
+// of rank r's buffer and waits, bounded, until rank r's epoch has arrived in slot r of its own buffer.
+// The kernels that wait on each other run on different GPUs.
+struct PeerBarrier {
+    unsigned long long* table_dev = nullptr;   // device copy of the `world` flag-buffer pointers
+    unsigned int* done_counter = nullptr;      // device word: CTAs of a fused kernel that have finished; returns to 0
+    int world = 1, rank = 0;
+    unsigned long long epoch = 0;
+    unsigned long long wait_limit_ns = 2000000000ull;
+};
+
+// What one thread does for one peer. Everything this GPU wrote to peer memory before the caller's
+// system fence is visible to the peer once it sees the epoch. A peer that never arrives is reported
+// (0x500 + its rank) and the wait ends.
+__device__ __forceinline__ void peer_flag_exchange(unsigned long long* const* flags, int rank, int r,
+                                                   unsigned long long epoch, unsigned long long wait_limit_ns,
+                                                   uint32_t* err_word) {
+    unsigned long long* remote = flags[r] + rank;
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(remote), "l"(epoch) : "memory");
+    const unsigned long long* mine = flags[rank] + r;
+    unsigned long long t0 = 0, seen = 0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (uint32_t it = 0;; ++it) {
+        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(mine) : "memory");
+        if (seen >= epoch) break;
+        if ((it & 0x3f) == 0x3f) {
+            unsigned long long t1;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (t1 - t0 > wait_limit_ns) {
+                if (err_word) atomicCAS(err_word, 0u, 0x500u + (uint32_t)r);
+                break;
+            }
+            __nanosleep(100);
+        }
+    }
+}
+
 // ---- device-side element conversion -----------------------------------------------------------
 template <typename T> struct Elem;
 template <> struct Elem<float> {

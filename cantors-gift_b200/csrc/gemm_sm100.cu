@@ -80,6 +80,13 @@ struct GemmParams {
     uint32_t idesc_half;   // instruction descriptor with N = BN / 2
     int tail_split;        // host side only: 0 = library default, 1 = off, 2 = on (cg_b200_gemm_tuning)
     uint32_t* err_word;
+    // Barrier folded into the kernel's tail (fused all-gather only; bar_flags == nullptr: none): every CTA
+    // counts itself on bar_done after its peer stores, the last one publishes this rank's epoch to the
+    // peers' flag buffers and waits, bounded, for theirs.
+    unsigned long long* const* bar_flags;
+    unsigned int* bar_done;
+    unsigned long long bar_epoch, bar_limit_ns;
+    int bar_world, bar_rank;
 };
 
 __device__ __forceinline__ float tanh_fast(float x) {
@@ -501,6 +508,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1u;
         }
+        if (p.bar_flags) __threadfence_system();   // this thread's peer stores, before the CTA counts itself done
     }
 
     // ---------------- teardown ----------------
@@ -513,6 +521,23 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
         else
             asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+    if (p.bar_flags) {
+        // The flag barrier of the fused all-gather, without a launch of its own: the last CTA of the grid
+        // to get here knows that every other CTA's peer stores are fenced, and speaks for the rank.
+        __shared__ bool last_cta;
+        if (threadIdx.x == 0) {
+            const unsigned int prev = atomicAdd(p.bar_done, 1u);
+            last_cta = prev == gridDim.x - 1;
+            if (last_cta) *p.bar_done = 0;   // every CTA has counted itself: ready for the next launch
+        }
+        __syncthreads();
+        if (last_cta) {
+            __threadfence_system();
+            const int r = (int)threadIdx.x;
+            if (r < p.bar_world && r != p.bar_rank)
+                peer_flag_exchange(p.bar_flags, p.bar_rank, r, p.bar_epoch, p.bar_limit_ns, p.err_word);
+        }
     }
 }
 
@@ -840,6 +865,7 @@ extern "C" int cg_b200_gemm_workspace_bytes(const cg_b200_gemm_desc* desc, size_
 struct PeerSet {
     void* const* peer_c = nullptr;   // `world` pointers to the peers' full C buffers (entry `rank` is skipped)
     int world = 1, rank = 0;
+    PeerBarrier* barrier = nullptr;  // folded into the kernel's tail when given
 };
 
 static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B, const void* bias,
@@ -904,6 +930,14 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
         p.dst_row_offset = (long long)peers->rank * d.M * d.ldc;
         for (int r = 0; r < peers->world; ++r)
             if (r != peers->rank) p.peer[p.n_peer++] = peers->peer_c[r];
+        if (PeerBarrier* b = peers->barrier) {
+            p.bar_flags = reinterpret_cast<unsigned long long* const*>(b->table_dev);
+            p.bar_done = b->done_counter;
+            p.bar_epoch = b->epoch;
+            p.bar_limit_ns = b->wait_limit_ns;
+            p.bar_world = b->world;
+            p.bar_rank = b->rank;
+        }
     }
     p.epilogue = epi; p.alpha = d.alpha;
     p.b_mn_major = (d.b_transposed || sp.active) ? 0 : 1;   // the fp32 workspace copy of B is K-contiguous
@@ -1103,4 +1137,35 @@ extern "C" int cg_b200_gemm_allgather(const cg_b200_gemm_desc* desc, const void*
     ps.world = world;
     ps.rank = rank;
     return gemm_run(desc, A, B, bias, residual, C_full, workspace, workspace_bytes, stream, true, nullptr, &ps);
+}
+
+extern "C" int cg_b200_gemm_allgather_sync(const cg_b200_gemm_desc* desc, const cg_b200_gemm_tuning* tuning, const void* A,
+                                           const void* B, const void* bias, const void* residual, void* C_full,
+                                           void* const* peer_C, int world, int rank, void* barrier, void* workspace,
+                                           size_t workspace_bytes, void* stream) {
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return CG_B200_ERR_INVALID_ARG;
+    if (!desc) return CG_B200_ERR_NULL_POINTER;
+    if (desc->batch != 1) return CG_B200_ERR_UNSUPPORTED;
+    PeerBarrier* b = static_cast<PeerBarrier*>(barrier);
+    if (b && (b->world != world || b->rank != rank)) return CG_B200_ERR_INVALID_ARG;
+    if (world > 1) {
+        if (!peer_C) return CG_B200_ERR_NULL_POINTER;
+        for (int r = 0; r < world; ++r)
+            if (r != rank && (!peer_C[r] || !aligned_to(peer_C[r], 16))) return peer_C[r] ? CG_B200_ERR_MISALIGNED : CG_B200_ERR_NULL_POINTER;
+    }
+    if (desc->M == 0 || desc->N == 0) {
+        // nothing to compute, but the other ranks still wait for this one at the barrier
+        return b ? cg_b200_peer_barrier(barrier, stream) : CG_B200_OK;
+    }
+    PeerSet ps;
+    ps.peer_c = peer_C;
+    ps.world = world;
+    ps.rank = rank;
+    if (b && world > 1) {
+        ++b->epoch;
+        ps.barrier = b;
+    }
+    const int st = gemm_run(desc, A, B, bias, residual, C_full, workspace, workspace_bytes, stream, true, nullptr, &ps, tuning);
+    if (st != CG_B200_OK && b && world > 1) --b->epoch;   // nothing was launched
+    return st;
 }

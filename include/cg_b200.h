@@ -362,6 +362,21 @@ int cg_b200_gemm_allgather(const cg_b200_gemm_desc* desc, const void* A, const v
                            const void* bias, const void* residual, void* C_full,
                            void* const* peer_C, int world, int rank, void* workspace,
                            size_t workspace_bytes, void* stream);
+/* The same with the tile choice open to the caller (`tuning`, may be NULL) and the barrier folded into the
+ * kernel (`barrier` from cg_b200_peer_barrier_create, may be NULL): the last CTA to finish publishes
+ * this rank's epoch and waits for the peers', so the call stands for cg_b200_gemm_allgather followed by
+ * cg_b200_peer_barrier without the second launch. Counts as one barrier call on the handle. */
+int cg_b200_gemm_allgather_sync(const cg_b200_gemm_desc* desc, const cg_b200_gemm_tuning* tuning,
+                                const void* A, const void* B, const void* bias, const void* residual,
+                                void* C_full, void* const* peer_C, int world, int rank, void* barrier,
+                                void* workspace, size_t workspace_bytes, void* stream);
+/* Copies `bytes` (a multiple of 16) from `src` to peer_dst[r] for every r != rank (entry `rank` is
+ * ignored): each 16-byte packet is read once and stored to all peers over NVLink by one kernel whose
+ * grid is small enough to run beside a compute kernel on another stream. With `barrier` (may be NULL)
+ * the kernel ends in the flag barrier, as above; everything pushed earlier on the same stream is then
+ * visible to the peers as well. For results that are gathered while later work still computes. */
+int cg_b200_peer_push(const void* src, void* const* peer_dst, int world, int rank, size_t bytes,
+                      void* barrier, void* stream);
 
 #if defined(__GNUC__)
 #pragma GCC visibility pop

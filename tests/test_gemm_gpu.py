@@ -257,6 +257,93 @@ def test_fused_allgather_writes_every_destination(ops, cgb, oracle):
     assert torch.equal(bufs[0], bufs[1]) and torch.equal(bufs[1], bufs[2])
 
 
+@pytest.mark.parametrize("tile_n,pair", [(0, 0), (128, 2), (128, 1), (64, 1)])
+def test_fused_allgather_with_the_barrier_in_its_tail(ops, cgb, oracle, tile_n, pair):
+    """cg_b200_gemm_allgather_sync on one GPU: the "peers" are local buffers, and their side of the flag
+    barrier is played by the host, which writes the epochs this rank will wait for into its flag buffer
+    before the launch. Checked: every destination holds the rows, the peers' flag buffers hold this
+    rank's epoch, a second call (epoch 2) works - so the kernel's CTA counter returned to zero - and
+    every tile choice gives the same bits."""
+    import torch
+    capi, O = cgb.capi, oracle
+    L = cgb.lib()
+    world, rank, M, N, K = 3, 1, 520, 392, 136
+    rng = np.random.default_rng(5)
+    A = O.to_bf16(rng.standard_normal((M, K), dtype=np.float32) * 0.05)
+    B = O.to_bf16(rng.standard_normal((K, N), dtype=np.float32) * 0.05)
+    bias = O.to_bf16(rng.standard_normal(N, dtype=np.float32))
+    od = O.make_gemm_desc(M, N, K, O.BF16, O.BF16, epilogue="bias_gelu_tanh")
+    want = O.from_bf16(O.gemm(od, A, B, bias=bias, out=np.zeros(M * N, dtype=np.uint16))).reshape(M, N)
+    dev = lambda h: torch.from_numpy(h.view(np.int16)).cuda().view(torch.bfloat16)  # noqa: E731
+    bufs = [torch.zeros(world * M, N, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    flags = [torch.zeros(8, dtype=torch.int64, device="cuda") for _ in range(world)]
+    flags[rank][:] = 2   # the peers' epochs 1 and 2 "have arrived"
+    peers = (C.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    ftab = (C.c_void_p * world)(*[f.data_ptr() for f in flags])
+    bar = C.c_void_p()
+    capi.check(L.cg_b200_peer_barrier_create(C.byref(bar), ftab, world, rank), "peer_barrier_create")
+    capi.check(L.cg_b200_peer_barrier_set_timeout(bar, 50_000_000), "set_timeout")
+    gd = capi.make_gemm_desc(M, N, K, capi.BF16, capi.BF16, epilogue="bias_gelu_tanh")
+    tuning = capi.GemmTuning(tile_n=tile_n, cta_pair=pair, tail_split=0, reserved=0)
+    Ad, Bd, bd = dev(A), dev(B), dev(bias)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    try:
+        for epoch in (1, 2):
+            for b in bufs:
+                b.zero_()
+            capi.check(L.cg_b200_gemm_allgather_sync(C.byref(gd), C.byref(tuning), C.c_void_p(Ad.data_ptr()),
+                                                     C.c_void_p(Bd.data_ptr()), C.c_void_p(bd.data_ptr()), None,
+                                                     C.c_void_p(bufs[rank].data_ptr()), peers, world, rank, bar, None, 0, stream),
+                       "gemm_allgather_sync")
+            assert ops.last_device_error() == 0, "the flag wait ran out"
+            for r in range(world):
+                if r != rank:
+                    assert int(flags[r][rank].item()) == epoch
+            full = _host_f32(O, bufs[0].view(-1), capi.BF16).reshape(world * M, N)
+            assert_close(full[rank * M:(rank + 1) * M], want, 1e-2, f"sync all-gather rows tile_n={tile_n} pair={pair}")
+            assert not full[:rank * M].any() and not full[(rank + 1) * M:].any()
+            assert torch.equal(bufs[0], bufs[1]) and torch.equal(bufs[1], bufs[2])
+        plain = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+        ops.gemm(gd, Ad, Bd, plain, bias=bd)
+        assert torch.equal(plain, bufs[0][rank * M:(rank + 1) * M])   # the sharded kernel's bits are the one-GPU kernel's
+    finally:
+        capi.check(L.cg_b200_peer_barrier_destroy(bar), "peer_barrier_destroy")
+
+
+def test_peer_push_copies_to_every_destination_and_ends_in_the_barrier(ops, cgb):
+    """cg_b200_peer_push with local stand-ins for the peers: odd sizes, the grid's tail loop, and the
+    barrier in the kernel's tail (peers' epochs pre-written by the host)."""
+    import torch
+    capi = cgb.capi
+    L = cgb.lib()
+    world, rank = 4, 2
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    flags = [torch.zeros(8, dtype=torch.int64, device="cuda") for _ in range(world)]
+    flags[rank][:] = 1
+    ftab = (C.c_void_p * world)(*[f.data_ptr() for f in flags])
+    bar = C.c_void_p()
+    capi.check(L.cg_b200_peer_barrier_create(C.byref(bar), ftab, world, rank), "peer_barrier_create")
+    capi.check(L.cg_b200_peer_barrier_set_timeout(bar, 50_000_000), "set_timeout")
+    try:
+        for n_bytes, with_barrier in ((16, False), (16 * 2049, False), (16 * (1 << 18) + 48, True)):
+            src = torch.randint(-128, 127, (n_bytes,), dtype=torch.int8, device="cuda")
+            dst = [torch.zeros(n_bytes + 32, dtype=torch.int8, device="cuda") for _ in range(world)]
+            tab = (C.c_void_p * world)(*[d.data_ptr() + 16 for d in dst])
+            capi.check(L.cg_b200_peer_push(C.c_void_p(src.data_ptr()), tab, world, rank, n_bytes, bar if with_barrier else None,
+                                           stream), "peer_push")
+            assert ops.last_device_error() == 0
+            for r in range(world):
+                if r == rank:
+                    assert not dst[r].any()                     # the rank's own entry is never written
+                else:
+                    assert torch.equal(dst[r][16:16 + n_bytes], src) and not dst[r][:16].any() and not dst[r][16 + n_bytes:].any()
+            if with_barrier:
+                assert all(int(flags[r][rank].item()) == 1 for r in range(world) if r != rank)
+        assert L.cg_b200_peer_push(None, None, world, rank, 24, None, stream) == capi.ERR_INVALID_ARG   # not a multiple of 16
+    finally:
+        capi.check(L.cg_b200_peer_barrier_destroy(bar), "peer_barrier_destroy")
+
+
 def test_k_zero_gives_epilogue_of_zero(ops, cgb, oracle):
     capi = cgb.capi
     got, want = run_case(ops, cgb, oracle, 130, 72, 0, capi.BF16, capi.BF16, epilogue="bias")
