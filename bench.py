@@ -732,6 +732,7 @@ class GraphBlock:
         self.gather = self.ext.Tensor.from_ptr(int(y_full_ptr), [self.w.B, self.w.S, self.w.D], self.cg.DType.BF16, self.dev)
 
     def launch(self, x, y, stream=None):
+        """y: a torch tensor, or None: the full-size y of the fused gather (gather_into)."""
         import torch
         s = torch.cuda.current_stream() if stream is None else stream
         h = self.stream_of.get(s.cuda_stream)
