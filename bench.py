@@ -347,7 +347,7 @@ class GemmWorkload(Workload):
             self.barrier = C.c_void_p()
             capi.check(capi.lib().cg_b200_peer_barrier_create(C.byref(self.barrier), flag_tables[0], world, rank),
                        "peer_barrier_create")
-        self.launches_per_step = 1 if self.in_dtype_name == "BF16" else 2
+        self.launches_per_step = 1   # fp32 too: the tf32 hi / lo split happens inside the GEMM kernel
 
     def step(self, i):
         import ctypes as C
@@ -509,7 +509,8 @@ class GemmWorkload(Workload):
 
 
 class MatmulF32Workload(GemmWorkload):
-    """fp32 M=N=K=1024 through the 3xTF32 split (latency-bound: about 2 GFLOP per launch)."""
+    """fp32 M=N=K=1024 through the 3xTF32 split, done inside the GEMM kernel (about 2 GFLOP per launch: bound by
+    the L2-to-SM operand traffic of 128 x 64 tiles and by launch latency, not by the tensor cores)."""
     name, dtype = "matmul_f32", "f32 (3xTF32)"
     M = N = K = 1024
     in_dtype_name, epilogue = "F32", "none"

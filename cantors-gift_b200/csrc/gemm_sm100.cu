@@ -46,6 +46,9 @@ constexpr int kRowBytes = 128;      // bytes of K per row per stage (one swizzle
 constexpr int kUmmaKBytes = 32;     // bytes of K one tcgen05.mma consumes per row
 constexpr int kThreads = 320;
 constexpr int kEpilogueWarps = 8;
+constexpr int kConvertWarps = 8;            // fp32 operands split inside the kernel: warps 10-17
+constexpr int kMaxOpStages = 4;             // operand stages the split warps fill ahead of the tensor cores (at most)
+constexpr int kThreadsConv = kThreads + 32 * kConvertWarps;
 constexpr int kEpilogueStagingBytes = kEpilogueWarps * 4096;   // 32 rows x 128 bytes per epilogue warp
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 224 * 1024;
@@ -116,6 +119,34 @@ __device__ __forceinline__ float2 gelu_pair_fast(float2 x) {
     return __ffma2_rn(h, make_float2(tanh_fast(u.x), tanh_fast(u.y)), h);
 }
 
+// hi = x with the low 13 mantissa bits cleared (exactly a tf32 value), lo = (x - hi) cleared the same way
+__device__ __forceinline__ void tf32_split(float x, float& h, float& l) {
+    h = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
+    l = __uint_as_float(__float_as_uint(x - h) & 0xffffe000u);
+}
+
+// The split as the tensor cores see it. A tf32 operand is read by its upper 19 bits, the 13 low mantissa bits
+// are ignored, so x itself stands for hi and (x - hi) for lo without clearing either; two values per
+// instruction (packed fp32 subtract).
+__device__ __forceinline__ void tf32_lo_pair(float x0, float x1, float& l0, float& l1) {
+    const uint32_t h0 = __float_as_uint(x0) & 0xffffe000u, h1 = __float_as_uint(x1) & 0xffffe000u;
+    uint64_t d;
+    asm("{\n\t.reg .b64 a, b;\n\t"
+        "mov.b64 a, {%1, %2};\n\t"
+        "mov.b64 b, {%3, %4};\n\t"
+        "sub.rn.f32x2 %0, a, b;\n\t}"
+        : "=l"(d)
+        : "r"(__float_as_uint(x0)), "r"(__float_as_uint(x1)), "r"(h0), "r"(h1));
+    l0 = __uint_as_float((uint32_t)d);
+    l1 = __uint_as_float((uint32_t)(d >> 32));
+}
+__device__ __forceinline__ float4 tf32_lo4(const float4& x) {
+    float4 l;
+    tf32_lo_pair(x.x, x.y, l.x, l.y);
+    tf32_lo_pair(x.z, x.w, l.z, l.w);
+    return l;
+}
+
 struct TileCoord {
     int b, m0, n0;
     int width;   // columns of this unit: bn, or bn / 2 for a tail half
@@ -141,27 +172,42 @@ __device__ __forceinline__ TileCoord decode_tile(long long unit, const GemmParam
 
 // kCopies: operand copies per stage (1, or 2 = hi and lo halves of the fp32 split)
 // BNL: rows (N) of B staged by one CTA = BN / kCta
-template <int kCopies, int BNL>
+// kConv: the in-kernel fp32 split. Two rings then: a deep one of RAW stages the copy engine fills (A and B as
+// they lie in memory, 128 bytes of K per row), and a short one of OPERAND stages the split warps write and the
+// tensor cores read: hi and lo parts of B in shared memory, hi and lo parts of A in tensor memory (64 columns
+// per stage behind the two accumulators), so that A costs no shared-memory bandwidth when the products run.
+template <int kCopies, int BNL, bool kConv = false>
 struct StageLayout {
     static constexpr int kABytes = kBM * kRowBytes;      // 16 KiB
     static constexpr int kBBytes = BNL * kRowBytes;
-    static constexpr int kStageBytes = kCopies * (kABytes + kBBytes);
-    static constexpr int kStagesFit = (kSmemBudget - kEpilogueStagingBytes) / kStageBytes;
+    static constexpr int kStageBytes = (kConv ? 1 : kCopies) * (kABytes + kBBytes);
+    // narrow tiles: the split warps take two k-blocks per trip (one wait for the tensor-memory stores, one proxy
+    // fence and one round of arrivals for both), which wants an even number of operand stages
+    static constexpr int kConvBatch = BNL <= 64 ? 2 : 1;
+    static constexpr int kOpStages = kConv ? (kConvBatch == 2 ? 4 : 3) : 0;
+    static constexpr int kOpBytes = kConv ? 2 * kBBytes : 0;
+    static constexpr int kStagesFit = (kSmemBudget - kEpilogueStagingBytes - kOpStages * kOpBytes) / kStageBytes;
     static constexpr int kStages = kStagesFit > kMaxStages ? kMaxStages : kStagesFit;
-    static constexpr int kDynSmem = kStages * kStageBytes + kEpilogueStagingBytes + 1024;   // + alignment slack
+    static constexpr int kMainBytes = kStages * kStageBytes + kOpStages * kOpBytes;
+    static constexpr int kDynSmem = kMainBytes + kEpilogueStagingBytes + 1024;   // + alignment slack
     static_assert(kStages >= 2, "at least a double buffer");
 };
 
-template <int kCta, bool kTF32, bool kSplit, int BN, typename OutT>
-__global__ void __launch_bounds__(kThreads, 1)
+// kConv (fp32 3xTF32 only): the operands are read in place by TMA and split into their tf32 hi and lo parts
+// by four extra warps inside the kernel, stage by stage, instead of by a pre-pass into a workspace: one
+// launch, no scratch memory, and half the operand traffic from L2 (the lo part never travels).
+template <int kCta, bool kTF32, bool kSplit, int BN, typename OutT, bool kConv = false>
+__global__ void __launch_bounds__(kConv ? kThreadsConv : kThreads, 1)
 gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_lo,
                   const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b_lo,
                   const __grid_constant__ GemmParams p) {
+    static_assert(!kConv || (kTF32 && kSplit && kCta == 1), "the in-kernel split is the fp32 3xTF32 path on one CTA");
     constexpr int kCopies = kSplit ? 2 : 1;
+    constexpr int kLoadCopies = kConv ? 1 : kCopies;   // copies that arrive by TMA
     constexpr int kPasses = kSplit ? 3 : 1;   // tcgen05.mma passes per k-step
     constexpr int BNL = BN / kCta;             // B rows this CTA stages
     constexpr int kTileM = kBM * kCta;
-    using L = StageLayout<kCopies, BNL>;
+    using L = StageLayout<kCopies, BNL, kConv>;
     constexpr int kStages = L::kStages;
     constexpr int kElem = kTF32 ? 4 : 2;
     constexpr int kBKElems = kRowBytes / kElem;         // K elements per stage
@@ -174,6 +220,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
     __shared__ __align__(8) uint64_t bar_acc_full[2];
     __shared__ __align__(8) uint64_t bar_acc_empty[2];
+    __shared__ __align__(8) uint64_t bar_conv[kMaxOpStages];       // kConv: an operand stage's hi / lo parts are written
+    __shared__ __align__(8) uint64_t bar_op_empty[kMaxOpStages];   // kConv: the tensor cores are through with an operand stage
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile uint32_t abort_flag;
 
@@ -187,7 +235,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(smem_u32(&bar_full[s]), 1);
-            mbar_init(smem_u32(&bar_empty[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), kConv ? kConvertWarps : 1);   // kConv: released by the split warps
+        }
+        for (int a = 0; a < kMaxOpStages; ++a) {
+            mbar_init(smem_u32(&bar_conv[a]), kConvertWarps);
+            mbar_init(smem_u32(&bar_op_empty[a]), 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&bar_acc_full[a]), 1);
@@ -237,7 +289,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 const int b_in = (int)(t.b % p.batch_in), b_out = (int)(t.b / p.batch_in);
                 const int za = p.a_in ? b_in : 0, wa = p.a_out ? b_out : 0;
                 const int zb = p.b_in ? b_in : 0, wb = p.b_out ? b_out : 0;
-                const uint32_t stage_tx = (uint32_t)(kCta * kCopies * (L::kABytes + bnl * kRowBytes));
+                const uint32_t stage_tx = (uint32_t)(kCta * kLoadCopies * (L::kABytes + bnl * kRowBytes));
                 for (int kb = 0; kb < p.num_kb; ++kb) {
                     if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag, p.err_word, 0x100u + stage)) {
                         ok = false;
@@ -247,16 +299,22 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     // the even CTA's barrier collects the bytes of both CTAs
                     if (cta_rank == 0) mbar_expect_tx(full, stage_tx);
                     const uint32_t sa = smem_base + stage * L::kStageBytes;
-                    const uint32_t sb = sa + kCopies * L::kABytes;
+                    const uint32_t sb = sa + kLoadCopies * L::kABytes;
                     const int k0 = kb * kBKElems;
 #pragma unroll
-                    for (int ps = 0; ps < kCopies; ++ps) {
+                    for (int ps = 0; ps < kLoadCopies; ++ps) {
                         const CUtensorMap* ma = ps == 0 ? &tm_a : &tm_a_lo;
                         const CUtensorMap* mb = ps == 0 ? &tm_b : &tm_b_lo;
                         // K-contiguous B, tail half: without the fp32 split the second B map is free and
                         // holds the half-height box
                         const CUtensorMap* mb_k = (half && !kSplit) ? &tm_b_lo : mb;
                         tma_load_4d<kCta>(sa + ps * L::kABytes, ma, full, k0, t.m0, za, wa);
+                        if constexpr (kConv) {
+                            if (p.b_mn_major) {   // [K, N] as stored: one box of 32 K-rows x BNL columns, no swizzle
+                                tma_load_4d<kCta>(sb, mb, full, t.n0, k0, zb, wb);
+                                continue;
+                            }
+                        }
                         if (p.b_mn_major) {
 #pragma unroll
                             for (int j = 0; j < BNL / kBBoxCols; ++j)
@@ -303,10 +361,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             uint32_t acc_phase = 0;
             bool ok = true;
             const uint32_t a_lbo = 16, a_sbo = 1024;
-            const uint32_t b_lbo = p.b_mn_major ? (uint32_t)kBBoxBytes : 16u, b_sbo = 1024;
+            const bool b_mn = p.b_mn_major && !kConv;   // the in-kernel split always produces K-contiguous B tiles
+            const uint32_t b_lbo = b_mn ? (uint32_t)kBBoxBytes : 16u, b_sbo = 1024;
             // bytes to advance the B descriptor per tcgen05.mma: one 32-byte K slice inside the swizzle
             // span when K is contiguous, kUmmaK rows of 128 bytes when N is contiguous
-            const uint32_t b_kstep = p.b_mn_major ? (uint32_t)(kUmmaKBytes / kElem) * kRowBytes : (uint32_t)kUmmaKBytes;
+            const uint32_t b_kstep = b_mn ? (uint32_t)(kUmmaKBytes / kElem) * kRowBytes : (uint32_t)kUmmaKBytes;
             for (long long tile = tile_first; ok && tile < p.num_tiles; tile += tile_step) {
                 bool w = mbar_wait(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, &abort_flag, p.err_word, 0x200u + acc);
                 if (!__all_sync(0xffffffffu, w)) {
@@ -318,15 +377,32 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 const uint32_t idesc = tile >= p.full_units ? p.idesc_half : p.idesc;
                 uint32_t first = 0;
                 for (int kb = 0; kb < p.num_kb; ++kb) {
-                    w = mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag, p.err_word, 0x300u + stage);
+                    // (kConv: `stage` walks the double buffer of operand stages)
+                    w = mbar_wait(smem_u32(kConv ? &bar_conv[stage] : &bar_full[stage]), phase, &abort_flag, p.err_word, 0x300u + stage);
                     if (!__all_sync(0xffffffffu, w)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
                     const uint32_t sa = smem_base + stage * L::kStageBytes;
-                    const uint32_t sb = sa + kCopies * L::kABytes;
-                    if (elect_one()) {
+                    const uint32_t sb = kConv ? smem_base + kStages * L::kStageBytes + stage * L::kOpBytes
+                                              : sa + kCopies * L::kABytes;
+                    if constexpr (kConv) {
+                        if (elect_one()) {
+                            // A from tensor memory: one 32-bit column per tf32 value, 8 columns per product
+                            const uint32_t ta = tmem_base + (uint32_t)(2 * BN + stage * 64);
+#pragma unroll
+                            for (int ps = 0; ps < 3; ++ps) {   // (lo, hi), (hi, lo), (hi, hi)
+                                const int ia = ps == 0 ? 1 : 0, ib = ps == 1 ? 1 : 0;
+                                const uint64_t db = make_smem_desc(sb + ib * L::kBBytes, b_lbo, b_sbo);
+#pragma unroll
+                                for (int k = 0; k < kKSteps; ++k)
+                                    umma_ts_tf32(tmem_d, ta + (uint32_t)(ia * 32 + k * 8), db + (uint64_t)((k * kUmmaKBytes) >> 4),
+                                                 idesc, (ps | k | (int)first) ? 1u : 0u);
+                            }
+                            tc_commit<kCta>(smem_u32(&bar_op_empty[stage]));
+                        }
+                    } else if (elect_one()) {
                         // passes: (lo, hi), (hi, lo), (hi, hi) for the split; (hi, hi) alone otherwise
 #pragma unroll
                         for (int ps = 0; ps < kPasses; ++ps) {
@@ -344,7 +420,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     }
                     __syncwarp();
                     first = 1;
-                    if (++stage == kStages) {
+                    if (++stage == (kConv ? L::kOpStages : kStages)) {
                         stage = 0;
                         phase ^= 1u;
                     }
@@ -354,6 +430,113 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 __syncwarp();
                 acc ^= 1;
                 if (acc == 0) acc_phase ^= 1u;
+            }
+        }
+    } else if (kConv && warp >= 2 + kEpilogueWarps) {
+        // ---------------- operand split (warps 10..17) ----------------
+        // Each raw stage holds fp32 A and B as they lie in memory. Into the next operand stage go
+        // hi = x with the low 13 mantissa bits cleared (exactly a tf32 value) and lo = (x - hi) cleared the
+        // same way: A's into tensor memory (a warp reaches the 32 lanes of its id mod 4: one row of the tile
+        // per thread, the two warps of a quarter take 16 of the 32 K columns each), B's into shared memory.
+        if constexpr (kConv) {
+            static_assert(2 * BN + L::kOpStages * 64 <= (int)kTmemCols && L::kOpStages <= kMaxOpStages, "accumulators and A stages fit tensor memory");
+            const int t = (int)threadIdx.x - 32 * (2 + kEpilogueWarps);
+            const int khalf = (warp - (2 + kEpilogueWarps)) >> 2;
+            const int m = (warp & 3) * 32 + lane;
+            const uint32_t a_tmem = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(2 * BN + khalf * 16);
+            int stage = 0, ostage = 0;         // raw ring and operand ring positions
+            uint32_t phase = 0, ophase = 0;
+            uint8_t* const base = smem_raw + (smem_base - smem_u32(smem_raw));
+            // this CTA's k-blocks, over all of its tiles: the split does not care where a tile ends
+            const long long my_tiles = tile_first < p.num_tiles ? (p.num_tiles - tile_first + tile_step - 1) / tile_step : 0;
+            const long long total_kb = my_tiles * p.num_kb;
+            constexpr int kBatch = L::kConvBatch;
+            for (long long i = 0; i < total_kb; i += kBatch) {
+                const int nb = total_kb - i < kBatch ? (int)(total_kb - i) : kBatch;
+                int st[kBatch], os[kBatch];
+                bool w = true;
+#pragma unroll
+                for (int j = 0; j < kBatch; ++j) {
+                    st[j] = stage;
+                    os[j] = ostage;
+                    if (j < nb) {
+                        if (w) w = mbar_wait_poll(smem_u32(&bar_full[stage]), phase, &abort_flag, p.err_word, 0x700u + stage);
+                        if (w) w = mbar_wait_poll(smem_u32(&bar_op_empty[ostage]), ophase ^ 1u, &abort_flag, p.err_word, 0x710u + ostage);
+                        if (++stage == kStages) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                        if (++ostage == L::kOpStages) {
+                            ostage = 0;
+                            ophase ^= 1u;
+                        }
+                    }
+                }
+                if (!__all_sync(0xffffffffu, w)) break;
+                tc_fence_after();
+#pragma unroll
+                for (int j = 0; j < kBatch; ++j) {
+                    if (j >= nb) break;
+                    const uint8_t* const raw_a = base + st[j] * L::kStageBytes;
+                    const uint8_t* const raw_b = raw_a + L::kABytes;
+                    uint8_t* const b_hi = base + kStages * L::kStageBytes + os[j] * L::kOpBytes;
+                    uint8_t* const b_lo = b_hi + L::kBBytes;
+                    {
+                        // row m of the tile: 16-byte chunk c sits at position c ^ (m & 7) of its 128 bytes
+                        float4 x[4];
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            x[c] = *reinterpret_cast<const float4*>(raw_a + m * kRowBytes + (((khalf * 4 + c) ^ (m & 7)) << 4));
+                        uint32_t h[16], l[16];
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const float4 lo = tf32_lo4(x[c]);
+                            h[4 * c + 0] = __float_as_uint(x[c].x); l[4 * c + 0] = __float_as_uint(lo.x);
+                            h[4 * c + 1] = __float_as_uint(x[c].y); l[4 * c + 1] = __float_as_uint(lo.y);
+                            h[4 * c + 2] = __float_as_uint(x[c].z); l[4 * c + 2] = __float_as_uint(lo.z);
+                            h[4 * c + 3] = __float_as_uint(x[c].w); l[4 * c + 3] = __float_as_uint(lo.w);
+                        }
+                        tmem_st16(a_tmem + (uint32_t)(os[j] * 64), h);
+                        tmem_st16(a_tmem + (uint32_t)(os[j] * 64 + 32), l);
+                    }
+                    if (!p.b_mn_major) {
+                        // same offsets in and out, so the swizzle the copy engine applied carries over
+#pragma unroll
+                        for (int off = t * 16; off < L::kBBytes; off += 32 * kConvertWarps * 16) {
+                            const float4 x = *reinterpret_cast<const float4*>(raw_b + off);
+                            *reinterpret_cast<float4*>(b_hi + off) = x;
+                            *reinterpret_cast<float4*>(b_lo + off) = tf32_lo4(x);
+                        }
+                    } else {
+                        // B arrived [32 K-rows][BNL columns]; the tensor cores want rows of N with K contiguous
+                        // (128 bytes per row, 16-byte chunk c of row n at position c ^ (n & 7), the layout the copy
+                        // engine's 128-byte swizzle gives a K-contiguous tile). One chunk = 4 consecutive K of one n.
+                        const float* raw = reinterpret_cast<const float*>(raw_b);
+#pragma unroll
+                        for (int q = t; q < BNL * 8; q += 32 * kConvertWarps) {
+                            const int n = q % BNL, c = q / BNL;
+                            const float4 x = make_float4(raw[(4 * c + 0) * BNL + n], raw[(4 * c + 1) * BNL + n],
+                                                         raw[(4 * c + 2) * BNL + n], raw[(4 * c + 3) * BNL + n]);
+                            const int off = n * kRowBytes + ((c ^ (n & 7)) << 4);
+                            *reinterpret_cast<float4*>(b_hi + off) = x;
+                            *reinterpret_cast<float4*>(b_lo + off) = tf32_lo4(x);
+                        }
+                    }
+                }
+                tmem_wait_st();
+                // the tensor cores read shared memory through the async proxy
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+#pragma unroll
+                    for (int j = 0; j < kBatch; ++j) {
+                        if (j < nb) {
+                            mbar_arrive(smem_u32(&bar_conv[os[j]]));    // operands ready
+                            mbar_arrive(smem_u32(&bar_empty[st[j]]));   // raw stage free for the next load
+                        }
+                    }
+                }
             }
         }
     } else {
@@ -374,7 +557,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         constexpr int kPack = 16 / sizeof(OutT);  // elements per 16-byte store
         constexpr int kRowPieces = 32 / kPack;    // 16-byte pieces per row of a 32-column chunk
         constexpr int kSub = 8 / kRowPieces;      // chunks per 128-byte staging row (2 for 16-bit outputs)
-        uint8_t* const stg = smem_raw + (smem_base - smem_u32(smem_raw)) + kStages * L::kStageBytes + (warp - 2) * 4096;
+        uint8_t* const stg = smem_raw + (smem_base - smem_u32(smem_raw)) + L::kMainBytes + (warp - 2) * 4096;
         for (long long tile = tile_first; tile < p.num_tiles; tile += tile_step) {
             bool ok = mbar_wait(smem_u32(&bar_acc_full[acc]), acc_phase, &abort_flag, p.err_word, 0x400u + acc,
                                 2000000000ull, 200);
@@ -545,10 +728,6 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 // 13 mantissa bits cleared (exactly a tf32 value) and, for the 3xTF32 split, lo = (x - hi) cleared
 // the same way (lo == nullptr skips it). rows x cols, source row stride ld_src, destination row
 // stride ld_dst >= cols (the pad columns are written as zero).
-__device__ __forceinline__ void tf32_split(float x, float& h, float& l) {
-    h = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
-    l = __uint_as_float(__float_as_uint(x - h) & 0xffffe000u);
-}
 
 // Both operands in ONE launch (the whole fp32 GEMM of 1024^3 takes 40 us, a launch a tenth of that):
 // blocks [0, a_blocks) split A row-wise; the others handle B, row-wise when it is stored [N, K], through
@@ -668,7 +847,7 @@ struct BatchDims {
 // 4-D map {inner, rows, batch_in, batch_out}; box {box_inner, box_rows, 1, 1}; 128-byte swizzle; OOB
 // reads give zero. A level with count 1 is never stepped, so its stride only has to be encodable.
 static int make_map(CUtensorMap* map, const void* base, int dtype, uint64_t inner, uint64_t rows, const BatchDims& bd,
-                    uint64_t ld_elems, uint32_t box_inner, uint32_t box_rows) {
+                    uint64_t ld_elems, uint32_t box_inner, uint32_t box_rows, bool swizzle = true) {
     EncodeTiledFn fn = tensor_map_encoder();
     if (!fn) return CG_B200_ERR_CUDA;
     const uint64_t esz = dtype_bytes(dtype);
@@ -681,7 +860,8 @@ static int make_map(CUtensorMap* map, const void* base, int dtype, uint64_t inne
     cuuint32_t box[4] = {box_inner, box_rows, 1, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = fn(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         note_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
         return CG_B200_ERR_CUDA;
@@ -766,11 +946,11 @@ static bool tail_split_enabled() {
     return on;
 }
 
-template <int kCta, bool kTF32, bool kSplit, int BN, typename OutT>
+template <int kCta, bool kTF32, bool kSplit, int BN, typename OutT, bool kConv = false>
 static int launch_variant(const CUtensorMap& ta, const CUtensorMap& ta_lo, const CUtensorMap& tb,
                           const CUtensorMap& tb_lo, GemmParams& p, cudaStream_t s) {
-    using L = StageLayout<kSplit ? 2 : 1, BN / kCta>;
-    auto kern = gemm_sm100_kernel<kCta, kTF32, kSplit, BN, OutT>;
+    using L = StageLayout<kSplit ? 2 : 1, BN / kCta, kConv>;
+    auto kern = gemm_sm100_kernel<kCta, kTF32, kSplit, BN, OutT, kConv>;
     // the attribute is per device; setting it again is cheap
     CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynSmem));
     const int elem = kTF32 ? 4 : 2;
@@ -794,7 +974,7 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& ta_lo, const
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3((unsigned)(groups * kCta), 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.blockDim = dim3(kConv ? kThreadsConv : kThreads, 1, 1);
     cfg.dynamicSmemBytes = L::kDynSmem;
     cfg.stream = s;
     cudaLaunchAttribute attr[2];
@@ -871,7 +1051,7 @@ struct PeerSet {
 static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B, const void* bias,
                     const void* residual, void* C, void* workspace, size_t workspace_bytes, void* stream,
                     bool shared_err_word, uint32_t* err_word, const PeerSet* peers = nullptr,
-                    const cg_b200_gemm_tuning* tuning = nullptr) {
+                    const cg_b200_gemm_tuning* tuning = nullptr, bool use_workspace_split = false) {
     int st = validate_desc(desc);
     if (st) return st;
     if (tuning) {
@@ -891,6 +1071,13 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
     if (need_res && !residual) return CG_B200_ERR_NULL_POINTER;
     const size_t in_sz = dtype_bytes(d.in_dtype), out_sz = dtype_bytes(d.out_dtype);
     const Fp32Plan sp = plan_fp32(desc);
+    // fp32, 3xTF32: when TMA can read A and B where they lie (16-byte aligned bases and strides) the hi / lo
+    // split happens inside the GEMM kernel and no workspace is touched; otherwise a pre-pass rewrites the
+    // operands into the workspace first. use_workspace_split forces the pre-pass (the entry point whose
+    // scratch is the library's own array exists to exercise exactly that path).
+    const bool in_kernel_split =
+        sp.active && sp.copies == 2 && !use_workspace_split && d.K > 0 && aligned_to(A, 16) && aligned_to(B, 16) &&
+        (d.lda * 4) % 16 == 0 && (d.ldb * 4) % 16 == 0 && (d.batch_stride_a * 4) % 16 == 0 && (d.batch_stride_b * 4) % 16 == 0;
     // C rows are written with 16-byte stores
     if (!aligned_to(C, 16) || (d.ldc * out_sz) % 16 || (d.batch_stride_c * out_sz) % 16) return CG_B200_ERR_MISALIGNED;
     if (d.batch_inner > 1 && (d.inner_stride_c * out_sz) % 16) return CG_B200_ERR_MISALIGNED;
@@ -906,8 +1093,10 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
     } else {
         if (d.batch_inner > 1) return CG_B200_ERR_UNSUPPORTED;   // fp32 operands: one batch level only
         if (!aligned_to(A, 4) || !aligned_to(B, 4)) return CG_B200_ERR_MISALIGNED;
-        if (!workspace || workspace_bytes < sp.bytes) return CG_B200_ERR_WORKSPACE;
-        if (!aligned_to(workspace, 256)) return CG_B200_ERR_MISALIGNED;
+        if (!in_kernel_split) {
+            if (!workspace || workspace_bytes < sp.bytes) return CG_B200_ERR_WORKSPACE;
+            if (!aligned_to(workspace, 256)) return CG_B200_ERR_MISALIGNED;
+        }
     }
     st = require_sm100();
     if (st) return st;
@@ -940,7 +1129,7 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
         }
     }
     p.epilogue = epi; p.alpha = d.alpha;
-    p.b_mn_major = (d.b_transposed || sp.active) ? 0 : 1;   // the fp32 workspace copy of B is K-contiguous
+    p.b_mn_major = (d.b_transposed || (sp.active && !in_kernel_split)) ? 0 : 1;   // the fp32 workspace copy of B is K-contiguous
     const long long a_s_in = two ? d.inner_stride_a : d.batch_stride_a, a_s_out = two ? d.batch_stride_a : 0;
     const long long b_s_in = two ? d.inner_stride_b : d.batch_stride_b, b_s_out = two ? d.batch_stride_b : 0;
     p.a_in = a_s_in != 0 && p.batch_in > 1;
@@ -973,8 +1162,9 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
         if (cta == 2 && bn == 64) return CG_B200_ERR_UNSUPPORTED;             // a pair's tile is 128 or 256 wide
         p.tail_split = t.tail_split;
     }
-    p.idesc = make_idesc(d.in_dtype, tf32, p.b_mn_major != 0, kBM * cta, bn);
-    p.idesc_half = make_idesc(d.in_dtype, tf32, p.b_mn_major != 0, kBM * cta, bn / 2);
+    const bool b_desc_mn = p.b_mn_major != 0 && !in_kernel_split;   // the in-kernel split hands the tensor cores K-contiguous B tiles
+    p.idesc = make_idesc(d.in_dtype, tf32, b_desc_mn, kBM * cta, bn);
+    p.idesc_half = make_idesc(d.in_dtype, tf32, b_desc_mn, kBM * cta, bn / 2);
     const uint32_t box_k = (uint32_t)(kRowBytes / in_sz);
 
     // with K == 0 no load is ever issued; the maps only need an encodable base address
@@ -988,7 +1178,7 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
     bda.n_out = p.a_out ? (uint64_t)n_out : 1;    bda.s_out = (uint64_t)a_s_out;
     bdb.n_in = p.b_in ? (uint64_t)p.batch_in : 1; bdb.s_in = (uint64_t)b_s_in;
     bdb.n_out = p.b_out ? (uint64_t)n_out : 1;    bdb.s_out = (uint64_t)b_s_out;
-    if (sp.active) {
+    if (sp.active && !in_kernel_split) {
         float* w = static_cast<float*>(workspace);
         float* wa_hi = w;
         float* wa_lo = sp.copies == 2 ? w + sp.a_elems : nullptr;
@@ -1031,7 +1221,12 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
     if (st) return st;
     st = make_map(&ta_lo, a_lo, d.in_dtype, k_dim, d.M, bda, lda, box_k, kBM);
     if (st) return st;
-    if (p.b_mn_major) {
+    if (p.b_mn_major && in_kernel_split) {
+        // [K, N] fp32 read as it lies: one unswizzled box of 32 K-rows x (tile width) columns per stage
+        st = make_map(&tb, b_hi, d.in_dtype, d.N, k_dim, bdb, ldb, (uint32_t)bn, box_k, /*swizzle=*/false);
+        if (st) return st;
+        st = make_map(&tb_lo, b_lo, d.in_dtype, d.N, k_dim, bdb, ldb, (uint32_t)bn, box_k, false);
+    } else if (p.b_mn_major) {
         st = make_map(&tb, b_hi, d.in_dtype, d.N, k_dim, bdb, ldb, box_k, box_k);
         if (st) return st;
         st = make_map(&tb_lo, b_lo, d.in_dtype, d.N, k_dim, bdb, ldb, box_k, box_k);
@@ -1045,6 +1240,10 @@ static int gemm_run(const cg_b200_gemm_desc* desc, const void* A, const void* B,
     if (st) return st;
 
     if (tf32) {
+        if (in_kernel_split) {
+            if (bn == 64) return launch_variant<1, true, true, 64, float, true>(ta, ta_lo, tb, tb_lo, p, s);
+            return launch_variant<1, true, true, 128, float, true>(ta, ta_lo, tb, tb_lo, p, s);
+        }
         if (sp.copies == 2) return launch_bn<1, true, true, float>(bn, ta, ta_lo, tb, tb_lo, p, s);
         return launch_bn<1, true, false, float>(bn, ta, ta_lo, tb, tb_lo, p, s);
     }
@@ -1117,7 +1316,7 @@ extern "C" int cg_b200_gemm_f32_static(const cg_b200_gemm_desc* desc, const void
     // The split pre-pass rewrites every scratch byte the GEMM reads (pad columns included), so
     // nothing left over from an earlier call can leak into this one.
     return gemm_run(desc, A, B, bias, residual, C, scratch, (size_t)CG_B200_GEMM_F32_STATIC_SCRATCH_BYTES, stream,
-                    false, dev_error_word);
+                    false, dev_error_word, nullptr, nullptr, /*use_workspace_split=*/true);
 }
 
 // ---- GEMM fused with the all-gather of its M-sharded output ------------------------------------------
