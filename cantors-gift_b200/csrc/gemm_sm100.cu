@@ -194,7 +194,7 @@ struct StageLayout {
 };
 
 // kConv (fp32 3xTF32 only): the operands are read in place by TMA and split into their tf32 hi and lo parts
-// by four extra warps inside the kernel, stage by stage, instead of by a pre-pass into a workspace: one
+// by eight extra warps inside the kernel, stage by stage, instead of by a pre-pass into a workspace: one
 // launch, no scratch memory, and half the operand traffic from L2 (the lo part never travels).
 template <int kCta, bool kTF32, bool kSplit, int BN, typename OutT, bool kConv = false>
 __global__ void __launch_bounds__(kConv ? kThreadsConv : kThreads, 1)
@@ -922,7 +922,11 @@ static int validate_desc(const cg_b200_gemm_desc* d) {
     if (d->batch_inner < 0 || (d->batch_inner > 1 && d->batch % d->batch_inner != 0)) return CG_B200_ERR_INVALID_ARG;
     if (d->batch_inner > 1 && (d->inner_stride_a < 0 || d->inner_stride_b < 0 || d->inner_stride_c <= 0))
         return CG_B200_ERR_INVALID_ARG;
-    if (d->batch_inner <= 1 && d->batch > 1 && d->batch_stride_c < d->M * d->ldc) return CG_B200_ERR_INVALID_ARG;
+    // outputs of different batches must not overlap: one after another, or side by side inside the rows
+    // (column blocks, e.g. the heads of an attention output)
+    if (d->batch_inner <= 1 && d->batch > 1 && d->batch_stride_c < d->M * d->ldc &&
+        !(d->batch_stride_c >= d->N && d->batch * d->batch_stride_c <= d->ldc))
+        return CG_B200_ERR_INVALID_ARG;
     if (d->M > 0x7fffffffLL || d->N > 0x7fffffffLL || d->K > 0x7fffffffLL || d->batch > 0x7fffffffLL)
         return CG_B200_ERR_UNSUPPORTED;
     return CG_B200_OK;

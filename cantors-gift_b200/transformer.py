@@ -10,7 +10,9 @@ never executes it (benchmarks/REPORT_TRANSFORMER.md:53-57). Seven launches per b
   [B*S, d_model]) | out-proj GEMM + residual | layernorm | FFN1 GEMM + bias + gelu |
   FFN2 GEMM + bias + residual
 Without the fused kernel (head_dim != 64, fp32) attention is three launches: Q K^T GEMM (heads as the
-inner batch level, scale in the epilogue), row softmax, P V GEMM.
+inner batch level, scale in the epilogue), row softmax, P V GEMM. fp32 GEMMs take one batch level, so an
+fp32 block (the dtype of the reference's own graph; a functional path, not a tuned one) runs the two
+attention GEMMs once per sequence with the heads as that level: 5 + 2 * B + 1 launches.
 Weights are [in, out] row-major (x @ W), all tensors bf16/f16/f32 of one dtype.
 """
 import ctypes as C
@@ -18,7 +20,7 @@ import math
 
 import torch
 
-from . import capi
+from . import capi, ops
 from .capi import check, lib
 from .ops import DTYPE_OF_TORCH
 
@@ -79,8 +81,10 @@ class EncoderBlock:
 
         def gemm(desc, a, b, c, bias=None, res=None, a_off=0, b_off=0):
             es = a.element_size()
+            # fp32 operands TMA cannot read in place (unaligned base or stride) are rewritten into a workspace
+            ws, ws_bytes = ops.gemm_workspace(desc, dev) if self.dtype == torch.float32 else (None, 0)
             check(L.cg_b200_gemm(C.byref(desc), C.c_void_p(a.data_ptr() + a_off * es), C.c_void_p(b.data_ptr() + b_off * es),
-                                 p(bias), p(res), p(c), None, 0, st), "gemm")
+                                 p(bias), p(res), p(c), p(ws), ws_bytes, st), "gemm")
 
         check(L.cg_b200_layernorm(dt, p(x2), None, None, self.eps, p(ln1), rows, D, st), "layernorm")
         gemm(capi.make_gemm_desc(rows, 3 * D, D, dt, dt, b_transposed=1), ln1, self._wt["qkv"], qkv)
@@ -111,9 +115,21 @@ class EncoderBlock:
     def _unfused_attention(self, qkv, scores, ctx, B, S, gemm, p, st):
         D, H, dh, dt = self.D, self.H, self.dh, self.dt
         L = lib()
+        scale = 1.0 / math.sqrt(dh)
+        if self.dtype == torch.float32:
+            # one batch level per launch: the heads of one sequence (stride dh in the qkv rows)
+            d_qk = capi.make_gemm_desc(S, S, dh, dt, dt, epilogue="scale", alpha=scale, batch=H, b_transposed=1,
+                                       lda=3 * D, ldb=3 * D, ldc=S, bsa=dh, bsb=dh, bsc=S * S)
+            d_pv = capi.make_gemm_desc(S, dh, S, dt, dt, batch=H, lda=S, ldb=3 * D, ldc=D, bsa=S * S, bsb=dh, bsc=dh)
+            for b in range(B):
+                gemm(d_qk, qkv, qkv, scores[b * H:], a_off=b * S * 3 * D, b_off=b * S * 3 * D + D)
+            check(L.cg_b200_softmax(dt, p(scores), p(scores), B * H * S, S, st), "softmax")
+            for b in range(B):
+                gemm(d_pv, scores[b * H:], qkv, ctx[b * S:], b_off=b * S * 3 * D + 2 * D)
+            return
         # scores[b, h] = Q_bh K_bh^T / sqrt(dh): Q, K are column blocks of the qkv rows (row stride 3D);
         # heads are the inner batch level (stride dh), sequences the outer one (stride S * 3D)
-        d_qk = capi.make_gemm_desc(S, S, dh, dt, dt, epilogue="scale", alpha=1.0 / math.sqrt(dh), batch=B * H,
+        d_qk = capi.make_gemm_desc(S, S, dh, dt, dt, epilogue="scale", alpha=scale, batch=B * H,
                                    b_transposed=1, lda=3 * D, ldb=3 * D, ldc=S, batch_inner=H,
                                    bsa=S * 3 * D, bsb=S * 3 * D, bsc=H * S * S, isa=dh, isb=dh, isc=S * S)
         gemm(d_qk, qkv, qkv, scores, b_off=D)
@@ -125,4 +141,5 @@ class EncoderBlock:
 
     @property
     def launches_per_forward(self):
+        """16-bit types; an fp32 block launches 6 + 2 * batch kernels."""
         return 7 if self.fused_attention else 9

@@ -242,10 +242,16 @@ typedef struct cg_b200_gemm_desc {
     int64_t inner_stride_a, inner_stride_b, inner_stride_c;
 } cg_b200_gemm_desc;
 
-/* Bytes of device scratch cg_b200_gemm needs for this problem (0 if none). */
+/* Bytes of device scratch cg_b200_gemm may need for this problem (0 for 16-bit inputs). fp32 inputs are
+ * split into tf32 hi / lo parts: inside the kernel, with no scratch, when A and B can be read in place
+ * (16-byte aligned bases, row and batch strides multiples of 16 bytes); operands that are only 4-byte
+ * aligned are rewritten into the workspace by a pre-pass first, and CG_B200_ERR_WORKSPACE is returned
+ * when it is missing or too small. Both ways give the same bits. */
 int cg_b200_gemm_workspace_bytes(const cg_b200_gemm_desc* desc, size_t* bytes);
-/* A, B, C: 16-byte aligned base pointers; strides multiples of 16 bytes. `bias` is [N],
- * `residual` is [M, N] with row stride ldc (and batch_stride_c), both of out_dtype. */
+/* 16-bit A, B: 16-byte aligned base pointers; strides multiples of 16 bytes. C: always so. `bias` is [N],
+ * `residual` is [M, N] with row stride ldc (and batch_stride_c), both of out_dtype. The C tiles of
+ * different batches must not overlap: batch_stride_c >= M * ldc, or column blocks side by side
+ * (batch_stride_c >= N and batch * batch_stride_c <= ldc). */
 int cg_b200_gemm(const cg_b200_gemm_desc* desc, const void* A, const void* B,
                  const void* bias, const void* residual, void* C, void* workspace,
                  size_t workspace_bytes, void* stream);
@@ -299,9 +305,11 @@ int cg_b200_attention(const cg_b200_attention_desc* desc, const void* Q, const v
  * include/cg/runtime/runtime.hpp:84-88, which carries no allocator), a service whose device
  * memory was given out in full to its own pools at start-up, or a latency-critical loop that
  * must not hit the implicit device synchronisation of cudaMalloc/cudaFree. cg_b200_gemm needs
- * a caller-provided workspace for fp32 inputs; this entry point instead keeps that scratch in a
+ * a caller-provided workspace for fp32 inputs it cannot read in place (see above); this entry
+ * point takes operands of any 4-byte alignment and keeps that scratch in a
  * fixed array of CG_B200_GEMM_F32_STATIC_SCRATCH_BYTES inside the library, held by every GPU
- * that loads the library until the process exits. It calls no allocating routine.
+ * that loads the library until the process exits. It calls no allocating routine and always runs
+ * the pre-pass form.
  *  - in_dtype must be fp32 (other types need no scratch: use cg_b200_gemm); problems whose
  *    workspace (cg_b200_gemm_workspace_bytes) exceeds the array return CG_B200_ERR_WORKSPACE.
  *  - dev_error_word: optional caller-owned device uint32 (zeroed by the caller) that receives a

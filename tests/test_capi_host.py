@@ -74,11 +74,21 @@ def test_argument_errors_come_before_device_access(cgb):
     assert L.cg_b200_gemm(C.byref(g), p, p, None, None, p, None, 0, None) == capi.ERR_NULL_POINTER  # bias missing
     g = capi.make_gemm_desc(128, 128, 60, capi.BF16, capi.BF16)   # lda*2 not a multiple of 16
     assert L.cg_b200_gemm(C.byref(g), p, p, None, None, p, None, 0, None) == capi.ERR_MISALIGNED
-    g = capi.make_gemm_desc(128, 128, 64, capi.F32, capi.F32)     # 3xTF32 needs its workspace
+    # 3xTF32 splits its operands inside the kernel when TMA can read them in place (16-byte aligned bases and
+    # strides); operands that are only 4-byte aligned are rewritten into a workspace first, which must be there
+    g = capi.make_gemm_desc(128, 128, 64, capi.F32, capi.F32)
     need = C.c_size_t(0)
     assert L.cg_b200_gemm_workspace_bytes(C.byref(g), C.byref(need)) == capi.OK
     assert need.value == 2 * (128 * 64 + 64 * 128) * 4
+    p4 = C.c_void_p(1028)
+    assert L.cg_b200_gemm(C.byref(g), p4, p, None, None, p, None, 0, None) == capi.ERR_WORKSPACE
+    g = capi.make_gemm_desc(128, 128, 62, capi.F32, capi.F32)     # row stride 248 bytes
     assert L.cg_b200_gemm(C.byref(g), p, p, None, None, p, None, 0, None) == capi.ERR_WORKSPACE
+    # column blocks of C side by side (heads of an attention output) do not overlap; anything tighter does
+    g = capi.make_gemm_desc(16, 64, 64, capi.BF16, capi.BF16, batch=4, ldc=256, bsc=64)
+    assert L.cg_b200_gemm_workspace_bytes(C.byref(g), C.byref(need)) == capi.OK
+    g = capi.make_gemm_desc(16, 64, 64, capi.BF16, capi.BF16, batch=4, ldc=256, bsc=32)
+    assert L.cg_b200_gemm_workspace_bytes(C.byref(g), C.byref(need)) == capi.ERR_INVALID_ARG
     g = capi.make_gemm_desc(128, 128, 64, capi.BF16, capi.BF16, compute="tf32x3")
     assert L.cg_b200_gemm(C.byref(g), p, p, None, None, p, None, 0, None) == capi.ERR_INVALID_ARG
     g = capi.make_gemm_desc(0, 128, 64, capi.BF16, capi.BF16)

@@ -22,6 +22,8 @@ def _dev(ops, a, dtype):
 def _host(O, t, dtype):
     import torch
     c = t.cpu()
+    if dtype == O.F32:
+        return c.numpy()
     return O.to_f32(c.view(torch.int16).numpy().view(np.uint16 if dtype == O.BF16 else np.float16), dtype)
 
 
@@ -53,6 +55,25 @@ def test_block_matches_oracle(ops, cgb, oracle, dtype_name, B, S, D, H, F, fused
     strict = 1e-2 if (not fused_attention or dtype_name == "F16") else 5e-2
     _check(_host(O, y, dtype), want, 1e-2, f"block {dtype_name} B{B} S{S} D{D} H{H} F{F} fused={fused_attention}",
            p999_tol=strict)
+
+
+@pytest.mark.parametrize("B,S,D,H,F", [(2, 128, 128, 2, 512), (3, 200, 256, 4, 384)])
+def test_fp32_block_matches_oracle(ops, cgb, oracle, B, S, D, H, F):
+    """The reference's own graph is fp32 (benchmarks/benchmark_transformer.py:122-170). fp32 bound of the path:
+    1e-4 (3xTF32 GEMMs, fp32 row kernels), strict per-element metric included."""
+    import torch
+    from cantors_gift_b200.transformer import EncoderBlock
+    from oracle import transformer as T
+    O = oracle
+    rng = np.random.default_rng(B * 1000 + S + 1)
+    x, w = _make(O, rng, B, S, D, F, O.F32)
+    want = O.to_f32(T.encoder_block(x, n_heads=H, dtype=O.F32, **w), O.F32)
+    blk = EncoderBlock(D, H, F, **{k: _dev(ops, v, O.F32) for k, v in w.items()})
+    assert not blk.fused_attention
+    y = blk.forward(_dev(ops, x, O.F32))
+    torch.cuda.synchronize()
+    assert ops.last_device_error() == 0
+    _check(_host(O, y, O.F32), want, 1e-4, f"fp32 block B{B} S{S} D{D} H{H} F{F}", p999_tol=1e-4)
 
 
 def test_full_size_block_sequences_are_independent_and_match(ops, cgb, oracle):
