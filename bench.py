@@ -1,16 +1,24 @@
 """Benchmark of the B200 execution path for cantors-gift Executables.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload gemm|eltwise|rowreduce|matmul_f32|block]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload gemm|eltwise|rowreduce|matmul_f32|block|attention]
                     [--impl ours|reference] [--no-also]
 
 One JSON line on stdout (rank 0). The headline workload is the bf16 4096^3 GEMM with fused
 bias + GELU(tanh) (TFLOP/s); the memory-bound kernels of the path (fused elementwise chain,
-softmax -> layernorm; GB/s) and the fp32 1024^3 matmul are reported in the same line under
-"also". All inputs are seeded synthetic data of the configured shapes.
+softmax -> layernorm; GB/s), the fp32 1024^3 matmul and the transformer encoder block (a Tensor-IR
+graph lowered, compiled, bound and launched through the reference's own TensorToCodegenLowering /
+NvidiaBackend / Runtime interfaces) are short entries under "also", repeated inside "roofline". With
+N > 1 GPUs the GEMM is sharded along M and the block along the batch, the last GEMM's epilogue
+stores into every rank's output (fused all-gather), "also" holds the block, and outside the timed
+region every rank compares what it holds after the gather with the one-GPU result, bit for bit
+("gather_check"). "library_baseline" is torch.matmul on the GEMM's operands. All inputs are seeded
+synthetic data of the configured shapes.
 
 Timing: W >= 3 warm-up steps, then K steps between two CUDA events on the launching stream,
 bracketed by barrier + synchronize, max over ranks. Memory-bound workloads stream inputs larger
-than L2 every step; the GEMM rotates over buffer sets larger than L2.
+than L2 every step; the GEMMs rotate over buffer sets larger than L2. Tensor-bound fractions divide
+by the measured burst peak when the timed region lasts under a second (sustained peak and nominal
+2.25 PFLOP/s as side keys).
 """
 import argparse
 import json
@@ -31,7 +39,8 @@ PROG_CHAIN = [("input", 0), ("input", 1), "mul", ("input", 2), "add", "relu", ("
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
 # profiles/ (None until a capture exists for that kernel).
-NCU_TRAFFIC_BYTES = {"gemm": 85168896, "eltwise": 1047363072, "rowreduce": 485570560, "matmul_f32": None, "block": None}
+NCU_TRAFFIC_BYTES = {"gemm": 85168896, "eltwise": 1047363072, "rowreduce": 485570560, "matmul_f32": 8465408, "block": None,
+                     "attention": None}
 
 
 def measured_peaks():
@@ -625,7 +634,7 @@ class BlockWorkload(Workload):
     def work_per_step(self):
         return self.flops() / 1e12
 
-    def algorithmic_per_launch(self):   # per step here: nine launches make one pass of the block
+    def algorithmic_per_launch(self):   # per step here: seven launches make one pass of the block
         return self.flops() / self.world
 
     def e2e_setup(self):
@@ -687,7 +696,98 @@ class BlockWorkload(Workload):
                           "but never executes it"}, dt_s * self.B
 
 
-WORKLOADS = {"block": BlockWorkload, "gemm": GemmWorkload, "eltwise": EltwiseWorkload, "rowreduce": RowReduceWorkload,
+class AttentionWorkload(Workload):
+    """The fused attention kernel alone at the block's shape: bf16, 16 heads of 64, seq 2048, Q / K / V read in
+    place from a packed [batch * seq, 3 * d_model] projection. $CG_B200_BENCH_ATTENTION_BATCH (default 32)
+    shrinks the batch for profiler captures."""
+    name, unit, bound, dtype = "attention", "TFLOP/s", "tensor", "bf16"
+    S, D, H = 2048, 1024, 16
+
+    def __init__(self):
+        self.B = int(os.environ.get("CG_B200_BENCH_ATTENTION_BATCH", "32"))
+
+    def config(self, world):
+        return {"workload": f"fused attention softmax(Q K^T / 8) V, bf16, batch {self.B}, 16 heads, seq 2048, head_dim 64, "
+                            "Q/K/V in place from the packed QKV projection",
+                "l2": f"rotating over {self.sets} QKV buffers" if self.B < 32 else "QKV and output (537 MB) larger than L2",
+                "parallelism": "1 GPU"}
+
+    def setup(self, rank, world):
+        import ctypes as C
+        import math
+        import torch
+        from cantors_gift_b200 import capi
+        assert world == 1, "the attention workload is a one-GPU measurement"
+        B, S, D, H = self.B, self.S, self.D, self.H
+        dh = D // H
+        self.sets = 1 if B >= 32 else max(2, min(16, 32 // B))
+        g = torch.Generator(device="cuda").manual_seed(6)
+        self.qkv = [torch.randn(B * S, 3 * D, device="cuda", generator=g).to(torch.bfloat16) for _ in range(self.sets)]
+        self.ctx = [torch.empty(B * S, D, device="cuda", dtype=torch.bfloat16) for _ in range(self.sets)]
+        self.desc = capi.AttentionDesc(dtype=capi.BF16, head_dim=dh, batch=B, heads=H, seq_q=S, seq_kv=S, ldq=3 * D,
+                                       ldk=3 * D, ldv=3 * D, ldo=D, head_stride_q=dh, head_stride_k=dh, head_stride_v=dh,
+                                       head_stride_o=dh, batch_stride_q=S * 3 * D, batch_stride_k=S * 3 * D,
+                                       batch_stride_v=S * 3 * D, batch_stride_o=S * D, scale=1.0 / math.sqrt(dh))
+        self._C = C
+
+    def step(self, i):
+        import torch
+        from cantors_gift_b200 import capi
+        C = self._C
+        q = self.qkv[i % self.sets]
+        base, es = q.data_ptr(), 2
+        capi.check(capi.lib().cg_b200_attention(
+            C.byref(self.desc), C.c_void_p(base), C.c_void_p(base + self.D * es), C.c_void_p(base + 2 * self.D * es),
+            C.c_void_p(self.ctx[i % self.sets].data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream)), "attention")
+
+    def flops(self):
+        return 4.0 * self.B * self.H * self.S * self.S * (self.D // self.H)
+
+    def work_per_step(self):
+        return self.flops() / 1e12
+
+    def algorithmic_per_launch(self):
+        return self.flops()
+
+    def library_baseline(self, steps):
+        """torch's scaled_dot_product_attention (library kernel) on the same Q, K, V (strided views, no copy)."""
+        import torch
+        B, S, D, H = self.B, self.S, self.D, self.H
+        views = []
+        for q in self.qkv:
+            t = q.view(B, S, 3, H, D // H)
+            views.append(tuple(t[:, :, j].transpose(1, 2) for j in range(3)))
+        f = torch.nn.functional.scaled_dot_product_attention
+        for i in range(5):
+            f(*views[i % self.sets])
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            f(*views[i % self.sets])
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        return {"what": "torch scaled_dot_product_attention on the same Q, K, V", "ms_per_step": ms,
+                "value": self.flops() / (ms * 1e-3) / 1e12, "unit": "TFLOP/s"}
+
+    def cpu_baseline(self, budget_s, prefer_ref=True):
+        from oracle import oracle as O
+        threads = os.cpu_count() or 1
+        O.set_num_threads(threads)
+        rng = np.random.default_rng(6)
+        dh = self.D // self.H
+        q, k, v = (O.to_bf16(rng.standard_normal((1, 1, self.S, dh), dtype=np.float32)) for _ in range(3))
+        t0 = time.perf_counter()
+        O.attention(q, k, v, O.BF16, 1.0 / np.sqrt(dh))
+        dt_s = time.perf_counter() - t0
+        fl = self.flops() / (self.B * self.H)
+        return {"value": fl / dt_s / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                "sample": f"1 of {self.B * self.H} (batch, head) pairs; the reference annotates this pattern and "
+                          "executes nothing"}, dt_s * self.B * self.H
+
+
+WORKLOADS = {"attention": AttentionWorkload, "block": BlockWorkload, "gemm": GemmWorkload, "eltwise": EltwiseWorkload, "rowreduce": RowReduceWorkload,
              "matmul_f32": MatmulF32Workload}
 
 
@@ -882,7 +982,7 @@ def run_workload(name, steps, warmup, rank, world, peaks, sample_clocks, with_cp
     ms_per_step = secs / steps * 1e3
     value = w.work_per_step() * steps / secs
     e2e_steps = max(3, min(steps, 10))
-    if with_e2e:
+    if with_e2e and hasattr(w, "e2e_setup"):
         e_secs, h2d, d2h = time_e2e(w, e2e_steps, warmup, world)
     else:
         e_secs, h2d, d2h = float("inf"), 0, 0
@@ -899,7 +999,7 @@ def run_workload(name, steps, warmup, rank, world, peaks, sample_clocks, with_cp
     res = {
         "metric": METRIC, "value": value, "unit": w.unit, "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "strong" if name in ("gemm", "matmul_f32", "block") else "weak", "vs_baseline": None,
+        "scaling": "strong" if name in ("gemm", "matmul_f32", "block", "attention") else "weak", "vs_baseline": None,
         "dtype": w.dtype, "data": "synthetic", "config": w.config(world),
         "e2e": {"value": e2e_work * e2e_steps / e_secs, "unit": w.unit, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "steps": e2e_steps,
@@ -922,7 +1022,7 @@ def run_workload(name, steps, warmup, rank, world, peaks, sample_clocks, with_cp
         t = torch.tensor([w.gather_check()], device="cuda", dtype=torch.int64)
         dist.all_reduce(t)
         res["gather_check"] = "bit-identical" if int(t.item()) == 0 else f"{int(t.item())} elements differ over {world} ranks"
-    if world == 1 and hasattr(w, "library_baseline") and name == "gemm":
+    if world == 1 and hasattr(w, "library_baseline") and name in ("gemm", "attention"):
         res["library_baseline"] = w.library_baseline(steps)
     if clocks is not None:
         res["clocks"] = clocks
@@ -1026,7 +1126,7 @@ def main():
     if not args.no_also:
         # one GPU: every other configuration of the path; several GPUs: the transformer block, the other
         # workload that is partitioned (batch-sharded, y gathered by its last GEMM)
-        others = ("eltwise", "rowreduce", "matmul_f32", "block") if world == 1 else ("block",)
+        others = ("eltwise", "rowreduce", "matmul_f32", "block", "attention") if world == 1 else ("block",)
         also = {}
         for other in others:
             if other == args.workload:

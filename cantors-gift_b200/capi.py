@@ -23,6 +23,7 @@ BCAST = {"full": 0, "scalar": 1, "row": 2, "col": 3}
 EPILOGUE = {"none": 0, "bias": 1, "bias_relu": 2, "bias_gelu_tanh": 3, "bias_residual": 4,
             "residual": 5, "scale": 6, "relu": 7, "gelu_tanh": 8}
 COMPUTE = {"default": 0, "tf32x3": 1, "tf32": 2}
+REDUCE = {"sum": 0, "max": 1, "mean": 2}
 COMM_ID_BYTES = 128
 IPC_HANDLE_BYTES = 64
 GEMM_F32_STATIC_SCRATCH_BYTES = 16 << 20
@@ -110,6 +111,7 @@ SIGNATURES = {
     "cg_b200_softmax": (_i, [_i, _vp, _vp, _i64, _i64, _vp]),
     "cg_b200_layernorm": (_i, [_i, _vp, _vp, _vp, C.c_float, _vp, _i64, _i64, _vp]),
     "cg_b200_softmax_layernorm": (_i, [_i, _vp, _vp, _vp, C.c_float, _vp, _i64, _i64, _vp]),
+    "cg_b200_reduce": (_i, [_i, _i, _vp, _vp, _i64, _i64, _i64, _vp]),
     "cg_b200_attention": (_i, [C.POINTER(AttentionDesc), _vp, _vp, _vp, _vp, _vp]),
     "cg_b200_gemm_workspace_bytes": (_i, [C.POINTER(GemmDesc), C.POINTER(_sz)]),
     "cg_b200_gemm": (_i, [C.POINTER(GemmDesc), _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),

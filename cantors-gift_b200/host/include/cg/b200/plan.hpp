@@ -26,14 +26,15 @@ struct PlanBuffer {
 };
 
 struct PlanRecord {
-    enum Kind : std::uint32_t { Eltwise = 1, Gemm = 2, Softmax = 3, LayerNorm = 4, SoftmaxLayerNorm = 5, Attention = 6 };
+    enum Kind : std::uint32_t { Eltwise = 1, Gemm = 2, Softmax = 3, LayerNorm = 4, SoftmaxLayerNorm = 5, Attention = 6, Reduce = 7 };
     std::uint32_t kind = 0;
     cg_b200_eltwise_desc eltwise{};      // Eltwise
     cg_b200_gemm_desc gemm{};            // Gemm
     cg_b200_gemm_tuning tuning{};        // Gemm: all zero = the library's heuristic
     cg_b200_attention_desc attention{};  // Attention
     std::int32_t row_dtype = 0;          // row reductions
-    std::int64_t rows = 0, cols = 0;
+    std::int64_t rows = 0, cols = 0;     // Reduce: outer and reduced extent of the [outer, reduce, inner] box (inner in n)
+    std::int32_t reduce_op = 0;          // Reduce: cg_b200_reduce_op
     float eps = 1e-5f;
     std::uint64_t n = 0;                 // Eltwise: elements
     std::int32_t n_inputs = 0;

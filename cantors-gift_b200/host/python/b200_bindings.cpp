@@ -126,8 +126,8 @@ PYBIND11_MODULE(cg_b200_ext, m) {
         py::list out;
         auto plan = b200::LaunchPlan::deserialize(exe.machine_code);
         if (!plan) return out;
-        static const char* names[] = {"?", "eltwise", "gemm", "softmax", "layernorm", "softmax_layernorm", "attention"};
-        for (const auto& r : plan->records) out.append(std::string(names[r.kind <= 6 ? r.kind : 0]));
+        static const char* names[] = {"?", "eltwise", "gemm", "softmax", "layernorm", "softmax_layernorm", "attention", "reduce"};
+        for (const auto& r : plan->records) out.append(std::string(names[r.kind <= 7 ? r.kind : 0]));
         return out;
     }, "Kernel names of the launch plan an Executable carries (empty for text-only executables).");
 

@@ -6,7 +6,7 @@
 namespace cg::b200 {
 namespace {
 
-constexpr std::uint32_t kPlanVersion = 2;
+constexpr std::uint32_t kPlanVersion = 3;
 
 struct Out {
     std::vector<std::uint8_t> bytes;
@@ -81,7 +81,7 @@ std::optional<LaunchPlan> LaunchPlan::deserialize(const std::vector<std::uint8_t
     for (std::uint32_t i = 0; i < nr; ++i) {
         PlanRecord r = in.get<PlanRecord>();
         if (!in.ok) return std::nullopt;
-        if (r.kind < PlanRecord::Eltwise || r.kind > PlanRecord::Attention) return std::nullopt;
+        if (r.kind < PlanRecord::Eltwise || r.kind > PlanRecord::Reduce) return std::nullopt;
         for (std::int32_t b : r.input)
             if (!in_range(b)) return std::nullopt;
         for (std::int64_t o : r.input_offset)

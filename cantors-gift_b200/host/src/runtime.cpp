@@ -207,6 +207,10 @@ private:
                                           at(r.input[2], r.input_offset[2], dt), at(r.output, r.output_offset, dt), st);
                     break;
                 }
+                case b200::PlanRecord::Reduce:
+                    s = cg_b200_reduce(r.row_dtype, r.reduce_op, at(r.input[0], r.input_offset[0], r.row_dtype),
+                                       at(r.output, r.output_offset, r.row_dtype), r.rows, r.cols, static_cast<std::int64_t>(r.n), st);
+                    break;
                 default: s = CG_B200_ERR_INVALID_ARG;
             }
             if (s != CG_B200_OK) return s;   // the reference's launch returns silently; the status is kept

@@ -737,6 +737,41 @@ struct Planner {
                       "rows=" + std::to_string(r.rows) + " cols=" + std::to_string(r.cols));
     }
 
+    // ---- reductions over axes --------------------------------------------------------------------------------
+    // reduce_sum / reduce_max / reduce_mean (src/ir/ops.cpp:74-102, 417-436): `axes` (negative = from the end),
+    // `keep_dims`. A run of adjacent axes of a contiguous operand is a [outer, reduce, inner] box and has a
+    // kernel; anything else stays in the generic instruction stream only.
+    void plan_reduce(int id) {
+        const Node& nd = nodes[id];
+        const Node& in = nodes[nd.in[0]];
+        const int dt = abi_dtype(nd.dtype);
+        auto axes = nd.src ? nd.src->attributes.get("axes") : nullptr;
+        if (dt < 0 || !axes || axes->ints.empty()) throw Fail(CG_B200_ERR_UNSUPPORTED, "reduce: unsupported type or no axes");
+        const i64 rank = static_cast<i64>(in.shape.size());
+        std::vector<i64> ax;
+        for (i64 a : axes->ints) {
+            if (a < 0) a += rank;
+            if (a < 0 || a >= rank) throw Fail(CG_B200_ERR_UNSUPPORTED, "reduce: axis out of range");
+            if (std::find(ax.begin(), ax.end(), a) == ax.end()) ax.push_back(a);
+        }
+        std::sort(ax.begin(), ax.end());
+        if (ax.back() - ax.front() + 1 != static_cast<i64>(ax.size()))
+            throw Fail(CG_B200_ERR_UNSUPPORTED, "reduce: the reduced axes are not adjacent (no B200 kernel)");
+        PlanRecord r;
+        r.kind = PlanRecord::Reduce;
+        r.row_dtype = dt;
+        r.reduce_op = nd.op == OP_REDUCE_SUM ? CG_B200_REDUCE_SUM : (nd.op == OP_REDUCE_MAX ? CG_B200_REDUCE_MAX : CG_B200_REDUCE_MEAN);
+        i64 outer = 1, red = 1, inner = 1;
+        for (i64 i = 0; i < rank; ++i) (i < ax.front() ? outer : (i > ax.back() ? inner : red)) *= in.shape[static_cast<usize>(i)];
+        if (red == 0) throw Fail(CG_B200_ERR_UNSUPPORTED, "reduce: empty reduced extent");
+        r.rows = outer;
+        r.cols = red;
+        r.n = static_cast<u64>(inner);
+        r.n_inputs = 1;
+        contiguous_operand(nd.in[0], &r.input[0], &r.input_offset[0], "reduce");
+        finish_kernel(id, r, "reduce", "outer=" + std::to_string(outer) + " reduce=" + std::to_string(red) + " inner=" + std::to_string(inner));
+    }
+
     // ---- elementwise trees ---------------------------------------------------------------------------------------
     struct EwBuild {
         cg_b200_eltwise_desc d{};
@@ -971,6 +1006,7 @@ struct Planner {
                     break;
                 }
                 case OP_SOFTMAX: case OP_LAYERNORM: plan_row(i); break;
+                case OP_REDUCE_SUM: case OP_REDUCE_MAX: case OP_REDUCE_MEAN: plan_reduce(i); break;
                 default:
                     if (is_view(nd.op)) break;
                     if (!is_eltwise(nd.op))

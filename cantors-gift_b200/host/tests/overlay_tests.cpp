@@ -330,6 +330,41 @@ TEST(B200Lowering, OpsWithoutAKernelLeaveTheGenericStreamOnly) {
     EXPECT_FALSE(cg.functions[0].instructions.empty());
 }
 
+TEST(B200Lowering, ReductionsOverAdjacentAxesBecomeKernels) {
+    auto mean_of = [](Builder& b, Value a, std::vector<i64> axes, bool keep) {   // the builder has no reduce_mean helper
+        AttributeDict attrs;
+        attrs.set("axes", Attribute::make_int_array(std::move(axes)));
+        attrs.set("keep_dims", Attribute::make_bool(keep));
+        return b.create(OP_REDUCE_MEAN, {a}, std::move(attrs))->results[0];
+    };
+    Module m;
+    auto f = m.create_function("reductions", {tt({4, 6, 8}, DType::BF16)},
+                               {tt({4}, DType::BF16), tt({4, 6, 1}, DType::BF16), tt({6, 8}, DType::BF16)});
+    Builder b(f);
+    Value x = f->args()[0];
+    b.output_tensor(b.reduce_sum(x, {1, 2}));
+    b.output_tensor(b.reduce_max(x, {-1}, true));
+    b.output_tensor(mean_of(b, x, {0}, false));
+    CGModule cg = TensorToCodegenLowering().lower(m);
+    EXPECT_EQ(b200::last_lowering_status(), static_cast<int>(CG_B200_OK));
+    auto recs = records_of(cg.functions[0]);
+    EXPECT_EQ(recs.size(), 3u);
+    if (recs.size() != 3) return;
+    for (const auto& r : recs) EXPECT_EQ(r.kind, static_cast<u32>(PlanRecord::Reduce));
+    EXPECT_TRUE(recs[0].reduce_op == CG_B200_REDUCE_SUM && recs[0].rows == 4 && recs[0].cols == 48 && recs[0].n == 1);
+    EXPECT_TRUE(recs[1].reduce_op == CG_B200_REDUCE_MAX && recs[1].rows == 24 && recs[1].cols == 8 && recs[1].n == 1);
+    EXPECT_TRUE(recs[2].reduce_op == CG_B200_REDUCE_MEAN && recs[2].rows == 1 && recs[2].cols == 4 && recs[2].n == 48);
+    // axes that are not adjacent have no kernel: the generic stream alone, and a status that says so
+    Module m2;
+    auto f2 = m2.create_function("gapped", {tt({4, 6, 8}, DType::F32)}, {tt({6}, DType::F32)});
+    Builder b2(f2);
+    b2.output_tensor(b2.reduce_sum(f2->args()[0], {0, 2}));
+    CGModule cg2 = TensorToCodegenLowering().lower(m2);
+    EXPECT_EQ(b200::last_lowering_status(), static_cast<int>(CG_B200_ERR_UNSUPPORTED));
+    EXPECT_TRUE(records_of(cg2.functions[0]).empty());
+    EXPECT_FALSE(cg2.functions[0].instructions.empty());
+}
+
 TEST(B200Lowering, ScheduleTilesChooseTheGemmKernel) {
     auto space = ScheduleSpace::grid_matmul({128, 256}, {64, 128, 256}, {64}, {8});
     EXPECT_EQ(space.size(), 6u);
@@ -592,6 +627,50 @@ TEST(B200Gpu, ChainRunsBitExact) {
     bound->launch(two, out, *g.stream);
     EXPECT_EQ(b200::last_launch_status(), static_cast<int>(CG_B200_ERR_INVALID_ARG));
     for (Tensor* t : {&ta, &tb, &tc, &ty}) b200::release_tensor(*g.dev, *t);
+}
+
+TEST(B200Gpu, ReductionsMatchAHostLoop) {
+    if (!gpu_mode()) return;
+    Gpu g;
+    if (!g.dev) { EXPECT_TRUE(false); return; }
+    const i64 A = 33, R = 170, C = 9;
+    Module m;
+    auto f = m.create_function("reductions", {tt({A, R, C}, DType::F32)}, {tt({A, C}, DType::F32), tt({A, R}, DType::F32)});
+    {
+        Builder b(f);
+        b.output_tensor(b.reduce_sum(f->args()[0], {1}));     // strided: inner = C
+        b.output_tensor(b.reduce_max(f->args()[0], {2}));     // rows: inner = 1
+    }
+    auto bound = g.compile(m);
+    EXPECT_TRUE(bound != nullptr);
+    if (!bound) return;
+    auto x = randn(A * R * C, 11);
+    Tensor tx = g.upload(x.data(), {A, R, C}, DType::F32);
+    Tensor ts = b200::make_tensor(*g.dev, {A, C}, DType::F32), tm = b200::make_tensor(*g.dev, {A, R}, DType::F32);
+    std::vector<Tensor*> in = {&tx}, out = {&ts, &tm};
+    bound->launch(in, out, *g.stream);
+    EXPECT_EQ(b200::last_launch_status(), static_cast<int>(CG_B200_OK));
+    std::vector<float> sum(A * C), mx(A * R);
+    b200::copy_to_host(sum.data(), ts, ts.num_bytes, *g.stream);
+    b200::copy_to_host(mx.data(), tm, tm.num_bytes, *g.stream);
+    g.stream->sync();
+    double worst = 0.0;
+    bool max_exact = true;
+    for (i64 a = 0; a < A; ++a) {
+        for (i64 c = 0; c < C; ++c) {
+            double acc = 0.0;
+            for (i64 r = 0; r < R; ++r) acc += x[(a * R + r) * C + c];
+            worst = std::max(worst, std::fabs(acc - sum[a * C + c]));
+        }
+        for (i64 r = 0; r < R; ++r) {
+            float v = x[(a * R + r) * C];
+            for (i64 c = 1; c < C; ++c) v = std::max(v, x[(a * R + r) * C + c]);
+            max_exact = max_exact && v == mx[a * R + r];
+        }
+    }
+    EXPECT_LT(worst, 1e-4);
+    EXPECT_TRUE(max_exact);
+    for (Tensor* t : {&tx, &ts, &tm}) b200::release_tensor(*g.dev, *t);
 }
 
 TEST(B200Gpu, MlpAndLateEpilogueOperandMatchTheOracle) {

@@ -64,6 +64,40 @@ def softmax_layernorm(x, gamma=None, beta=None, eps=1e-5, out=None, stream=None)
     return out
 
 
+def reduce_box(shape, axes):
+    """(outer, reduce, inner) of a row-major tensor reduced over `axes`, or None when the axes are not a run of
+    adjacent ones (no kernel then). Negative axes count from the end, as in the reference's shape inference."""
+    rank = len(shape)
+    ax = sorted({a + rank if a < 0 else a for a in axes})
+    if not ax or ax[0] < 0 or ax[-1] >= rank or ax != list(range(ax[0], ax[-1] + 1)):
+        return None
+    outer = inner = red = 1
+    for i, d in enumerate(shape):
+        if i < ax[0]:
+            outer *= d
+        elif i > ax[-1]:
+            inner *= d
+        else:
+            red *= d
+    return outer, red, inner
+
+
+def reduce(x, op, axes, keep_dims=False, out=None, stream=None):
+    """reduce_sum / reduce_max / reduce_mean (op: "sum" | "max" | "mean") of a contiguous tensor over adjacent axes."""
+    _require_cuda(x, out)
+    box = reduce_box(tuple(x.shape), axes)
+    if box is None or not x.is_contiguous():
+        raise ValueError("reduce: the axes must be adjacent and the tensor contiguous")
+    outer, red, inner = box
+    rank = x.dim()
+    ax = {a + rank if a < 0 else a for a in axes}
+    shape = [1 if i in ax else d for i, d in enumerate(x.shape) if keep_dims or i not in ax]
+    out = torch.empty(shape, dtype=x.dtype, device=x.device) if out is None else out
+    check(lib().cg_b200_reduce(DTYPE_OF_TORCH[x.dtype], capi.REDUCE[op], _ptr(x), _ptr(out), outer, red, inner,
+                               _stream(stream)), "reduce")
+    return out
+
+
 _workspaces = {}
 
 

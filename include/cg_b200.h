@@ -199,6 +199,17 @@ int cg_b200_softmax_layernorm(int dtype, const void* in, const void* gamma,
                               const void* beta, float eps, void* out, int64_t rows,
                               int64_t cols, void* stream);
 
+/* ---- reductions over a run of adjacent axes -----------------------------------------
+ * Replaces the reduce lowering (VectorLoad, Reduce, VectorStore, src/lowering/tensor_to_codegen.cpp:332;
+ * CGOpcode::Reduce is a comment in the PTX emitter, src/backend/ptx/ptx_emitter.cpp:136-142). Semantics
+ * follow OP_REDUCE_SUM / _MAX / _MEAN (src/ir/ops.cpp:74-102, 417-436): the reduced axes of a row-major
+ * tensor, when adjacent, make it a [outer, reduce, inner] box; out is [outer, inner] (keep_dims changes
+ * the result's shape only). Accumulation in fp32, one rounding to `dtype`; mean = sum / reduce; max
+ * ignores NaN operands (fmaxf). outer == 0 or inner == 0: no-op; reduce == 0: CG_B200_ERR_INVALID_ARG. */
+enum cg_b200_reduce_op { CG_B200_REDUCE_SUM = 0, CG_B200_REDUCE_MAX = 1, CG_B200_REDUCE_MEAN = 2 };
+int cg_b200_reduce(int dtype, int op, const void* in, void* out, int64_t outer, int64_t reduce,
+                   int64_t inner, void* stream);
+
 /* ---- GEMM with fused epilogue -----------------------------------------------------
  * Replaces the matmul lowering (3 Const, 2 shared VectorLoad, K/k_tile FMA,
  * src/lowering/tensor_to_codegen.cpp:137-210) and the mma.sync skeleton

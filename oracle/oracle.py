@@ -259,6 +259,22 @@ def ref_matmul(A, B):
 
 
 # ---- attention (restatement: matmul, softmax, matmul with fp32 intermediates) --------------------
+def reduce(x, dtype, op, axes, keep_dims=False):
+    """reduce_sum / reduce_max / reduce_mean (op: "sum" | "max" | "mean") over `axes` of x in storage representation
+    (src/ir/ops.cpp:74-102, 417-436: `axes`, `keep_dims`, result dtype = operand dtype). Sums in double, one
+    rounding to `dtype`; max ignores NaN operands. PARITY UNPINNED: the reference lowers these ops to a Reduce
+    instruction its emitters print as a comment (src/backend/ptx/ptx_emitter.cpp:136-142)."""
+    f = to_f32(x, dtype).astype(np.float64)
+    ax = tuple(axes)
+    if op == "sum":
+        r = f.sum(axis=ax, keepdims=keep_dims)
+    elif op == "mean":
+        r = f.mean(axis=ax, keepdims=keep_dims)
+    else:
+        r = np.fmax.reduce(f, axis=ax, keepdims=keep_dims)
+    return to_storage(np.asarray(r, dtype=np.float32), dtype)
+
+
 def attention(q, k, v, dtype, scale):
     """q: [B, H, Sq, d], k/v: [B, H, Skv, d] in storage representation. Scores and probabilities stay
     fp32 (no rounding between the three ops); the result is rounded to `dtype`. PARITY UNPINNED:
