@@ -143,6 +143,54 @@ private:
     Opcode opc_;
 };
 
+// reduce_sum / reduce_max / reduce_mean over adjacent axes (the [outer, reduce, inner] box of cg_b200_reduce).
+class B200Reduce final : public VendorKernel {
+public:
+    explicit B200Reduce(Opcode opc) : opc_(opc) {}
+    VendorKind vendor() const override { return VendorKind::CUTLASS; }
+    std::string name() const override {
+        return opc_ == OP_REDUCE_SUM ? "cg_b200_reduce_sum" : (opc_ == OP_REDUCE_MAX ? "cg_b200_reduce_max" : "cg_b200_reduce_mean");
+    }
+    Opcode opcode() const override { return opc_; }
+    bool supports(const Operation& op) const override {
+        i64 box[3];
+        return op.opcode == opc_ && box_of(op, box);
+    }
+    bool execute(const Operation& op, void* stream) override {
+        i64 box[3];
+        if (op.opcode != opc_ || !box_of(op, box)) return false;
+        void *in = pointer_attr(op, "b200.in0"), *out = pointer_attr(op, "b200.out0");
+        if (!in || !out) return false;
+        const int rop = opc_ == OP_REDUCE_SUM ? CG_B200_REDUCE_SUM : (opc_ == OP_REDUCE_MAX ? CG_B200_REDUCE_MAX : CG_B200_REDUCE_MEAN);
+        return cg_b200_reduce(abi_dtype(op.operands[0].as_tensor()->dtype), rop, in, out, box[0], box[1], box[2], stream) == CG_B200_OK;
+    }
+
+private:
+    static bool box_of(const Operation& op, i64 (&box)[3]) {
+        if (op.operands.size() != 1) return false;
+        auto x = op.operands[0].as_tensor();
+        auto axes = op.attributes.get("axes");
+        std::vector<i64> s;
+        if (!x || abi_dtype(x->dtype) < 0 || !axes || axes->ints.empty() || !static_dims(*x, s)) return false;
+        const i64 rank = static_cast<i64>(s.size());
+        i64 lo = rank, hi = -1;
+        std::vector<char> seen(s.size(), 0);
+        usize distinct = 0;
+        for (i64 a : axes->ints) {
+            if (a < 0) a += rank;
+            if (a < 0 || a >= rank) return false;
+            if (!seen[static_cast<usize>(a)]) { seen[static_cast<usize>(a)] = 1; ++distinct; }
+            lo = std::min(lo, a);
+            hi = std::max(hi, a);
+        }
+        if (hi - lo + 1 != static_cast<i64>(distinct)) return false;   // not a run of adjacent axes
+        box[0] = box[1] = box[2] = 1;
+        for (i64 i = 0; i < rank; ++i) box[i < lo ? 0 : (i > hi ? 2 : 1)] *= s[static_cast<usize>(i)];
+        return box[1] > 0;
+    }
+    Opcode opc_;
+};
+
 // One elementwise op over whole tensors of one shape (broadcasts go through the planner).
 class B200Eltwise final : public VendorKernel {
 public:
@@ -216,6 +264,7 @@ VendorDispatcher::VendorDispatcher() {
     register_kernel(std::make_unique<B200Gemm>());
     register_kernel(std::make_unique<B200Row>(OP_SOFTMAX));
     register_kernel(std::make_unique<B200Row>(OP_LAYERNORM));
+    for (Opcode opc : {OP_REDUCE_SUM, OP_REDUCE_MAX, OP_REDUCE_MEAN}) register_kernel(std::make_unique<B200Reduce>(opc));
     const struct { Opcode opc; int ew; int arity; } ops[] = {
         {OP_ADD, CG_B200_EW_ADD, 2}, {OP_SUB, CG_B200_EW_SUB, 2}, {OP_MUL, CG_B200_EW_MUL, 2}, {OP_DIV, CG_B200_EW_DIV, 2},
         {OP_NEG, CG_B200_EW_NEG, 1}, {OP_RELU, CG_B200_EW_RELU, 1}, {OP_GELU, CG_B200_EW_GELU_TANH, 1},

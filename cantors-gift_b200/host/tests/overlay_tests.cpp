@@ -867,4 +867,27 @@ TEST(B200Gpu, VendorKernelsExecuteOnBoundPointers) {
     g.stream->sync();
     cgo_softmax(CG_B200_F32, x.data(), want.data(), 64, 128);
     EXPECT_LE(max_rel(got, want), 1e-4);
+    // a reduction through the dispatcher: column maxima of the same tensor
+    auto f2 = m.create_function("colmax", {tt({64, 128}, DType::F32)}, {tt({128}, DType::F32)});
+    Builder b2(f2);
+    b2.output_tensor(b2.reduce_max(f2->args()[0], {0}));
+    Operation* rop = nullptr;
+    for (auto& o : *f2->entry())
+        if (o.opcode == OP_REDUCE_MAX) rop = &o;
+    Tensor tm = b200::make_tensor(*g.dev, {128}, DType::F32);
+    b200::bind_pointers(*rop, {tx.data}, tm.data);
+    VendorKernel* rk = VendorDispatcher::instance().find_best(*rop);
+    EXPECT_TRUE(rk != nullptr && rk->name() == "cg_b200_reduce_max");
+    if (!rk) return;
+    EXPECT_TRUE(rk->execute(*rop, b200::native_stream(*g.stream)));
+    std::vector<float> cm(128);
+    b200::copy_to_host(cm.data(), tm, tm.num_bytes, *g.stream);
+    g.stream->sync();
+    bool exact = true;
+    for (int c = 0; c < 128; ++c) {
+        float v = x[c];
+        for (int r = 1; r < 64; ++r) v = std::max(v, x[r * 128 + c]);
+        exact = exact && v == cm[c];
+    }
+    EXPECT_TRUE(exact);
 }

@@ -149,3 +149,30 @@ def test_gemm_epilogues_and_batch(oracle):
     mask = np.ones(Bt * M, dtype=bool)
     mask[rows] = False
     assert not part[mask].any()
+
+
+def test_reduce_definitions_and_boxes(oracle):
+    """reduce_sum / reduce_max / reduce_mean of the oracle against their definitions (src/ir/ops.cpp:74-102: axes,
+    keep_dims, result dtype = operand dtype), and the [outer, reduce, inner] box the kernel is given."""
+    from cantors_gift_b200 import ops
+    O = oracle
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((3, 4, 5), dtype=np.float32)
+    xs = O.to_storage(x, O.BF16)
+    xf = O.to_f32(xs, O.BF16).astype(np.float64)
+    for axes in ([0], [1], [2], [-1], [0, 1], [1, 2], [0, 1, 2]):
+        for keep in (False, True):
+            ax = tuple(axes)
+            got = O.to_f32(O.reduce(xs, O.BF16, "sum", axes, keep), O.BF16)
+            want = O.to_f32(O.to_storage(np.asarray(xf.sum(axis=ax, keepdims=keep), dtype=np.float32), O.BF16), O.BF16)
+            assert np.array_equal(got.reshape(want.shape), want)
+            got = O.to_f32(O.reduce(xs, O.BF16, "max", axes, keep), O.BF16)
+            assert np.array_equal(got.reshape(xf.max(axis=ax, keepdims=keep).shape), xf.max(axis=ax, keepdims=keep).astype(np.float32))
+    # max ignores NaN, sum does not
+    y = np.array([[1.0, np.nan, 3.0]], dtype=np.float32)
+    assert O.reduce(y, O.F32, "max", [1])[0] == 3.0 and np.isnan(O.reduce(y, O.F32, "sum", [1])[0])
+    assert ops.reduce_box((3, 4, 5), [1]) == (3, 4, 5)
+    assert ops.reduce_box((3, 4, 5), [-1]) == (12, 5, 1)
+    assert ops.reduce_box((3, 4, 5), [0, 1]) == (1, 12, 5)
+    assert ops.reduce_box((3, 4, 5), [2, 1, 0]) == (1, 60, 1)
+    assert ops.reduce_box((3, 4, 5), [0, 2]) is None and ops.reduce_box((3, 4, 5), [3]) is None
