@@ -211,8 +211,13 @@ __device__ __forceinline__ void eval_lanes(const EltParams& p, const Prog& prog,
 // block 0. The grid normally covers the whole array (see launch_typed), so most threads make one
 // trip: with the registers of a single packet the kernel runs at full occupancy, which measured
 // faster on B200 than two packets per thread at half occupancy.
+// A 16-bit packet is eight fp32 lanes per stack slot: under the 32 registers of eight resident CTAs those kernels
+// spill, so they are built for five (compile-time chains, 48 registers) or four (run-time interpreter, 64).
 template <typename T, typename Prog>
-__global__ void __launch_bounds__(256, 8) eltwise_vec_kernel(const __grid_constant__ EltParams p) {
+constexpr int vec_min_ctas() { return sizeof(T) == 2 ? (Prog::kStatic ? 5 : 4) : 8; }
+
+template <typename T, typename Prog>
+__global__ void __launch_bounds__(256, (vec_min_ctas<T, Prog>())) eltwise_vec_kernel(const __grid_constant__ EltParams p) {
     constexpr int L = 16 / sizeof(T);
     const Prog prog(p);
     T* out = static_cast<T*>(p.out);
