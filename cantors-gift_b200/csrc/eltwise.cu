@@ -211,10 +211,12 @@ __device__ __forceinline__ void eval_lanes(const EltParams& p, const Prog& prog,
 // block 0. The grid normally covers the whole array (see launch_typed), so most threads make one
 // trip: with the registers of a single packet the kernel runs at full occupancy, which measured
 // faster on B200 than two packets per thread at half occupancy.
-// A 16-bit packet is eight fp32 lanes per stack slot: under the 32 registers of eight resident CTAs those kernels
-// spill, so they are built for five (compile-time chains, 48 registers) or four (run-time interpreter, 64).
+// A 16-bit packet is eight fp32 lanes per stack slot. The run-time interpreter for those types keeps four slots
+// alive and spilled heavily under the 32 registers of eight resident CTAs (0.85 TB/s on gelu(a*b)+c in bf16); built
+// for four CTAs (64 registers) it runs at 1.9 TB/s. The compile-time chains spill a few words at 32 registers and
+// measured the same or faster that way (4.6 vs 4.2 TB/s on relu(a*b+c)*s in bf16), so they keep eight.
 template <typename T, typename Prog>
-constexpr int vec_min_ctas() { return sizeof(T) == 2 ? (Prog::kStatic ? 5 : 4) : 8; }
+constexpr int vec_min_ctas() { return (sizeof(T) == 2 && !Prog::kStatic) ? 4 : 8; }
 
 template <typename T, typename Prog>
 __global__ void __launch_bounds__(256, (vec_min_ctas<T, Prog>())) eltwise_vec_kernel(const __grid_constant__ EltParams p) {
