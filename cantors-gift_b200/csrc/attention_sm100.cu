@@ -11,23 +11,29 @@
 // way while the softmax groups finish the current one (no fill and drain per unit; the Q tiles are
 // double-buffered for that). Both query tiles meet each
 // K/V tile while it is in shared memory, which halves the K/V traffic from L2 - the first limit of a
-// one-tile CTA at head_dim 64. Work item w = 2 j + g is (key tile j, query tile g):
+// one-tile CTA at head_dim 64. Query tile g (0 or 1) owns a score buffer S_g (128 TMEM columns), a
+// probability buffer P_g (64 columns: two 16-bit keys per column) and an output accumulator O_g (64):
 //   warp 8     TMA: the two Q tiles of a unit, then K and V tiles of 128 key rows through a 5-stage ring
-//   warp 9     issues S_w = Q_g K_j^T (128 x 128 x 64) into TMEM score buffer w%3 and
-//              O_g += P_w V_j (128 x 64 x 128, P_w read from TMEM) into the TMEM output accumulator of
-//              query tile g (the first product of a unit starts it). The warp runs its loop converged
-//              and one elected lane issues, which keeps descriptors and addresses in uniform
-//              registers. S_{w+3} is issued right behind the product of item w, so the scores of a
-//              group's next item are complete before the group asks for them.
+//   warps 9,10 one issuing warp per query tile. For key tile j of its tile g the warp issues
+//              S_g = Q_g K_j^T (128 x 128 x 64) as soon as the softmax group has taken the previous scores
+//              out of S_g, i.e. while the group is still computing on them, and O_g += P_g V_j
+//              (128 x 64 x 128, P_g read from TMEM) when the group has written P_g. The two warps share
+//              nothing but the in-order tensor pipe, so neither waits for the other query tile's softmax,
+//              and each runs a short loop (two waits, twelve MMAs, three commits per key tile): with one
+//              warp issuing for both tiles in item order, that warp's own instruction stream - waits,
+//              fences, address arithmetic, about 2400 cycles per item - set the pace of the whole kernel.
+//              The loop runs converged and one elected lane issues, which keeps descriptors and addresses
+//              in uniform registers.
 //   warps 0-3  softmax group 0: query tile 0;  warps 4-7  softmax group 1: query tile 1 (two whole
-//              warpgroups, which take the registers the third one gives up: 232 per thread).
+//              warpgroups, which take the registers the third one gives up: 216 per thread).
 //              One thread per query row, so no exchange between threads: the row's 128 scores are read
-//              from TMEM once into registers, row max, p = 2^(s - m), row sum, and P_w is written as
-//              bf16/f16 pairs over the first 64 columns of the same score buffer. m is a reference
+//              from TMEM once into registers (S_g is free again from that moment), row max,
+//              p = 2^(s - m), row sum, and P is written as bf16/f16 pairs into P_g once the previous
+//              product has read it. m is a reference
 //              maximum that follows the running maximum only when that has grown by more than 2^8, so
 //              the output accumulator in tensor memory is rescaled (O *= 2^(m_old - m_new), by the row's
 //              own thread) only on those rare occasions instead of on every key tile. The two warps that
-//              share a scheduler belong to different groups, i.e. to different items in different
+//              share a scheduler belong to different groups, i.e. to different key tiles in different
 //              phases: one runs its exponentials while the other loads, reduces or waits.
 // Q, K, V are read in place from strided buffers (head = 64 contiguous columns of a row), so the
 // packed [rows, 3*d_model] output of a QKV projection needs no reshuffle. head_dim is 64.
@@ -47,9 +53,8 @@ constexpr int kAttnQRows = 2 * kAttnBM;   // query rows per CTA
 constexpr int kAttnBN = 128;          // key rows per step
 constexpr int kAttnD = 64;            // head dim: 128 bytes of bf16 = one swizzle span
 constexpr int kAttnKVStages = 5;
-constexpr int kAttnSBufs = 3;
-constexpr int kAttnThreads = 384;        // three warpgroups: softmax group 0, softmax group 1, {TMA, MMA, two idle warps}
-constexpr int kAttnTmaWarp = 8, kAttnMmaWarp = 9;
+constexpr int kAttnThreads = 384;        // three warpgroups: softmax group 0, softmax group 1, {TMA, two MMA warps, one idle warp}
+constexpr int kAttnTmaWarp = 8, kAttnMmaWarp = 9;   // MMA warps: 9 (query tile 0) and 10 (query tile 1)
 // Registers per thread after the warpgroups re-divide the register file. The kernel is launched with
 // 168 per thread (65536 / 384, rounded down to a multiple of 8); an increase waits in hardware, without
 // a time limit, until that many registers are free, so the new shares must fit in what the launch
@@ -60,8 +65,9 @@ static_assert(2 * 128 * kAttnSoftmaxRegs + 128 * kAttnIssueRegs <= kAttnThreads 
 constexpr int kAttnTileBytes = 128 * 128;                 // a 128-row x 128-byte tile (Q, K or V)
 constexpr int kAttnSmem = 2 * 2 * kAttnTileBytes + kAttnKVStages * 2 * kAttnTileBytes + 1024;
 constexpr uint32_t kAttnTmemCols = 512;
-constexpr uint32_t kAttnSCol = 0;     // three score buffers of 128 columns; P over the first 64 of each
-constexpr uint32_t kAttnTCol = 384;   // two output accumulators (one per query tile) of 64 columns
+constexpr uint32_t kAttnSCol = 0;     // two score buffers (one per query tile) of 128 columns
+constexpr uint32_t kAttnPCol = 256;   // two probability buffers of 64 columns (two 16-bit keys per column)
+constexpr uint32_t kAttnTCol = 384;   // two output accumulators of 64 columns
 
 struct AttnParams {
     long long S_q, S_kv;
@@ -100,7 +106,7 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_q_full[2], bar_q_empty[2];
     __shared__ __align__(8) uint64_t bar_kv_full[kAttnKVStages], bar_kv_empty[kAttnKVStages];
-    __shared__ __align__(8) uint64_t bar_s_full[kAttnSBufs], bar_p_full[2], bar_t_full[2];
+    __shared__ __align__(8) uint64_t bar_s_full[2], bar_s_free[2], bar_p_full[2], bar_t_full[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile uint32_t abort_flag;
 
@@ -122,20 +128,20 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         return u;
     };
     const int n_tiles = p.kv_tiles;
-    const int n_items = 2 * n_tiles;   // per unit
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&bar_q_full[i]), 1);
-            mbar_init(smem_u32(&bar_q_empty[i]), 1);
+            mbar_init(smem_u32(&bar_q_empty[i]), 2);   // one commit per MMA warp: both query tiles are through with Q
         }
         for (int s = 0; s < kAttnKVStages; ++s) {
             mbar_init(smem_u32(&bar_kv_full[s]), 1);
-            mbar_init(smem_u32(&bar_kv_empty[s]), 1);
+            mbar_init(smem_u32(&bar_kv_empty[s]), 2);  // one commit per MMA warp
         }
-        for (int i = 0; i < kAttnSBufs; ++i) mbar_init(smem_u32(&bar_s_full[i]), 1);
         for (int i = 0; i < 2; ++i) {
-            mbar_init(smem_u32(&bar_p_full[i]), 4);    // one arrival per warp of the group
+            mbar_init(smem_u32(&bar_s_full[i]), 1);
+            mbar_init(smem_u32(&bar_s_free[i]), 4);    // one arrival per warp of the group
+            mbar_init(smem_u32(&bar_p_full[i]), 4);
             mbar_init(smem_u32(&bar_t_full[i]), 1);
         }
         abort_flag = 0;
@@ -188,42 +194,32 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 }
             }
         }
-    } else if (warp == kAttnMmaWarp) {
-        // ---------------- MMA issuer ----------------
-        // The whole warp runs the loop and waits; one elected lane issues (see elect_one()).
-        // Items are numbered through all units of this CTA: W = k * n_items + 2 j + g. S_W goes into score
-        // buffer W%3. The tensor pipe runs its instructions in issue order, and S_W is issued behind
-        // T_{W-3}, the last reader of that buffer (P_{W-3} lives in it). Positions are kept as small
-        // rotating counters: "s" for the scores being issued (three items ahead), "t" for the T behind.
+    } else if (warp == kAttnMmaWarp || warp == kAttnMmaWarp + 1) {
+        // ---------------- MMA issuer of query tile g ----------------
+        // The whole warp runs the loop and waits; one elected lane issues (see elect_one()). Key tiles are
+        // numbered through all units of this CTA: n = k * n_tiles + j. In program order:
+        //   S(0); for every n: [ S(n+1) once the group has read S(n) ]; T(n) once the group has written P(n).
+        const int g = warp - kAttnMmaWarp;
         const uint32_t my_units = (uint32_t)p.units > blockIdx.x ? ((uint32_t)p.units - 1u - blockIdx.x) / gridDim.x + 1u : 0u;
-        const long long total = (long long)my_units * n_items;
-        struct Pos {
-            int w;          // item within the unit
-            uint32_t k;     // unit count
-            int st;         // K/V ring stage of the item's key tile, and the parity of that round
-            uint32_t st_phase;
-            int sb;         // score buffer, and the parity of its current use
-            uint32_t sb_phase;
-        };
-        auto advance = [&](Pos& x) {
-            if (++x.sb == kAttnSBufs) { x.sb = 0; x.sb_phase ^= 1u; }
-            if (x.w & 1) {   // second query tile of the key tile: next key tile
-                if (++x.st == kAttnKVStages) { x.st = 0; x.st_phase ^= 1u; }
-            }
-            if (++x.w == n_items) { x.w = 0; ++x.k; }
-        };
+        const uint32_t total = my_units * (uint32_t)n_tiles;   // < 2^31: units is, and a CTA's share times the key tiles of one head stays far below
+        const uint32_t tmem_s = tmem_base + kAttnSCol + (uint32_t)(g * kAttnBN);
+        const uint32_t tmem_p = tmem_base + kAttnPCol + (uint32_t)(g * kAttnD);
+        const uint32_t tmem_t = tmem_base + kAttnTCol + (uint32_t)(g * kAttnD);
+        // position of the next S: key tile within its unit, unit count, K/V ring stage and its parity
+        int sj = 0, s_st = 0;
+        uint32_t sk = 0, s_st_phase = 0;
+        // position of the next T
+        int tj = 0, t_st = 0;
         bool ok = true;
-        auto prep_s = [&](const Pos& x) -> bool {   // operands of S for item x: Q of a new unit, K of a new key tile
+        auto issue_s = [&]() -> bool {   // S of the key tile at the "s" position; advances it
             bool w = true;
-            if (x.w == 0) w = mbar_wait_poll(smem_u32(&bar_q_full[x.k & 1u]), (x.k >> 1) & 1u, &abort_flag, p.err_word, 0x610u);
-            if (w && !(x.w & 1)) w = mbar_wait_poll(smem_u32(&bar_kv_full[x.st]), x.st_phase, &abort_flag, p.err_word, 0x640u + x.st);
-            return __all_sync(0xffffffffu, w);
-        };
-        auto issue_s = [&](const Pos& x) {   // after prep_s(x)
-            const int g = x.w & 1;
-            const uint32_t qa = s_q + (uint32_t)(x.k & 1u) * 2 * kAttnTileBytes + g * kAttnTileBytes;
-            const uint32_t kb = s_kv + x.st * 2 * kAttnTileBytes;
-            const uint32_t tmem_s = tmem_base + kAttnSCol + (uint32_t)(x.sb * kAttnBN);
+            if (sj == 0) w = mbar_wait_poll(smem_u32(&bar_q_full[sk & 1u]), (sk >> 1) & 1u, &abort_flag, p.err_word, 0x610u + g);
+            if (w) w = mbar_wait_poll(smem_u32(&bar_kv_full[s_st]), s_st_phase, &abort_flag, p.err_word, 0x640u + s_st);
+            if (!__all_sync(0xffffffffu, w)) return false;
+            tc_fence_after();
+            const uint32_t qa = s_q + (sk & 1u) * 2 * kAttnTileBytes + g * kAttnTileBytes;
+            const uint32_t kb = s_kv + s_st * 2 * kAttnTileBytes;
+            const bool last = sj == n_tiles - 1;
             if (elect_one()) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {   // 16 of the 64 head dims per MMA
@@ -231,53 +227,44 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     const uint64_t db = make_smem_desc(kb + k * 32, 16, 1024);
                     umma<false, 1>(tmem_s, da, db, p.idesc_s, k > 0 ? 1u : 0u);
                 }
-                tc_commit<1>(smem_u32(&bar_s_full[x.sb]));
-                if (x.w == n_items - 1) tc_commit<1>(smem_u32(&bar_q_empty[x.k & 1u]));   // last reader of this Q buffer
+                tc_commit<1>(smem_u32(&bar_s_full[g]));
+                if (last) tc_commit<1>(smem_u32(&bar_q_empty[sk & 1u]));   // this query tile's last read of the Q buffer
             }
             __syncwarp();
+            if (++s_st == kAttnKVStages) { s_st = 0; s_st_phase ^= 1u; }
+            if (last) { sj = 0; ++sk; } else ++sj;
+            return true;
         };
-        Pos ps = {0, 0u, 0, 0u, 0, 0u}, pt = ps;
-        long long issued_s = 0;
-        for (; ok && issued_s < kAttnSBufs && issued_s < total; ++issued_s) {
-            ok = prep_s(ps);
+        if (total > 0) ok = issue_s();
+        for (uint32_t n = 0; ok && n < total; ++n) {
+            if (n + 1 < total) {
+                // the group has the scores of tile n in registers: S_g may be overwritten
+                bool w = mbar_wait_poll(smem_u32(&bar_s_free[g]), n & 1u, &abort_flag, p.err_word, 0x630u + g);
+                if (!__all_sync(0xffffffffu, w)) break;
+                if (!issue_s()) break;
+            }
+            // P(n) is written (and, for a unit's first tile, the group has taken the previous unit's output out
+            // of its accumulator)
+            bool ready = mbar_wait_poll(smem_u32(&bar_p_full[g]), n & 1u, &abort_flag, p.err_word, 0x620u + g);
+            if (!__all_sync(0xffffffffu, ready)) break;
             tc_fence_after();
-            if (ok) issue_s(ps);
-            advance(ps);
-        }
-        uint32_t tiles_done[2] = {0u, 0u};   // per query tile: T issued so far = parity source of p_full / t_full
-        for (long long W = 0; ok && W < total; ++W) {
-            const int g = pt.w & 1;
-            // operands of the scores issued behind T_W
-            if (issued_s < total && !prep_s(ps)) break;
-            // P_W is written and S_W read for the last time (and, for a unit's first item, the group has
-            // taken the previous unit's output out of its accumulator)
-            bool ready = mbar_wait_poll(smem_u32(&bar_p_full[g]), tiles_done[g] & 1u, &abort_flag, p.err_word, 0x620u + g);
-            ready = __all_sync(0xffffffffu, ready);
-            if (!ready) break;
-            tc_fence_after();
-            // O_g += P_W V_j: A = P_W in tensor memory, B = V_j ([key, d] with d contiguous: MN-major)
-            const uint32_t tmem_p = tmem_base + kAttnSCol + (uint32_t)(pt.sb * kAttnBN);
-            const uint32_t vb = s_kv + pt.st * 2 * kAttnTileBytes + kAttnTileBytes;
-            const uint32_t tmem_t = tmem_base + kAttnTCol + (uint32_t)(g * kAttnD);
+            // O_g += P V_j: A = P in tensor memory, B = V_j ([key, d] with d contiguous: MN-major)
+            const uint32_t vb = s_kv + t_st * 2 * kAttnTileBytes + kAttnTileBytes;
+            const uint32_t first = tj == 0 ? 0u : 1u;   // the unit's first product starts O
             if (elect_one()) {
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {   // 16 keys per MMA: 8 columns of P
                     const uint64_t db = make_smem_desc(vb + k * 2048, kAttnTileBytes, 1024);
-                    umma_ts(tmem_t, tmem_p + k * 8, db, p.idesc_t, (k > 0 || pt.w >= 2) ? 1u : 0u);   // O += P V; the unit's first product starts O
+                    umma_ts(tmem_t, tmem_p + k * 8, db, p.idesc_t, (k > 0) ? 1u : first);
                 }
                 tc_commit<1>(smem_u32(&bar_t_full[g]));
-                if (g == 1) tc_commit<1>(smem_u32(&bar_kv_empty[pt.st]));   // both query tiles are through with the stage
+                tc_commit<1>(smem_u32(&bar_kv_empty[t_st]));   // this query tile is through with the stage
             }
             __syncwarp();
-            ++tiles_done[g];
-            advance(pt);
-            if (issued_s < total) {
-                issue_s(ps);
-                advance(ps);
-                ++issued_s;
-            }
+            if (++t_st == kAttnKVStages) t_st = 0;
+            if (++tj == n_tiles) tj = 0;
         }
-    }   // (warps 10 and 11 have no role)
+    }   // (warp 11 has no role)
     } else {
         // ---------------- softmax; the output accumulates in tensor memory ----------------
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kAttnSoftmaxRegs));
@@ -297,8 +284,8 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const uint32_t o_addr = tmem_base + lane_base + kAttnTCol + (uint32_t)(g * kAttnD);
         float m, l;
         bool ok = true;
-        int sb = g;               // score buffer of the group's next item (items g, g+2, g+4, ... mod 3) and
-        uint32_t sb_phase = 0;    // the parity of that buffer's current use
+        const uint32_t s_addr = tmem_base + lane_base + kAttnSCol + (uint32_t)(g * kAttnBN);
+        const uint32_t p_addr = tmem_base + lane_base + kAttnPCol + (uint32_t)(g * kAttnD);
         uint32_t tcount = 0;      // key tiles this group has finished, over all units
         auto wait_pv = [&](uint32_t use) -> bool {   // the group's P V product number `use` has completed
             bool w = mbar_wait_poll(smem_u32(&bar_t_full[g]), use & 1u, &abort_flag, p.err_word, 0x660u + g);
@@ -311,8 +298,7 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             m = -INFINITY;
             l = 0.0f;
             for (int j = 0; ok && j < n_tiles; ++j) {
-                const uint32_t s_addr = tmem_base + lane_base + kAttnSCol + (uint32_t)(sb * kAttnBN);
-                bool ready = mbar_wait_poll(smem_u32(&bar_s_full[sb]), sb_phase, &abort_flag, p.err_word, 0x670u + sb);
+                bool ready = mbar_wait_poll(smem_u32(&bar_s_full[g]), tcount & 1u, &abort_flag, p.err_word, 0x670u + g);
                 ready = __all_sync(0xffffffffu, ready);
                 if (!ready) { ok = false; break; }
                 tc_fence_after();
@@ -322,6 +308,10 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #pragma unroll
                 for (int c = 0; c < kKeys / 32; ++c) tmem_ld32_issue(s_addr + c * 32, s[c]);
                 tmem_ld_wait();
+                // the scores are in registers: the next key tile's scores may be written over them
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bar_s_free[g]));
                 if (ragged) {   // only the last key tile: mask the zero-filled keys
 #pragma unroll
                     for (int c = 0; c < kKeys / 32; ++c) {
@@ -372,8 +362,16 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     l *= alpha;
                     m = m_new;
                 }
+                // P_g is rewritten below: the group's previous product, which reads it, must have run. (It was
+                // issued when all four warps had announced the previous P, a key tile's worth of work ago, so by
+                // now it has normally long finished. The same wait keeps a fast warp from announcing its part of
+                // this tile's P while a slower warp has not yet announced the previous one.)
+                if (!pv_seen) {
+                    ok = wait_pv(tcount - 1u);
+                    if (!ok) break;
+                }
                 // p = 2^(s * scale * log2e - m), two keys per instruction where the ISA allows it (fp32x2 fma /
-                // add, packed convert). P goes over the first 64 columns of the score buffer, two keys per column.
+                // add, packed convert), two keys per column of P_g.
                 float2 l2 = make_float2(0.0f, 0.0f);
                 const float2 sc2 = make_float2(p.scale_log2e, p.scale_log2e), nm2 = make_float2(-m, -m);
 #pragma unroll
@@ -386,29 +384,15 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                         l2 = __fadd2_rn(l2, ex);
                         pk[i >> 1] = pack_pair<T>(ex.x, ex.y);
                     }
-                    tmem_st16(s_addr + c * 16, pk);   // keys 32c .. 32c+31 of this row
+                    tmem_st16(p_addr + c * 16, pk);   // keys 32c .. 32c+31 of this row
                 }
-                // P (and a rescaled O) are complete in tensor memory; the scores have been read
+                // P (and a rescaled O) are complete in tensor memory
                 tmem_wait_st();
-                // A warp may not announce P of this item before the group's previous product has run: that
-                // product was issued only after all four warps of the group had announced their part of it, so
-                // this keeps a fast warp from arriving twice in one phase of the barrier (its arrival for this
-                // item counted in place of a slower warp's for the previous one). By now the product has
-                // normally long finished.
-                if (!pv_seen) {
-                    ok = wait_pv(tcount - 1u);
-                    if (!ok) break;
-                }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bar_p_full[g]));
                 l += l2.x + l2.y;
                 ++tcount;
-                sb += 2;
-                if (sb >= kAttnSBufs) {
-                    sb -= kAttnSBufs;
-                    sb_phase ^= 1u;
-                }
             }
             // the unit's output: O / l, once the last P V has landed
             if (ok && n_tiles > 0) ok = wait_pv(tcount - 1u);
