@@ -52,7 +52,7 @@ def test_reduce_matches_oracle(ops, cgb, oracle, dtype_name, op, shape, axes):
         ax = {a % len(shape) for a in axes}
         assert tuple(got_t.shape) == tuple(1 if i in ax else d for i, d in enumerate(shape) if keep or i not in ax)
         want = want.reshape(tuple(got_t.shape))   # (the oracle's storage conversion turns a 0-d result into one element)
-        got = _to_host_f32(O, got_t, dtype)
+        got = _to_host_f32(O, got_t, dtype).reshape(tuple(got_t.shape))
         if op == "max":
             assert np.array_equal(got, want), f"reduce_max {shape} {axes}"
         else:
