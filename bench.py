@@ -705,6 +705,7 @@ class AttentionWorkload(Workload):
 
     def __init__(self):
         self.B = int(os.environ.get("CG_B200_BENCH_ATTENTION_BATCH", "32"))
+        self.sets = 1 if self.B >= 32 else max(2, min(16, 32 // self.B))
 
     def config(self, world):
         return {"workload": f"fused attention softmax(Q K^T / 8) V, bf16, batch {self.B}, 16 heads, seq 2048, head_dim 64, "
@@ -1078,7 +1079,7 @@ def run_reference_arm(args, rank, world):
     cpu["value"] = v
     line = {"impl": "reference", "metric": METRIC, "value": v, "unit": w.unit, "n_gpus": args.gpus,
             "steps": len(vals), "warmup": args.warmup, "ms_per_step": float(np.median(secs)) * 1e3,
-            "higher_is_better": True, "scaling": "strong" if args.workload in ("gemm", "matmul_f32", "block") else "weak",
+            "higher_is_better": True, "scaling": "strong" if args.workload in ("gemm", "matmul_f32", "block", "attention") else "weak",
             "vs_baseline": None, "dtype": w.dtype, "data": "synthetic", "config": w.config(1),
             "cpu_baseline": cpu,
             "e2e": {"value": v, "unit": w.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
